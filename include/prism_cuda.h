@@ -1,0 +1,266 @@
+/*
+ * prism_cuda.h -- C ABI of the B200 (sm_100a) backend for Prism Engine's
+ * palettized-LUT matmul path.
+ *
+ * This is the boundary a Rust `CudaBackend` (a peer of `MetalBackend`,
+ * src/lut/engine_impl.rs:26-492) binds through `extern "C"`: plain pointers
+ * and sizes, no C++ types.  Each entry point names the reference interface it
+ * replaces (paths relative to the reference repository root).
+ *
+ * Conventions (those of the reference's existing C ABI, prism-ffi/src/lib.rs:18-72):
+ *   - every function returns 0 on success and a negative PRISM_E_* code on
+ *     failure; constructors hand back NULL/-1 handles on failure;
+ *   - prism_cuda_last_error(ctx) gives the text the Rust side would put in
+ *     its `Err(String)`;
+ *   - fp16 values are IEEE binary16 bit patterns carried as uint16_t
+ *     (`&[u16]` in the reference);
+ *   - a context is used from one host thread at a time (the reference wraps
+ *     its engine in a mutex, src/bin/prism_server.rs:282); calls on one
+ *     context are ordered on its stream; entry points taking HOST pointers
+ *     block until the result is in the caller's buffer, `_dev` entry points
+ *     take DEVICE pointers, enqueue on the context stream and return;
+ *   - shape and alignment violations are rejected on the host before any
+ *     launch; nothing here falls back to a CPU implementation.
+ */
+#ifndef PRISM_CUDA_H
+#define PRISM_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PRISM_OK 0
+#define PRISM_E_NULL (-1)      /* null argument */
+#define PRISM_E_ARG (-2)       /* bad shape / size / alignment / unsupported bits */
+#define PRISM_E_NOTFOUND (-3)  /* unknown tensor key or handle ("miss {key}") */
+#define PRISM_E_CUDA (-4)      /* CUDA runtime error (text in last_error) */
+#define PRISM_E_STATE (-5)     /* call not valid in this state (e.g. KV cache full) */
+#define PRISM_E_IO (-6)        /* file / container error */
+#define PRISM_E_COMM (-7)      /* collective (NCCL) error */
+#define PRISM_E_TIMEOUT (-8)   /* a bounded device-side wait gave up */
+
+typedef struct prism_cuda_ctx prism_cuda_ctx;
+typedef struct prism_cuda_engine prism_cuda_engine;
+
+/* ---- context: MetalBackend::new (src/lut/engine_impl.rs:51-153) ---------- */
+
+/* Creates a backend on CUDA device `device`.  Fails (no fallback) when the
+ * device is missing or is not compute capability 10.x. */
+int prism_cuda_create(int device, prism_cuda_ctx **out);
+void prism_cuda_destroy(prism_cuda_ctx *ctx);
+/* Text of the most recent failure on this context ("" if none).  With a NULL
+ * context: the failure text of the last prism_cuda_create on this thread. */
+const char *prism_cuda_last_error(prism_cuda_ctx *ctx);
+/* The CUDA stream (cudaStream_t) the context launches on. */
+void *prism_cuda_stream(prism_cuda_ctx *ctx);
+int prism_cuda_synchronize(prism_cuda_ctx *ctx);
+/* Tunables: "gemv_variant" (0 = plain CUDA-core kernel, 1 = pair-table
+ * tensor-core kernel, default), "fuse" (0/1, default 1: fused epilogues). */
+int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value);
+/* Number of kernels this library has launched on the context so far. */
+uint64_t prism_cuda_launch_count(prism_cuda_ctx *ctx);
+
+/* ---- weights: the upload loop of MetalBackend::new (engine_impl.rs:123-133)
+ *      and PrismEngine::load (engine_impl.rs:597-676) ---------------------- */
+
+/* Copies one palettized tensor to the device.  `payload` is the UNMODIFIED
+ * split-block byte string of the .cimage container (all palettes, then all
+ * index rows; src/quantization/cimage.rs:98-125, src/lut/compiler.rs:50-61);
+ * it is re-laid in HBM for coalesced 128-bit loads and the caller keeps
+ * ownership.  bits = 4 (16-entry palette, the reference's only format) or 2
+ * (4-entry palette).  dim_n*bits must be a multiple of 32 (the reference
+ * needs dim_n % 8 == 0, cpu_fallback.rs:24).  *handle receives a tensor id. */
+int prism_cuda_upload_palettized(prism_cuda_ctx *ctx, const char *name, const uint8_t *payload,
+                                 size_t len, uint32_t dim_m, uint32_t dim_n, uint32_t bits,
+                                 int32_t *handle);
+/* Same, keeping only rows [row0,row0+rows) and columns [col0,col0+cols) of the
+ * tensor: the shard a tensor-parallel rank owns.  col0 and cols must be
+ * multiples of 128/bits. */
+int prism_cuda_upload_palettized_shard(prism_cuda_ctx *ctx, const char *name,
+                                       const uint8_t *payload, size_t len, uint32_t dim_m,
+                                       uint32_t dim_n, uint32_t bits, uint32_t row0, uint32_t rows,
+                                       uint32_t col0, uint32_t cols, int32_t *handle);
+/* Synthesises a tensor of the benchmark distribution directly on the device
+ * (palette entries N(0, sigma) sorted ascending, uniform indices; seeded).
+ * Used where a model is too large to stage through host memory. */
+int prism_cuda_synth_palettized(prism_cuda_ctx *ctx, const char *name, uint32_t dim_m,
+                                uint32_t dim_n, uint32_t bits, uint64_t seed, float sigma,
+                                int32_t *handle);
+/* Looks a tensor up by the key it was uploaded under (weight_bufs.get(key),
+ * engine_impl.rs:156-159). */
+int prism_cuda_find_tensor(prism_cuda_ctx *ctx, const char *name, int32_t *handle);
+int prism_cuda_tensor_dims(prism_cuda_ctx *ctx, int32_t handle, uint32_t *dim_m, uint32_t *dim_n,
+                           uint32_t *bits);
+/* Inverse of the re-lay: writes the tensor back as a reference-format payload
+ * (len must equal dim_m*2^bits*2 + dim_m*dim_n*bits/8). */
+int prism_cuda_download_payload(prism_cuda_ctx *ctx, int32_t handle, uint8_t *payload, size_t len);
+/* Dequantised weights, row-major [dim_m][dim_n] fp16 bit patterns: the gather
+ * of PrismEngine::embed (engine_impl.rs:1407-1446) / dequantize_matrix
+ * (src/quantization/palette.rs:280-292) for every row.  Bit-exact. */
+int prism_cuda_dequant(prism_cuda_ctx *ctx, int32_t handle, uint16_t *out_host);
+int prism_cuda_dequant_dev(prism_cuda_ctx *ctx, int32_t handle, void *out_dev);
+int prism_cuda_free_tensor(prism_cuda_ctx *ctx, int32_t handle);
+/* Uploads every Palettized4Bit tensor of a reference-format .cimage file
+ * (src/quantization/cimage.rs:242-277) under its own key; *n_out = tensors uploaded. */
+int prism_cuda_load_cimage(prism_cuda_ctx *ctx, const char *path, uint32_t *n_out);
+
+/* ---- palettized GEMV: MetalBackend::gemv (engine_impl.rs:155-190), i.e.
+ *      lut_gemv_cpu (src/lut/cpu_fallback.rs:12-35) on the device ---------- */
+
+/* y[dim_m] = f16( sum_k f32(x[k]) * f32(palette[row][idx[row,k]]) ), fp32 accumulate. */
+int prism_cuda_gemv(prism_cuda_ctx *ctx, int32_t handle, const uint16_t *x, uint16_t *y);
+int prism_cuda_gemv_key(prism_cuda_ctx *ctx, const char *key, const uint16_t *x, size_t x_len,
+                        uint16_t *y, size_t y_len);
+int prism_cuda_gemv_dev(prism_cuda_ctx *ctx, int32_t handle, const void *x_dev, void *y_dev);
+/* y = f16( f32(f16(W x)) + f32(resid) ): GEMV followed by vec_add_inplace, the
+ * OProj / DownProj arms of step() (engine_impl.rs:1158-1162, 1196-1203). */
+int prism_cuda_gemv_residual_dev(prism_cuda_ctx *ctx, int32_t handle, const void *x_dev,
+                                 const void *resid_dev, void *y_dev);
+
+/* ---- fused gate/up SwiGLU: MetalBackend::fused_gate_up (engine_impl.rs:443-490)
+ *      with the CPU path's numerics (engine_impl.rs:1163-1195, 1349-1367) --- */
+
+/* out[i] = f16( f32(f16(silu(g_i))) * f32(u_i) ), g = f16(Wg x), u = f16(Wu x),
+ * silu(g) = g/(1+exp(-g)) in fp32; both GEMVs share one pass over x. */
+int prism_cuda_fused_gate_up(prism_cuda_ctx *ctx, int32_t gate, int32_t up, const uint16_t *x,
+                             uint16_t *out);
+int prism_cuda_fused_gate_up_key(prism_cuda_ctx *ctx, const char *gate_key, const char *up_key,
+                                 const uint16_t *x, size_t x_len, uint16_t *out, size_t out_len);
+int prism_cuda_fused_gate_up_dev(prism_cuda_ctx *ctx, int32_t gate, int32_t up, const void *x_dev,
+                                 void *out_dev);
+/* Whole MLP: out = f16(Wd * fused_gate_up(x)).  The [inter] activation between
+ * the two kernels lives in context-owned scratch memory. */
+int prism_cuda_mlp(prism_cuda_ctx *ctx, int32_t gate, int32_t up, int32_t down, const uint16_t *x,
+                   uint16_t *out);
+int prism_cuda_mlp_dev(prism_cuda_ctx *ctx, int32_t gate, int32_t up, int32_t down,
+                       const void *x_dev, void *out_dev);
+
+/* ---- prefill GEMM: the palettized_gemm kernel (templates/palettized_gemm.metal:16-117),
+ *      with the CPU prefill's numerics: one lut_gemv_cpu per activation row
+ *      (prefill_cpu, engine_impl.rs:1046-1053) ----------------------------- */
+
+/* Y[m_tok][dim_m] = X[m_tok][dim_n] * W^T, fp16 in, fp32 accumulate, fp16 out. */
+int prism_cuda_gemm(prism_cuda_ctx *ctx, int32_t handle, const uint16_t *X, uint32_t m_tok,
+                    uint16_t *Y);
+int prism_cuda_gemm_dev(prism_cuda_ctx *ctx, int32_t handle, const void *X_dev, uint32_t m_tok,
+                        void *Y_dev);
+
+/* ---- decode glue: MetalBackend::{norm_metal, rope_metal, softmax_metal,
+ *      silu_metal, vec_add_metal, attention, append_kv} (engine_impl.rs:194-441)
+ *      with the CPU ops' numerics (src/lut/cpu_fallback.rs:39-143) ---------- */
+
+/* rms_norm_inplace (cpu_fallback.rs:39-54): no learned weight. */
+int prism_cuda_rms_norm(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint32_t n, float eps);
+/* rope_inplace (cpu_fallback.rs:131-143): half-split pairs, base passed explicitly
+ * (the reference CPU path always uses 10000). */
+int prism_cuda_rope(prism_cuda_ctx *ctx, uint16_t *x, uint32_t n, int64_t pos, uint32_t head_dim,
+                    float base);
+int prism_cuda_softmax(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint32_t n);
+int prism_cuda_silu(prism_cuda_ctx *ctx, uint16_t *x, uint32_t n);
+int prism_cuda_vec_add(prism_cuda_ctx *ctx, uint16_t *a, const uint16_t *b, uint32_t n);
+/* attention_cpu (cpu_fallback.rs:84-127): GQA decode attention of one query
+ * token over `seq_len` cached positions, K/V laid [pos][kv_head][head_dim]. */
+int prism_cuda_attention(prism_cuda_ctx *ctx, const uint16_t *q, const uint16_t *k,
+                         const uint16_t *v, uint32_t seq_len, uint32_t num_heads,
+                         uint32_t kv_heads, uint32_t head_dim, uint16_t *out);
+/* argmax (engine_impl.rs:1448-1459): first strictly greatest. */
+int prism_cuda_argmax(prism_cuda_ctx *ctx, const uint16_t *logits, uint32_t n, uint32_t *index);
+
+/* ---- engine: PrismEngine (src/lut/engine_impl.rs:503-512; load :597, generate
+ *      :933-1044, step :1076-1405) with every op on the device -------------- */
+
+typedef struct prism_model_config {
+    /* the fields UnifiedConfig reads from config.json (src/lut/graph.rs:164-292) */
+    uint32_t num_layers, hidden_size, num_heads, num_kv_heads, head_dim, intermediate_size,
+        vocab_size;
+    float norm_eps, rope_theta;
+    uint32_t tie_word_embeddings;
+    uint32_t bits;       /* 4 (reference) or 2 */
+    uint32_t max_seq;    /* KV capacity in positions (MAX_SEQ = 4096 in the reference) */
+    uint32_t max_batch;  /* concurrent sequences (the reference has 1) */
+    /* behaviour switches; the reference CPU path is {0, 0, 1, 1} */
+    uint32_t rope_use_theta; /* 0: base 10000 regardless of rope_theta (cpu_fallback.rs:137) */
+    uint32_t rope_k;         /* 0: K cached un-rotated (engine_impl.rs:1131 precedes :1211) */
+    uint32_t kv_int8;        /* 1: int8 + f32 scale per token (engine_impl.rs:516-567) */
+    uint32_t down_guard;     /* 1: keep the dim test at engine_impl.rs:1124-1126 that skips
+                                DownProj when intermediate_size != hidden_size */
+} prism_model_config;
+
+/* Tensor roles of TensorRole (src/lut/graph.rs) as used by step(). */
+enum {
+    PRISM_ROLE_Q = 0, PRISM_ROLE_K = 1, PRISM_ROLE_V = 2, PRISM_ROLE_O = 3, PRISM_ROLE_GATE = 4,
+    PRISM_ROLE_UP = 5, PRISM_ROLE_DOWN = 6, PRISM_ROLE_EMBED = 7, PRISM_ROLE_LM_HEAD = 8
+};
+
+int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg,
+                             prism_cuda_engine **out);
+void prism_cuda_engine_destroy(prism_cuda_engine *eng);
+/* Binds an uploaded tensor to (role, layer); layer is ignored for EMBED / LM_HEAD. */
+int prism_cuda_engine_bind(prism_cuda_engine *eng, uint32_t role, uint32_t layer, int32_t handle);
+/* Binds by the reference's tensor keys, "model.layers.{i}.self_attn.q_proj.weight" ...
+ * (src/lut/graph.rs:304-531), for every tensor already uploaded to the context. */
+int prism_cuda_engine_bind_by_keys(prism_cuda_engine *eng, const char *key_prefix);
+/* PrismEngine::load: reads a reference-format .cimage (src/quantization/cimage.rs:242-277),
+ * uploads every palettized tensor and binds it. */
+int prism_cuda_engine_load_cimage(prism_cuda_engine *eng, const char *path, const char *key_prefix);
+/* Fills every weight of the model with seeded synthetic tensors on the device. */
+int prism_cuda_engine_synth_weights(prism_cuda_engine *eng, uint64_t seed, float sigma);
+/* PrismEngine::generate for `batch` sequences at once: prompts is
+ * [batch][n_prompt] token ids, out_tokens receives [batch][max_new].  Prefill is
+ * one step per prompt token and the first decode step re-feeds the last prompt
+ * token, as the reference does (engine_impl.rs:1015,1034,1046-1053).
+ * last_logits (optional) receives the fp16 logits [batch][vocab] of the final step. */
+int prism_cuda_engine_generate(prism_cuda_engine *eng, const uint32_t *prompts, uint32_t batch,
+                               uint32_t n_prompt, uint32_t max_new, uint32_t *out_tokens,
+                               uint16_t *last_logits);
+/* Finer-grained driving (what generate() is made of). */
+int prism_cuda_engine_reset(prism_cuda_engine *eng, uint32_t batch);
+/* One step(): feeds tokens[batch] at the current position, advances it, and
+ * returns the greedy next tokens; logits (optional, host) gets [batch][vocab]. */
+int prism_cuda_engine_step(prism_cuda_engine *eng, const uint32_t *tokens, uint32_t *next_tokens,
+                           uint16_t *logits);
+/* Runs `n_steps` decode steps back to back on the device, each feeding the
+ * previous step's greedy token (no host round trip between steps); tokens_in
+ * [batch] seeds the first step, out_tokens receives [batch][n_steps]. */
+int prism_cuda_engine_decode(prism_cuda_engine *eng, const uint32_t *tokens_in, uint32_t n_steps,
+                             uint32_t *out_tokens);
+/* Algorithmic HBM bytes of one decode step at the current position (weights +
+ * KV read), and the device time of the last generate/decode call. */
+uint64_t prism_cuda_engine_step_bytes(prism_cuda_engine *eng);
+/* Device time of the last generate/decode call: whole call including the
+ * host<->device token copies (last_ms) and the kernel region only (last_device_ms). */
+double prism_cuda_engine_last_ms(prism_cuda_engine *eng);
+double prism_cuda_engine_last_device_ms(prism_cuda_engine *eng);
+uint32_t prism_cuda_engine_position(prism_cuda_engine *eng);
+/* Kernels one step launches (counted when the step was first enqueued). */
+uint32_t prism_cuda_engine_kernels_per_step(prism_cuda_engine *eng);
+/* Measurement: times only the palettized GEMV launches of a decode step, `reps`
+ * passes over every weight of the model between two events on the context
+ * stream; returns elapsed ms, algorithmic bytes moved and launches issued. */
+int prism_cuda_engine_profile_gemv(prism_cuda_engine *eng, uint32_t reps, double *ms_out,
+                                   uint64_t *bytes_out, uint32_t *launches_out);
+/* Measurement: cycles through n_sets distinct weight sets (working set > L2) inside one
+ * CUDA graph replayed `reps` times.  kind 0 = GEMV (1 handle per set), 1 = fused
+ * gate/up (gate, up), 2 = MLP (gate, up, down). */
+int prism_cuda_bench_cycle(prism_cuda_ctx *ctx, int kind, const int32_t *handles, uint32_t n_sets,
+                           uint32_t reps, double *ms_out);
+
+/* ---- tensor parallelism (not in the reference; column/row-sharded linears
+ *      with an all-reduce after each row-parallel matmul) ------------------- */
+
+#define PRISM_NCCL_ID_BYTES 128
+/* Rank 0 fills `id` and hands the bytes to the other ranks (any transport). */
+int prism_cuda_tp_unique_id(uint8_t id[PRISM_NCCL_ID_BYTES]);
+/* Joins this context to a `world`-rank NCCL communicator. */
+int prism_cuda_tp_init(prism_cuda_ctx *ctx, int world, int rank, const uint8_t id[PRISM_NCCL_ID_BYTES]);
+int prism_cuda_tp_world(prism_cuda_ctx *ctx, int *world, int *rank);
+/* In-place fp16 sum over ranks of a device vector, on the context stream. */
+int prism_cuda_tp_all_reduce_dev(prism_cuda_ctx *ctx, void *buf_dev, size_t n_halfs);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PRISM_CUDA_H */

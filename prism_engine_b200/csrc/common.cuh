@@ -1,0 +1,176 @@
+// Shared declarations of the CUDA backend: device layout of a palettized
+// tensor, the context object behind the C ABI, and launch helpers.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/prism_cuda.h"
+
+namespace prism {
+
+// ---------------------------------------------------------------------------
+// Device layout of one palettized tensor ("re-laid" form of the .cimage
+// split-block payload, src/quantization/cimage.rs:98-125).
+//
+//   pal : [m_pad][2^bits] fp16      palette of every row, rows >= m are zero
+//   idx : [n_hb][n_chunks][32][16 B]
+//         half-block hb = rows hb*32 .. hb*32+31, chunk c = bytes 16c..16c+15
+//         of each row's packed index string (32 weights at 4 bit, 64 at 2 bit).
+//
+// One warp-wide 128-bit load therefore fetches the same 16-byte chunk of 32
+// consecutive rows as one contiguous 512-byte line, and a half-block's whole K
+// range is one contiguous run of n_chunks*512 bytes.  m_pad is a multiple of
+// 64 so a CTA can always read two half-blocks.
+// ---------------------------------------------------------------------------
+struct LutTensor {
+    std::string name;
+    uint32_t m = 0, k = 0, bits = 4;
+    uint32_t m_pad = 0, n_hb = 0;
+    uint32_t row_bytes = 0;  // k*bits/8
+    uint32_t n_chunks = 0;   // ceil(row_bytes/16)
+    uint8_t *idx = nullptr;
+    uint16_t *pal = nullptr;
+    size_t idx_bytes = 0, pal_bytes = 0;
+    bool live = false;
+    uint32_t n_ent() const { return 1u << bits; }
+    // bytes a GEMV over this tensor must move: indices + palettes + x + y
+    uint64_t algorithmic_bytes() const {
+        return (uint64_t)m * row_bytes + (uint64_t)m * n_ent() * 2 + 2ull * k + 2ull * m;
+    }
+};
+
+__host__ __device__ inline uint32_t round_up_u32(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+__host__ __device__ inline size_t lut_idx_offset(uint32_t n_chunks, uint32_t hb, uint32_t chunk,
+                                                 uint32_t lane) {
+    return ((size_t)hb * n_chunks + chunk) * 512 + (size_t)lane * 16;
+}
+
+}  // namespace prism
+
+struct prism_nccl_api;
+
+// The opaque context of the C ABI.
+struct prism_cuda_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    std::string err;
+    std::vector<prism::LutTensor> tensors;
+    std::unordered_map<std::string, int32_t> by_name;
+    // options
+    int gemv_variant = 1;
+    int fuse = 1;
+    uint64_t launches = 0;
+    // staging for host-pointer entry points (grown on demand)
+    uint8_t *stage_in = nullptr, *stage_out = nullptr;
+    size_t stage_in_bytes = 0, stage_out_bytes = 0;
+    // scratch for split-K partial sums, arrival counters, MLP activation
+    float *splitk_partials = nullptr;
+    size_t splitk_floats = 0;
+    unsigned int *splitk_counters = nullptr;
+    size_t splitk_counter_n = 0;
+    uint16_t *act_scratch = nullptr;
+    size_t act_halfs = 0;
+    uint16_t *tmp_scratch = nullptr;  // gate/up outputs of the unfused SwiGLU path
+    size_t tmp_halfs = 0;
+    // tensor parallel
+    int tp_world = 1, tp_rank = 0;
+    void *nccl_comm = nullptr;
+    prism_nccl_api *nccl = nullptr;
+};
+
+namespace prism {
+
+int fail(prism_cuda_ctx *ctx, int code, const std::string &msg);
+int cuda_fail(prism_cuda_ctx *ctx, cudaError_t e, const char *what);
+
+#define PRISM_CUDA_TRY(ctx, expr)                                         \
+    do {                                                                  \
+        cudaError_t _e = (expr);                                          \
+        if (_e != cudaSuccess) return prism::cuda_fail((ctx), _e, #expr); \
+    } while (0)
+
+#define PRISM_TRY(expr)           \
+    do {                          \
+        int _rc = (expr);         \
+        if (_rc != 0) return _rc; \
+    } while (0)
+
+// Checks the launch that was just issued and counts it.
+int after_launch(prism_cuda_ctx *ctx, const char *kernel);
+
+int ensure_stage(prism_cuda_ctx *ctx, size_t in_bytes, size_t out_bytes);
+int ensure_splitk(prism_cuda_ctx *ctx, size_t floats, size_t counters);
+int ensure_act(prism_cuda_ctx *ctx, size_t halfs);
+int ensure_tmp(prism_cuda_ctx *ctx, size_t halfs);
+LutTensor *get_tensor(prism_cuda_ctx *ctx, int32_t handle);
+
+// ---- kernels' host-side launchers (device pointers, context stream) -------
+
+// relay.cu
+int launch_relay(prism_cuda_ctx *ctx, const uint8_t *payload_dev, uint32_t src_m, uint32_t src_k,
+                 uint32_t row0, uint32_t col0, LutTensor &t);
+int launch_unrelay(prism_cuda_ctx *ctx, const LutTensor &t, uint8_t *payload_dev);
+int launch_dequant(prism_cuda_ctx *ctx, const LutTensor &t, uint16_t *out_dev);
+int launch_synth(prism_cuda_ctx *ctx, LutTensor &t, uint64_t seed, float sigma, uint32_t row0, uint32_t col0);
+int launch_embed(prism_cuda_ctx *ctx, const LutTensor &t, const uint32_t *tokens_dev, uint32_t batch,
+                 uint16_t *out_dev, uint16_t *out2_dev);
+
+// gemv.cu
+enum GemvMode { GEMV_PLAIN = 0, GEMV_RESID = 1, GEMV_SWIGLU = 2, GEMV_F32 = 3 };
+// y[b] = W x[b] for b < batch; x rows are x_stride halfs apart, y rows y_stride.
+// GEMV_RESID adds resid (same strides as y) after rounding to fp16.
+// GEMV_SWIGLU: t = gate, t2 = up, y = f16(f16(silu(f16(g))) * f16(u)).
+// GEMV_F32: y is float[batch][y_stride], the unrounded sums (partial products of a
+// K-sharded tensor-parallel rank, reduced across ranks before rounding).
+int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2,
+                const uint16_t *x, uint32_t x_stride, uint16_t *y, uint32_t y_stride,
+                const uint16_t *resid, uint32_t batch);
+
+// glue.cu
+int launch_rms_norm(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint32_t n, float eps,
+                    uint32_t batch);
+int launch_rope(prism_cuda_ctx *ctx, uint16_t *x, uint32_t n, const int32_t *pos_dev, int64_t pos_host,
+                uint32_t head_dim, float base, uint32_t batch);
+int launch_vec_add(prism_cuda_ctx *ctx, uint16_t *a, const uint16_t *b, uint32_t n);
+int launch_silu(prism_cuda_ctx *ctx, uint16_t *x, uint32_t n);
+int launch_silu_mul(prism_cuda_ctx *ctx, uint16_t *out, const uint16_t *g, const uint16_t *u, uint32_t n);
+int launch_softmax(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint32_t n);
+int launch_argmax(prism_cuda_ctx *ctx, const uint16_t *logits, uint32_t n, uint32_t stride, uint32_t batch,
+                  uint32_t *out_dev);
+struct AttnArgs {
+    const uint16_t *q;      // [batch][nh*hd]
+    const void *k, *v;      // cache base of this layer slot
+    uint16_t *out;          // [batch][nh*hd]
+    // cached positions = pos*slot_mul + slot_add + 1, pos read from pos_dev (device scalar,
+    // so a captured graph can be replayed) or pos_host when pos_dev == nullptr
+    const int32_t *pos_dev; int32_t pos_host; uint32_t slot_mul, slot_add;
+    uint32_t nh, nkv, hd, batch;
+    uint64_t seq_stride;    // elements (fp16) or bytes (int8) between sequences in the cache
+    uint32_t int8;          // cache holds [f32 scale][kvd x i8] per position
+    uint32_t max_seq;
+};
+int launch_attention(prism_cuda_ctx *ctx, const AttnArgs &a);
+struct KvAppendArgs {
+    const uint16_t *k, *v;  // [batch][kvd]
+    void *kc, *vc;
+    const int32_t *pos_dev; int32_t pos_host; uint32_t slot_mul, slot_add;  // slot = pos*mul+add
+    uint32_t kvd, batch; uint64_t seq_stride; uint32_t int8; uint32_t max_seq;
+};
+int launch_kv_append(prism_cuda_ctx *ctx, const KvAppendArgs &a);
+
+}  // namespace prism
+
+namespace prism {
+int synth_shard(prism_cuda_ctx *ctx, const char *name, uint32_t rows, uint32_t cols, uint32_t bits,
+                uint64_t seed, float sigma, uint32_t row0, uint32_t col0, int32_t *handle);
+// gemm.cu: Y[m_tok][m] = X[m_tok][k] * W^T (fp16 in/out, fp32 accumulate)
+int launch_gemm(prism_cuda_ctx *ctx, const LutTensor &t, const uint16_t *X, uint32_t m_tok, uint16_t *Y);
+}  // namespace prism

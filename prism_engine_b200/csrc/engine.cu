@@ -1,0 +1,686 @@
+// Device-resident twin of PrismEngine (src/lut/engine_impl.rs:503-512): the
+// node walk of step() (:1076-1405) for the Qwen2-family graph that
+// ModelGraph::build emits (src/lut/graph.rs:304-531) --
+//   Norm, Q, K, V, RoPE, SDPA, O, Norm, Gate, Up, Activation, Down   per layer,
+//   final Norm, LM head (or the tied embedding table)
+// -- enqueued as one fixed kernel sequence whose position-dependent values are
+// read from device memory, so the whole step is captured once in a CUDA graph
+// and replayed per token with no host round trip.  generate() follows
+// engine_impl.rs:933-1044: prefill is one step per prompt token and the first
+// decode step feeds the last prompt token again.
+#include <algorithm>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace prism {
+int tp_all_reduce_f32(prism_cuda_ctx *ctx, float *buf, size_t n);
+int tp_all_gather_bytes(prism_cuda_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank);
+int synth_shard(prism_cuda_ctx *ctx, const char *name, uint32_t rows, uint32_t cols, uint32_t bits,
+                uint64_t seed, float sigma, uint32_t row0, uint32_t col0, int32_t *handle);
+}  // namespace prism
+
+struct prism_cuda_engine {
+    prism_cuda_ctx *ctx = nullptr;
+    prism_model_config cfg{};
+    int T = 1, rank = 0;
+    // local (per-rank) dimensions
+    uint32_t H = 0, nh_l = 0, nkv_l = 0, hd = 0, qd_l = 0, kvd_l = 0, I_l = 0, V_l = 0;
+    uint32_t head0 = 0, kvhead0 = 0, i0 = 0, v0 = 0;  // first local q head / kv head / inter row / vocab row
+    std::vector<int32_t> wq, wk, wv, wo, wg, wu, wd;
+    int32_t embed = -1, lm_head = -1;
+    // activations
+    uint16_t *h = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr,
+             *act = nullptr, *logits = nullptr;
+    float *part = nullptr;       // [B][H] fp32 partial sums of row-parallel matmuls (TP)
+    uint32_t *tok = nullptr, *next = nullptr, *out_tokens = nullptr, *prompts = nullptr;
+    uint64_t *pairs_send = nullptr, *pairs_recv = nullptr;  // TP argmax: (value bits << 32 | ~index)
+    int32_t *scalars = nullptr;  // [0] pos, [1] step, [2] record
+    size_t prompts_cap = 0;
+    uint32_t act_stride = 0, out_cap = 0;
+    void *kc = nullptr, *vc = nullptr;
+    size_t kv_layer_bytes = 0;
+    uint64_t kv_seq_stride = 0;  // fp16: elements, int8: bytes
+    uint32_t kv_slots = 0;       // positions a layer slot can hold
+    uint32_t batch = 0, pos = 0;
+    bool guard_skip = false;     // down_guard && inter != hidden
+    cudaGraphExec_t graph = nullptr;
+    uint32_t graph_batch = 0;
+    int graph_variant = -1, graph_fuse = -1;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr, ev3 = nullptr;
+    double last_ms = 0.0, last_device_ms = 0.0;
+    uint32_t kernels_per_step = 0;
+};
+
+namespace prism {
+
+static void split_units(uint32_t total_units, int T, int r, uint32_t *u0, uint32_t *u1) {
+    *u0 = (uint32_t)((uint64_t)total_units * r / T);
+    *u1 = (uint32_t)((uint64_t)total_units * (r + 1) / T);
+}
+
+// h = f16( f32(f16(sum)) + f32(h) ): the rounding of a GEMV output followed by
+// vec_add_inplace with the residual (engine_impl.rs:1158-1162), applied to the
+// all-reduced fp32 sums of a row-parallel matmul.
+__global__ void round_add_resid_kernel(const float *__restrict__ sum, uint16_t *__restrict__ h, uint32_t n) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        float y = __half2float(__float2half_rn(sum[i]));
+        h[i] = __half_as_ushort(__float2half_rn(y + __half2float(__ushort_as_half(h[i]))));
+    }
+}
+
+// End of a step: pos += 1; when recording, out_tokens[b][step] = next[b],
+// tok[b] = next[b] (the greedy token feeds the next step), step += 1.
+__global__ void advance_kernel(int32_t *scalars, const uint32_t *__restrict__ next, uint32_t *__restrict__ tok,
+                               uint32_t *__restrict__ out_tokens, uint32_t batch, uint32_t out_cap) {
+    const int32_t step = scalars[1], record = scalars[2];
+    if (record) {
+        for (uint32_t b = threadIdx.x; b < batch; b += blockDim.x) {
+            const uint32_t t = next[b];
+            tok[b] = t;
+            if ((uint32_t)step < out_cap) out_tokens[(size_t)b * out_cap + step] = t;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        scalars[0] += 1;
+        if (record) scalars[1] = step + 1;
+    }
+}
+
+// Tensor-parallel argmax.  Each rank reduces its vocabulary slice to one
+// (value, global index) pair per sequence, packed so that a plain unsigned
+// max picks the greatest value and, among equals, the smallest index --
+// argmax's "first strictly greatest" (engine_impl.rs:1448-1459).
+__device__ __forceinline__ uint64_t pack_pair(float v, uint32_t idx) {
+    uint32_t b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // monotone map of float order to unsigned order
+    return ((uint64_t)b << 32) | (uint32_t)(~idx);
+}
+__global__ void local_pair_kernel(const uint16_t *__restrict__ logits, uint32_t n, uint32_t stride,
+                                  uint32_t idx0, uint64_t *__restrict__ pairs) {
+    __shared__ uint64_t sh[32];
+    const uint16_t *lg = logits + (size_t)blockIdx.x * stride;
+    uint64_t best = 0;  // below every real value; index 0 wins if nothing compares greater than -inf
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        float f = __half2float(__ushort_as_half(lg[i]));
+        if (f > -INFINITY) {  // NaN and -inf never win, as in the reference
+            uint64_t p = pack_pair(f, idx0 + i);
+            best = p > best ? p : best;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        uint64_t other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (uint32_t w = 1; w < (blockDim.x >> 5); w++) best = sh[w] > best ? sh[w] : best;
+        pairs[blockIdx.x] = best;
+    }
+}
+__global__ void final_pair_kernel(const uint64_t *__restrict__ pairs, uint32_t batch, int T,
+                                  uint32_t *__restrict__ next) {
+    uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    uint64_t best = 0;
+    for (int r = 0; r < T; r++) {
+        uint64_t p = pairs[(size_t)r * batch + b];
+        best = p > best ? p : best;
+    }
+    next[b] = best ? ~(uint32_t)(best & 0xFFFFFFFFu) : 0u;
+}
+
+static int enqueue_step(prism_cuda_engine *e) {
+    prism_cuda_ctx *ctx = e->ctx;
+    const prism_model_config &c = e->cfg;
+    const uint32_t B = e->batch, H = e->H;
+    const float base = c.rope_use_theta ? c.rope_theta : 10000.0f;
+    const int32_t *pos_dev = e->scalars;
+    const bool tp = e->T > 1;
+    const bool fused = ctx->fuse != 0;
+    const LutTensor &emb = ctx->tensors[e->embed];
+    PRISM_TRY(launch_embed(ctx, emb, e->tok, B, e->h, nullptr));
+    uint32_t li = 0;
+    for (uint32_t l = 0; l < c.num_layers; l++) {
+        const LutTensor &tq = ctx->tensors[e->wq[l]], &tk = ctx->tensors[e->wk[l]], &tv = ctx->tensors[e->wv[l]],
+                        &to = ctx->tensors[e->wo[l]], &tg = ctx->tensors[e->wg[l]], &tu = ctx->tensors[e->wu[l]];
+        PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
+        PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tq, nullptr, e->xn, H, e->q, e->qd_l, nullptr, B));
+        PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, e->kvd_l, nullptr, B));
+        PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, e->kvd_l, nullptr, B));
+        if (c.rope_k) PRISM_TRY(launch_rope(ctx, e->k, e->kvd_l, pos_dev, 0, e->hd, base, B));
+        const uint32_t slot_mul = e->guard_skip ? c.num_layers : 1, slot_add = e->guard_skip ? l : 0;
+        KvAppendArgs ka{};
+        ka.k = e->k; ka.v = e->v;
+        ka.kc = (char *)e->kc + (size_t)li * e->kv_layer_bytes;
+        ka.vc = (char *)e->vc + (size_t)li * e->kv_layer_bytes;
+        ka.pos_dev = pos_dev; ka.slot_mul = slot_mul; ka.slot_add = slot_add;
+        ka.kvd = e->kvd_l; ka.batch = B; ka.seq_stride = e->kv_seq_stride; ka.int8 = c.kv_int8; ka.max_seq = e->kv_slots;
+        PRISM_TRY(launch_kv_append(ctx, ka));
+        PRISM_TRY(launch_rope(ctx, e->q, e->qd_l, pos_dev, 0, e->hd, base, B));
+        AttnArgs aa{};
+        aa.q = e->q; aa.k = ka.kc; aa.v = ka.vc; aa.out = e->att;
+        aa.pos_dev = pos_dev; aa.slot_mul = slot_mul; aa.slot_add = slot_add;
+        aa.nh = e->nh_l; aa.nkv = e->nkv_l; aa.hd = e->hd; aa.batch = B;
+        aa.seq_stride = e->kv_seq_stride; aa.int8 = c.kv_int8; aa.max_seq = e->kv_slots;
+        PRISM_TRY(launch_attention(ctx, aa));
+        if (tp) {
+            PRISM_TRY(launch_gemv(ctx, GEMV_F32, to, nullptr, e->att, e->qd_l, (uint16_t *)e->part, H, nullptr, B));
+            PRISM_TRY(tp_all_reduce_f32(ctx, e->part, (size_t)B * H));
+            round_add_resid_kernel<<<(B * H + 255) / 256, 256, 0, ctx->stream>>>(e->part, e->h, B * H);
+            PRISM_TRY(after_launch(ctx, "round_add_resid_kernel"));
+        } else if (fused) {
+            PRISM_TRY(launch_gemv(ctx, GEMV_RESID, to, nullptr, e->att, e->qd_l, e->h, H, e->h, B));
+        } else {
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, to, nullptr, e->att, e->qd_l, e->xn, H, nullptr, B));
+            PRISM_TRY(launch_vec_add(ctx, e->xn, e->h, B * H));  // xn = f16(o + hr)
+            PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->h, e->xn, (size_t)B * H * 2, cudaMemcpyDeviceToDevice, ctx->stream));
+        }
+        PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
+        PRISM_TRY(launch_gemv(ctx, GEMV_SWIGLU, tg, &tu, e->xn, H, e->act, e->act_stride, nullptr, B));
+        if (e->guard_skip) continue;  // DownProj skipped by the dim test (engine_impl.rs:1124-1126)
+        const LutTensor &td = ctx->tensors[e->wd[l]];
+        if (tp) {
+            PRISM_TRY(launch_gemv(ctx, GEMV_F32, td, nullptr, e->act, e->act_stride, (uint16_t *)e->part, H, nullptr, B));
+            PRISM_TRY(tp_all_reduce_f32(ctx, e->part, (size_t)B * H));
+            round_add_resid_kernel<<<(B * H + 255) / 256, 256, 0, ctx->stream>>>(e->part, e->h, B * H);
+            PRISM_TRY(after_launch(ctx, "round_add_resid_kernel"));
+        } else if (fused) {
+            PRISM_TRY(launch_gemv(ctx, GEMV_RESID, td, nullptr, e->act, e->act_stride, e->h, H, e->h, B));
+        } else {
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, td, nullptr, e->act, e->act_stride, e->xn, H, nullptr, B));
+            PRISM_TRY(launch_vec_add(ctx, e->xn, e->h, B * H));
+            PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->h, e->xn, (size_t)B * H * 2, cudaMemcpyDeviceToDevice, ctx->stream));
+        }
+        li += 1;
+    }
+    PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
+    const LutTensor &head = ctx->tensors[(c.tie_word_embeddings || e->lm_head < 0) ? e->embed : e->lm_head];
+    const uint32_t lstride = round_up_u32(e->V_l, 8);
+    PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, head, nullptr, e->xn, H, e->logits, lstride, nullptr, B));
+    if (tp) {
+        local_pair_kernel<<<B, 1024, 0, ctx->stream>>>(e->logits, e->V_l, lstride, e->v0, e->pairs_send);
+        PRISM_TRY(after_launch(ctx, "local_pair_kernel"));
+        PRISM_TRY(tp_all_gather_bytes(ctx, e->pairs_send, e->pairs_recv, (size_t)B * 8));
+        final_pair_kernel<<<(B + 63) / 64, 64, 0, ctx->stream>>>(e->pairs_recv, B, e->T, e->next);
+        PRISM_TRY(after_launch(ctx, "final_pair_kernel"));
+    } else {
+        PRISM_TRY(launch_argmax(ctx, e->logits, e->V_l, lstride, B, e->next));
+    }
+    advance_kernel<<<1, 64, 0, ctx->stream>>>(e->scalars, e->next, e->tok, e->out_tokens, B, e->out_cap);
+    return after_launch(ctx, "advance_kernel");
+}
+
+static int check_bound(prism_cuda_engine *e) {
+    if (e->embed < 0) return fail(e->ctx, PRISM_E_STATE, "emb miss: no embedding tensor bound");
+    for (uint32_t l = 0; l < e->cfg.num_layers; l++) {
+        if (e->wq[l] < 0 || e->wk[l] < 0 || e->wv[l] < 0 || e->wo[l] < 0 || e->wg[l] < 0 || e->wu[l] < 0 ||
+            (!e->guard_skip && e->wd[l] < 0))
+            return fail(e->ctx, PRISM_E_STATE, "layer " + std::to_string(l) + " has unbound tensors");
+    }
+    return PRISM_OK;
+}
+
+static int capacity_ok(prism_cuda_engine *e, uint32_t steps) {
+    const uint64_t need = e->guard_skip ? (uint64_t)(e->pos + steps) * e->cfg.num_layers : (uint64_t)e->pos + steps;
+    if (need > e->kv_slots)
+        return fail(e->ctx, PRISM_E_STATE, "KV cache full: " + std::to_string(need) + " > " + std::to_string(e->kv_slots));
+    return PRISM_OK;
+}
+
+// Runs one step: the first call per (batch, options) runs eagerly (this sizes
+// every scratch buffer and sets kernel attributes), the second captures the
+// graph, later ones replay it.
+static int run_step(prism_cuda_engine *e) {
+    prism_cuda_ctx *ctx = e->ctx;
+    const bool graph_ok = e->graph && e->graph_batch == e->batch && e->graph_variant == ctx->gemv_variant &&
+                          e->graph_fuse == ctx->fuse;
+    if (graph_ok) {
+        PRISM_CUDA_TRY(ctx, cudaGraphLaunch(e->graph, ctx->stream));
+        ctx->launches += 1;
+        return PRISM_OK;
+    }
+    if (e->graph_batch != e->batch || e->graph_variant != ctx->gemv_variant || e->graph_fuse != ctx->fuse) {
+        // configuration changed: drop the old graph and warm up eagerly once
+        if (e->graph) {
+            cudaGraphExecDestroy(e->graph);
+            e->graph = nullptr;
+        }
+        e->graph_batch = e->batch;
+        e->graph_variant = ctx->gemv_variant;
+        e->graph_fuse = ctx->fuse;
+        const uint64_t l0 = ctx->launches;
+        PRISM_TRY(enqueue_step(e));
+        e->kernels_per_step = (uint32_t)(ctx->launches - l0);
+        return PRISM_OK;
+    }
+    cudaGraph_t g = nullptr;
+    PRISM_CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    const uint64_t before = ctx->launches;
+    int rc = enqueue_step(e);
+    cudaError_t ce = cudaStreamEndCapture(ctx->stream, &g);
+    ctx->launches = before;
+    if (rc != PRISM_OK) {
+        if (g) cudaGraphDestroy(g);
+        return rc;
+    }
+    if (ce != cudaSuccess) return cuda_fail(ctx, ce, "cudaStreamEndCapture");
+    ce = cudaGraphInstantiate(&e->graph, g, 0);
+    cudaGraphDestroy(g);
+    if (ce != cudaSuccess) {
+        e->graph = nullptr;
+        return cuda_fail(ctx, ce, "cudaGraphInstantiate");
+    }
+    PRISM_CUDA_TRY(ctx, cudaGraphLaunch(e->graph, ctx->stream));
+    ctx->launches += 1;
+    return PRISM_OK;
+}
+
+static int set_scalars(prism_cuda_engine *e, int32_t pos, int32_t step, int32_t record) {
+    int32_t v[3] = {pos, step, record};
+    // pageable source: the copy is complete on return, `v` may go out of scope
+    PRISM_CUDA_TRY(e->ctx, cudaMemcpyAsync(e->scalars, v, sizeof v, cudaMemcpyHostToDevice, e->ctx->stream));
+    PRISM_CUDA_TRY(e->ctx, cudaStreamSynchronize(e->ctx->stream));
+    return PRISM_OK;
+}
+
+}  // namespace prism
+
+using namespace prism;
+
+extern "C" {
+
+int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg, prism_cuda_engine **out) {
+    if (!ctx || !cfg || !out) return fail(ctx, PRISM_E_NULL, "null argument");
+    *out = nullptr;
+    const prism_model_config &c = *cfg;
+    if (!c.num_layers || !c.hidden_size || !c.num_heads || !c.num_kv_heads || !c.head_dim ||
+        !c.intermediate_size || !c.vocab_size || !c.max_seq || !c.max_batch)
+        return fail(ctx, PRISM_E_ARG, "model config has a zero dimension");
+    if (c.num_heads % c.num_kv_heads) return fail(ctx, PRISM_E_ARG, "num_heads must be a multiple of num_kv_heads");
+    if (c.bits != 2 && c.bits != 4) return fail(ctx, PRISM_E_ARG, "bits must be 2 or 4");
+    if (c.head_dim & 1) return fail(ctx, PRISM_E_ARG, "head_dim must be even");
+    const int T = ctx->tp_world, r = ctx->tp_rank;
+    if (T > 1) {
+        if (c.num_kv_heads % T || c.num_heads % T)
+            return fail(ctx, PRISM_E_ARG, "tensor parallel degree must divide the head counts");
+        if (c.down_guard && c.intermediate_size != c.hidden_size)
+            return fail(ctx, PRISM_E_ARG, "down_guard is a single-GPU reference-compatibility switch");
+        if (c.bits != 4) return fail(ctx, PRISM_E_ARG, "tensor parallel decode needs 4-bit palettes");
+        if ((c.num_heads / T * c.head_dim) % 32 || c.intermediate_size % 32 || c.hidden_size % 32)
+            return fail(ctx, PRISM_E_ARG, "sharded K ranges must be multiples of 32");
+    }
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    prism_cuda_engine *e = new prism_cuda_engine();
+    e->ctx = ctx; e->cfg = c; e->T = T; e->rank = r;
+    e->H = c.hidden_size; e->hd = c.head_dim;
+    e->nh_l = c.num_heads / T; e->nkv_l = c.num_kv_heads / T;
+    e->head0 = e->nh_l * r; e->kvhead0 = e->nkv_l * r;
+    e->qd_l = e->nh_l * e->hd; e->kvd_l = e->nkv_l * e->hd;
+    uint32_t u0, u1;
+    if (T > 1) {
+        split_units(c.intermediate_size / 32, T, r, &u0, &u1);
+        e->i0 = u0 * 32; e->I_l = (u1 - u0) * 32;
+        split_units((c.vocab_size + 31) / 32, T, r, &u0, &u1);
+        e->v0 = u0 * 32; e->V_l = std::min(c.vocab_size, u1 * 32) - e->v0;
+    } else {
+        e->i0 = 0; e->I_l = c.intermediate_size; e->v0 = 0; e->V_l = c.vocab_size;
+    }
+    e->guard_skip = c.down_guard && c.intermediate_size != c.hidden_size;
+    e->kv_slots = e->guard_skip ? c.max_seq * c.num_layers : c.max_seq;
+    if ((size_t)e->kv_slots * 4 > 200 * 1024) {
+        delete e;
+        return fail(ctx, PRISM_E_ARG, "max_seq too large for the attention score buffer (<= 51200 cached positions per layer slot)");
+    }
+    const uint32_t L = c.num_layers, B = c.max_batch;
+    e->wq.assign(L, -1); e->wk.assign(L, -1); e->wv.assign(L, -1); e->wo.assign(L, -1);
+    e->wg.assign(L, -1); e->wu.assign(L, -1); e->wd.assign(L, -1);
+    e->act_stride = round_up_u32(round_up_u32(e->I_l, 64), 8);
+    e->out_cap = c.max_seq;
+    const uint32_t kv_layers = e->guard_skip ? 1 : L;
+    if (c.kv_int8) {
+        e->kv_seq_stride = (uint64_t)e->kv_slots * (e->kvd_l + 4);
+        e->kv_layer_bytes = (size_t)B * e->kv_seq_stride;
+    } else {
+        e->kv_seq_stride = (uint64_t)e->kv_slots * e->kvd_l;
+        e->kv_layer_bytes = (size_t)B * e->kv_seq_stride * 2;
+    }
+    auto A = [&](void **p, size_t bytes) { return cudaMalloc(p, (bytes + 255) / 256 * 256); };
+    cudaError_t ce = cudaSuccess;
+#define ALLOC(ptr, bytes) if (ce == cudaSuccess) ce = A((void **)&(ptr), (bytes))
+    ALLOC(e->h, (size_t)B * e->H * 2);
+    ALLOC(e->xn, (size_t)B * e->H * 2);
+    ALLOC(e->q, (size_t)B * e->qd_l * 2);
+    ALLOC(e->k, (size_t)B * e->kvd_l * 2);
+    ALLOC(e->v, (size_t)B * e->kvd_l * 2);
+    ALLOC(e->att, (size_t)B * e->qd_l * 2);
+    ALLOC(e->act, (size_t)B * e->act_stride * 2);
+    ALLOC(e->logits, (size_t)B * round_up_u32(e->V_l, 8) * 2);
+    ALLOC(e->part, (size_t)B * e->H * 4);
+    ALLOC(e->tok, (size_t)B * 4);
+    ALLOC(e->next, (size_t)B * 4);
+    ALLOC(e->out_tokens, (size_t)B * e->out_cap * 4);
+    ALLOC(e->pairs_send, (size_t)B * 8);
+    ALLOC(e->pairs_recv, (size_t)B * 8 * T);
+    ALLOC(e->scalars, 64);
+    ALLOC(e->kc, e->kv_layer_bytes * kv_layers);
+    ALLOC(e->vc, e->kv_layer_bytes * kv_layers);
+#undef ALLOC
+    if (ce == cudaSuccess) ce = cudaEventCreate(&e->ev0);
+    if (ce == cudaSuccess) ce = cudaEventCreate(&e->ev1);
+    if (ce == cudaSuccess) ce = cudaEventCreate(&e->ev2);
+    if (ce == cudaSuccess) ce = cudaEventCreate(&e->ev3);
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(e->act, 0, (size_t)B * e->act_stride * 2, ctx->stream);
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(e->scalars, 0, 64, ctx->stream);
+    if (ce != cudaSuccess) {
+        prism_cuda_engine_destroy(e);
+        return cuda_fail(ctx, ce, "engine allocation");
+    }
+    e->batch = 1;
+    *out = e;
+    return PRISM_OK;
+}
+
+void prism_cuda_engine_destroy(prism_cuda_engine *e) {
+    if (!e) return;
+    cudaSetDevice(e->ctx->device);
+    cudaStreamSynchronize(e->ctx->stream);
+    if (e->graph) cudaGraphExecDestroy(e->graph);
+    void *ptrs[] = {e->h, e->xn, e->q, e->k, e->v, e->att, e->act, e->logits, e->part, e->tok, e->next,
+                    e->out_tokens, e->prompts, e->pairs_send, e->pairs_recv, e->scalars, e->kc, e->vc};
+    for (void *p : ptrs) cudaFree(p);
+    if (e->ev0) cudaEventDestroy(e->ev0);
+    if (e->ev1) cudaEventDestroy(e->ev1);
+    if (e->ev2) cudaEventDestroy(e->ev2);
+    if (e->ev3) cudaEventDestroy(e->ev3);
+    delete e;
+}
+
+int prism_cuda_engine_bind(prism_cuda_engine *e, uint32_t role, uint32_t layer, int32_t handle) {
+    if (!e) return PRISM_E_NULL;
+    prism_cuda_ctx *ctx = e->ctx;
+    LutTensor *t = get_tensor(ctx, handle);
+    if (!t) return PRISM_E_NOTFOUND;
+    const prism_model_config &c = e->cfg;
+    if (role <= PRISM_ROLE_DOWN && layer >= c.num_layers) return fail(ctx, PRISM_E_ARG, "layer out of range");
+    uint32_t want_m = 0, want_k = 0;
+    std::vector<int32_t> *slot = nullptr;
+    switch (role) {
+    case PRISM_ROLE_Q: want_m = e->qd_l; want_k = e->H; slot = &e->wq; break;
+    case PRISM_ROLE_K: want_m = e->kvd_l; want_k = e->H; slot = &e->wk; break;
+    case PRISM_ROLE_V: want_m = e->kvd_l; want_k = e->H; slot = &e->wv; break;
+    case PRISM_ROLE_O: want_m = e->H; want_k = e->qd_l; slot = &e->wo; break;
+    case PRISM_ROLE_GATE: want_m = e->I_l; want_k = e->H; slot = &e->wg; break;
+    case PRISM_ROLE_UP: want_m = e->I_l; want_k = e->H; slot = &e->wu; break;
+    case PRISM_ROLE_DOWN: want_m = e->H; want_k = e->I_l; slot = &e->wd; break;
+    case PRISM_ROLE_EMBED: want_m = c.vocab_size; want_k = e->H; break;
+    case PRISM_ROLE_LM_HEAD: want_m = e->V_l; want_k = e->H; break;
+    default: return fail(ctx, PRISM_E_ARG, "unknown role");
+    }
+    if (t->m != want_m || t->k != want_k || t->bits != c.bits)
+        return fail(ctx, PRISM_E_ARG, "tensor " + t->name + " is " + std::to_string(t->m) + "x" + std::to_string(t->k) +
+                                          ", role needs " + std::to_string(want_m) + "x" + std::to_string(want_k));
+    if (slot) (*slot)[layer] = handle;
+    else if (role == PRISM_ROLE_EMBED) e->embed = handle;
+    else e->lm_head = handle;
+    if (e->graph) {  // pointers baked into the graph are stale
+        cudaGraphExecDestroy(e->graph);
+        e->graph = nullptr;
+        e->graph_batch = 0;
+    }
+    return PRISM_OK;
+}
+
+int prism_cuda_engine_bind_by_keys(prism_cuda_engine *e, const char *key_prefix) {
+    if (!e) return PRISM_E_NULL;
+    prism_cuda_ctx *ctx = e->ctx;
+    if (e->T > 1) return fail(ctx, PRISM_E_STATE, "bind_by_keys binds whole tensors; shard and bind explicitly under tensor parallelism");
+    const std::string p = key_prefix && *key_prefix ? key_prefix : "model";
+    struct { const char *suffix; uint32_t role; } names[] = {
+        {"self_attn.q_proj.weight", PRISM_ROLE_Q}, {"self_attn.k_proj.weight", PRISM_ROLE_K},
+        {"self_attn.v_proj.weight", PRISM_ROLE_V}, {"self_attn.o_proj.weight", PRISM_ROLE_O},
+        {"mlp.gate_proj.weight", PRISM_ROLE_GATE}, {"mlp.up_proj.weight", PRISM_ROLE_UP},
+        {"mlp.down_proj.weight", PRISM_ROLE_DOWN}};
+    int32_t h;
+    for (uint32_t l = 0; l < e->cfg.num_layers; l++) {
+        for (auto &n : names) {
+            const std::string key = p + ".layers." + std::to_string(l) + "." + n.suffix;
+            PRISM_TRY(prism_cuda_find_tensor(ctx, key.c_str(), &h));
+            PRISM_TRY(prism_cuda_engine_bind(e, n.role, l, h));
+        }
+    }
+    PRISM_TRY(prism_cuda_find_tensor(ctx, (p + ".embed_tokens.weight").c_str(), &h));
+    PRISM_TRY(prism_cuda_engine_bind(e, PRISM_ROLE_EMBED, 0, h));
+    if (!e->cfg.tie_word_embeddings) {
+        // graph.rs:516-524 keys the head "{p}.lm_head.weight"
+        PRISM_TRY(prism_cuda_find_tensor(ctx, (p + ".lm_head.weight").c_str(), &h));
+        PRISM_TRY(prism_cuda_engine_bind(e, PRISM_ROLE_LM_HEAD, 0, h));
+    }
+    return PRISM_OK;
+}
+
+int prism_cuda_engine_synth_weights(prism_cuda_engine *e, uint64_t seed, float sigma) {
+    if (!e) return PRISM_E_NULL;
+    prism_cuda_ctx *ctx = e->ctx;
+    const prism_model_config &c = e->cfg;
+    const uint32_t H = e->H, bits = c.bits;
+    int32_t h;
+    auto S = [&](const std::string &name, uint64_t id, uint32_t rows, uint32_t cols, uint32_t row0, uint32_t col0,
+                 uint32_t role, uint32_t layer) -> int {
+        PRISM_TRY(synth_shard(ctx, name.c_str(), rows, cols, bits, seed * 1000003ull + id, sigma, row0, col0, &h));
+        return prism_cuda_engine_bind(e, role, layer, h);
+    };
+    for (uint32_t l = 0; l < c.num_layers; l++) {
+        const std::string p = "model.layers." + std::to_string(l) + ".";
+        const uint64_t id = (uint64_t)l * 16;
+        PRISM_TRY(S(p + "self_attn.q_proj.weight", id + 0, e->qd_l, H, e->head0 * e->hd, 0, PRISM_ROLE_Q, l));
+        PRISM_TRY(S(p + "self_attn.k_proj.weight", id + 1, e->kvd_l, H, e->kvhead0 * e->hd, 0, PRISM_ROLE_K, l));
+        PRISM_TRY(S(p + "self_attn.v_proj.weight", id + 2, e->kvd_l, H, e->kvhead0 * e->hd, 0, PRISM_ROLE_V, l));
+        PRISM_TRY(S(p + "self_attn.o_proj.weight", id + 3, H, e->qd_l, 0, e->head0 * e->hd, PRISM_ROLE_O, l));
+        PRISM_TRY(S(p + "mlp.gate_proj.weight", id + 4, e->I_l, H, e->i0, 0, PRISM_ROLE_GATE, l));
+        PRISM_TRY(S(p + "mlp.up_proj.weight", id + 5, e->I_l, H, e->i0, 0, PRISM_ROLE_UP, l));
+        PRISM_TRY(S(p + "mlp.down_proj.weight", id + 6, H, e->I_l, 0, e->i0, PRISM_ROLE_DOWN, l));
+    }
+    PRISM_TRY(S("model.embed_tokens.weight", 1ull << 40, c.vocab_size, H, 0, 0, PRISM_ROLE_EMBED, 0));
+    if (!c.tie_word_embeddings)
+        PRISM_TRY(S("model.lm_head.weight", (1ull << 40) + 1, e->V_l, H, e->v0, 0, PRISM_ROLE_LM_HEAD, 0));
+    else if (e->T > 1)  // tied head under TP: this rank's vocabulary rows of the same table
+        PRISM_TRY(S("model.embed_tokens.weight#shard", 1ull << 40, e->V_l, H, e->v0, 0, PRISM_ROLE_LM_HEAD, 0));
+    return PRISM_OK;
+}
+
+int prism_cuda_engine_reset(prism_cuda_engine *e, uint32_t batch) {
+    if (!e) return PRISM_E_NULL;
+    if (batch == 0 || batch > e->cfg.max_batch) return fail(e->ctx, PRISM_E_ARG, "batch outside [1, max_batch]");
+    PRISM_CUDA_TRY(e->ctx, cudaSetDevice(e->ctx->device));
+    e->batch = batch;
+    e->pos = 0;
+    return set_scalars(e, 0, 0, 0);
+}
+
+int prism_cuda_engine_step(prism_cuda_engine *e, const uint32_t *tokens, uint32_t *next_tokens, uint16_t *logits) {
+    if (!e || !tokens) return fail(e ? e->ctx : nullptr, PRISM_E_NULL, "null argument");
+    prism_cuda_ctx *ctx = e->ctx;
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    PRISM_TRY(check_bound(e));
+    PRISM_TRY(capacity_ok(e, 1));
+    PRISM_TRY(set_scalars(e, (int32_t)e->pos, 0, 0));
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->tok, tokens, (size_t)e->batch * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PRISM_TRY(run_step(e));
+    e->pos += 1;
+    if (next_tokens)
+        PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(next_tokens, e->next, (size_t)e->batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (logits) {
+        if (e->T > 1) return fail(ctx, PRISM_E_STATE, "logits are sharded under tensor parallelism");
+        const uint32_t ls = round_up_u32(e->V_l, 8);
+        PRISM_CUDA_TRY(ctx, cudaMemcpy2DAsync(logits, (size_t)e->V_l * 2, e->logits, (size_t)ls * 2, (size_t)e->V_l * 2,
+                                              e->batch, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return PRISM_OK;
+}
+
+int prism_cuda_engine_decode(prism_cuda_engine *e, const uint32_t *tokens_in, uint32_t n_steps, uint32_t *out_tokens) {
+    if (!e || !tokens_in || !out_tokens) return fail(e ? e->ctx : nullptr, PRISM_E_NULL, "null argument");
+    prism_cuda_ctx *ctx = e->ctx;
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    PRISM_TRY(check_bound(e));
+    if (n_steps == 0) return PRISM_OK;
+    if (n_steps > e->out_cap) return fail(ctx, PRISM_E_ARG, "n_steps exceeds max_seq");
+    PRISM_TRY(capacity_ok(e, n_steps));
+    PRISM_TRY(set_scalars(e, (int32_t)e->pos, 0, 1));
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev0, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->tok, tokens_in, (size_t)e->batch * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev2, ctx->stream));
+    for (uint32_t i = 0; i < n_steps; i++) PRISM_TRY(run_step(e));
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev3, ctx->stream));
+    e->pos += n_steps;
+    PRISM_CUDA_TRY(ctx, cudaMemcpy2DAsync(out_tokens, (size_t)n_steps * 4, e->out_tokens, (size_t)e->out_cap * 4,
+                                          (size_t)n_steps * 4, e->batch, cudaMemcpyDeviceToHost, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev1, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e->ev0, e->ev1);
+    e->last_ms = ms;
+    cudaEventElapsedTime(&ms, e->ev2, e->ev3);
+    e->last_device_ms = ms;
+    return PRISM_OK;
+}
+
+int prism_cuda_engine_generate(prism_cuda_engine *e, const uint32_t *prompts, uint32_t batch, uint32_t n_prompt,
+                               uint32_t max_new, uint32_t *out_tokens, uint16_t *last_logits) {
+    if (!e || (!prompts && n_prompt) || (!out_tokens && max_new))
+        return fail(e ? e->ctx : nullptr, PRISM_E_NULL, "null argument");
+    prism_cuda_ctx *ctx = e->ctx;
+    PRISM_TRY(check_bound(e));
+    PRISM_TRY(prism_cuda_engine_reset(e, batch));
+    if (max_new > e->out_cap) return fail(ctx, PRISM_E_ARG, "max_new exceeds max_seq");
+    PRISM_TRY(capacity_ok(e, n_prompt + max_new));
+    // prompts -> device, position-major so a step's tokens are contiguous
+    const size_t need = (size_t)std::max<uint32_t>(n_prompt, 1) * batch;
+    if (need > e->prompts_cap) {
+        PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaFree(e->prompts);
+        e->prompts = nullptr;
+        e->prompts_cap = 0;
+        PRISM_CUDA_TRY(ctx, cudaMalloc((void **)&e->prompts, need * 4));
+        e->prompts_cap = need;
+    }
+    std::vector<uint32_t> tr(need, 0);
+    for (uint32_t b = 0; b < batch; b++)
+        for (uint32_t i = 0; i < n_prompt; i++) tr[(size_t)i * batch + b] = prompts[(size_t)b * n_prompt + i];
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->prompts, tr.data(), need * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev0, ctx->stream));
+    // prefill_cpu (engine_impl.rs:1046-1053): one step per prompt token
+    for (uint32_t i = 0; i < n_prompt; i++) {
+        PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->tok, e->prompts + (size_t)i * batch, (size_t)batch * 4,
+                                            cudaMemcpyDeviceToDevice, ctx->stream));
+        PRISM_TRY(run_step(e));
+    }
+    e->pos = n_prompt;
+    // decode: `nt = *prompt.last().unwrap_or(&0)` (engine_impl.rs:1015) is fed first
+    if (n_prompt == 0) PRISM_CUDA_TRY(ctx, cudaMemsetAsync(e->tok, 0, (size_t)batch * 4, ctx->stream));
+    {
+        int32_t one = 1;  // record = 1; pos and step are already right (step stayed 0 while not recording)
+        PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->scalars + 2, &one, 4, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    for (uint32_t i = 0; i < max_new; i++) PRISM_TRY(run_step(e));
+    e->pos += max_new;
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev1, ctx->stream));
+    if (max_new)
+        PRISM_CUDA_TRY(ctx, cudaMemcpy2DAsync(out_tokens, (size_t)max_new * 4, e->out_tokens, (size_t)e->out_cap * 4,
+                                              (size_t)max_new * 4, batch, cudaMemcpyDeviceToHost, ctx->stream));
+    if (last_logits) {
+        if (e->T > 1) return fail(ctx, PRISM_E_STATE, "logits are sharded under tensor parallelism");
+        const uint32_t ls = round_up_u32(e->V_l, 8);
+        PRISM_CUDA_TRY(ctx, cudaMemcpy2DAsync(last_logits, (size_t)e->V_l * 2, e->logits, (size_t)ls * 2,
+                                              (size_t)e->V_l * 2, batch, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e->ev0, e->ev1);
+    e->last_ms = ms;
+    return PRISM_OK;
+}
+
+uint64_t prism_cuda_engine_step_bytes(prism_cuda_engine *e) {
+    if (!e) return 0;
+    prism_cuda_ctx *ctx = e->ctx;
+    uint64_t bytes = 0;
+    auto add = [&](int32_t h) {
+        if (h >= 0 && ctx->tensors[h].live) bytes += ctx->tensors[h].algorithmic_bytes();
+    };
+    for (uint32_t l = 0; l < e->cfg.num_layers; l++) {
+        add(e->wq[l]); add(e->wk[l]); add(e->wv[l]); add(e->wo[l]); add(e->wg[l]); add(e->wu[l]);
+        if (!e->guard_skip) add(e->wd[l]);
+    }
+    add((e->cfg.tie_word_embeddings || e->lm_head < 0) ? e->embed : e->lm_head);
+    // KV read: K and V of every cached position, every layer
+    const uint64_t per_pos = e->cfg.kv_int8 ? 2ull * (e->kvd_l + 4) : 4ull * e->kvd_l;
+    bytes += per_pos * (uint64_t)(e->pos + 1) * e->cfg.num_layers;
+    return bytes;
+}
+
+double prism_cuda_engine_last_ms(prism_cuda_engine *e) { return e ? e->last_ms : 0.0; }
+double prism_cuda_engine_last_device_ms(prism_cuda_engine *e) { return e ? e->last_device_ms : 0.0; }
+uint32_t prism_cuda_engine_kernels_per_step(prism_cuda_engine *e) { return e ? e->kernels_per_step : 0; }
+
+// Times only the palettized GEMV launches of one decode step (every layer's q, k, v, o,
+// fused gate/up, down, and the head), back to back on the context stream between two
+// events, `reps` times.  The weights of a whole model exceed L2, so every launch streams
+// from HBM.  Outputs: elapsed ms, algorithmic bytes and launches over all reps.
+extern "C" int prism_cuda_engine_profile_gemv(prism_cuda_engine *e, uint32_t reps, double *ms_out, uint64_t *bytes_out,
+                                   uint32_t *launches_out) {
+    if (!e || !ms_out) return fail(e ? e->ctx : nullptr, PRISM_E_NULL, "null argument");
+    prism_cuda_ctx *ctx = e->ctx;
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    PRISM_TRY(check_bound(e));
+    const uint32_t B = e->batch ? e->batch : 1, H = e->H;
+    uint64_t bytes = 0;
+    uint32_t launches = 0;
+    auto one_pass = [&](bool count) -> int {
+        for (uint32_t l = 0; l < e->cfg.num_layers; l++) {
+            const LutTensor &tq = ctx->tensors[e->wq[l]], &tk = ctx->tensors[e->wk[l]], &tv = ctx->tensors[e->wv[l]],
+                            &to = ctx->tensors[e->wo[l]], &tg = ctx->tensors[e->wg[l]], &tu = ctx->tensors[e->wu[l]];
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tq, nullptr, e->xn, H, e->q, e->qd_l, nullptr, B));
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, e->kvd_l, nullptr, B));
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, e->kvd_l, nullptr, B));
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, to, nullptr, e->att, e->qd_l, e->xn, H, nullptr, B));
+            PRISM_TRY(launch_gemv(ctx, GEMV_SWIGLU, tg, &tu, e->xn, H, e->act, e->act_stride, nullptr, B));
+            if (count) {
+                bytes += tq.algorithmic_bytes() + tk.algorithmic_bytes() + tv.algorithmic_bytes() +
+                         to.algorithmic_bytes() + tg.algorithmic_bytes() + tu.algorithmic_bytes() - 2ull * tg.k;
+                launches += 5;
+            }
+            if (!e->guard_skip) {
+                const LutTensor &td = ctx->tensors[e->wd[l]];
+                PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, td, nullptr, e->act, e->act_stride, e->xn, H, nullptr, B));
+                if (count) { bytes += td.algorithmic_bytes(); launches += 1; }
+            }
+        }
+        const LutTensor &head = ctx->tensors[(e->cfg.tie_word_embeddings || e->lm_head < 0) ? e->embed : e->lm_head];
+        PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, head, nullptr, e->xn, H, e->logits, round_up_u32(e->V_l, 8), nullptr, B));
+        if (count) { bytes += head.algorithmic_bytes(); launches += 1; }
+        return PRISM_OK;
+    };
+    PRISM_TRY(one_pass(false));  // warm-up: sizes scratch, sets attributes
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev2, ctx->stream));
+    for (uint32_t r = 0; r < reps; r++) PRISM_TRY(one_pass(true));
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev3, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e->ev2, e->ev3);
+    *ms_out = ms;
+    if (bytes_out) *bytes_out = bytes;
+    if (launches_out) *launches_out = launches;
+    return PRISM_OK;
+}
+prism_cuda_ctx *prism_cuda_engine_ctx(prism_cuda_engine *e) { return e ? e->ctx : nullptr; }
+uint32_t prism_cuda_engine_position(prism_cuda_engine *e) { return e ? e->pos : 0; }
+
+}  // extern "C"

@@ -1,0 +1,412 @@
+// Palettized GEMV kernels for sm_100a.
+//
+//   y[r] = f16( sum_k f32(x[k]) * f32(palette[r][idx[r,k]]) )      (fp32 accumulate)
+//
+// the sum of lut_gemv_cpu (src/lut/cpu_fallback.rs:12-35).  Two kernels:
+//
+//  * lut_gemv_simple_kernel: one lane per output row, palette in shared
+//    memory, CUDA-core FMAs.  Handles 2- and 4-bit palettes and any K with
+//    K*bits % 32 == 0.  The plain, easy-to-audit path.
+//
+//  * lut_gemv_mma_kernel (4-bit): the bandwidth kernel.  A weight costs half a
+//    shared-memory lookup and half an integer instruction:
+//      - every index BYTE (two weights) is looked up in a 256-entry table of
+//        half2 {palette[lo nibble], palette[hi nibble]} built per row;
+//      - the table of the row a lane works on lives entirely in that lane's own
+//        shared-memory bank (entry stride 256 B), so the 32 lookups of a warp
+//        never conflict whatever the indices are;
+//      - the looked-up half2 is directly a register of the A fragment of
+//        mma.sync.m16n8k16: each lane feeds two rows x four k.  The B fragment
+//        holds x only on the four "diagonal" lanes (column n = lane%4), so
+//        column n of the accumulator collects exactly the products of the
+//        lanes with lane%4 == n.  The tensor pipe does the fp32 multiply-
+//        accumulate; no cvt/FMA instructions are spent per weight.
+//    Epilogues fuse the fp16 rounding points of the reference's step():
+//    residual add (engine_impl.rs:1158-1162,1196-1203) and gate/up SwiGLU
+//    (engine_impl.rs:1163-1195,1349-1367).
+#include "common.cuh"
+
+namespace prism {
+
+// ---------------------------------------------------------------------------
+// Simple kernel
+// ---------------------------------------------------------------------------
+constexpr int SIMPLE_WARPS = 4;
+
+template <int BITS>
+__global__ void __launch_bounds__(SIMPLE_WARPS * 32)
+lut_gemv_simple_kernel(const uint8_t *__restrict__ idx, const uint16_t *__restrict__ pal, uint32_t m,
+                       uint32_t k, uint32_t n_chunks, const uint16_t *__restrict__ x, uint32_t x_stride,
+                       uint16_t *__restrict__ y, uint32_t y_stride) {
+    constexpr uint32_t NE = 1u << BITS, PER_WORD = 32 / BITS, MASK = NE - 1;
+    __shared__ float pal_s[NE * 32];               // [entry][lane]: lane-private bank
+    __shared__ float red[SIMPLE_WARPS * 32];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t hb = blockIdx.x, b = blockIdx.y;
+    const uint32_t row = hb * 32 + lane;
+    if (warp == 0) {
+#pragma unroll
+        for (uint32_t e = 0; e < NE; e++)
+            pal_s[e * 32 + lane] = __half2float(__ushort_as_half(pal[(size_t)row * NE + e]));
+    }
+    __syncthreads();
+    const uint16_t *xb = x + (size_t)b * x_stride;
+    float acc = 0.0f;
+    for (uint32_t c = warp; c < n_chunks; c += SIMPLE_WARPS) {
+        uint4 v = *reinterpret_cast<const uint4 *>(idx + lut_idx_offset(n_chunks, hb, c, lane));
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t k0 = c * (128 / BITS);
+#pragma unroll
+        for (uint32_t wi = 0; wi < 4; wi++) {
+            uint32_t kw = k0 + wi * PER_WORD;
+            if (kw < k) {  // K*BITS % 32 == 0, so a word is entirely inside or outside
+#pragma unroll
+                for (uint32_t j = 0; j < PER_WORD; j++) {
+                    float xv = __half2float(__ushort_as_half(__ldg(xb + kw + j)));
+                    acc = fmaf(xv, pal_s[((w[wi] >> (j * BITS)) & MASK) * 32 + lane], acc);
+                }
+            }
+        }
+    }
+    red[warp * 32 + lane] = acc;
+    __syncthreads();
+    if (warp == 0 && row < m) {
+        float s = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < SIMPLE_WARPS; wv++) s += red[wv * 32 + lane];
+        y[(size_t)b * y_stride + row] = __half_as_ushort(__float2half_rn(s));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Pair-table tensor-core kernel
+// ---------------------------------------------------------------------------
+constexpr int MMA_WARPS = 8;
+constexpr int MMA_THREADS = MMA_WARPS * 32;
+constexpr int MMA_TBL_BYTES = 256 * 256;  // 256 entries x (2 rows x 32 lanes x 4 B)
+constexpr int MMA_MAX_KSLICE = 4096;      // halves of x staged per CTA
+constexpr int MMA_PF = 4;                 // index chunks in flight per warp
+
+struct MmaGemvArgs {
+    const uint8_t *idx1, *idx2;   // index arrays the two half-blocks of a CTA come from
+    const uint16_t *pal1, *pal2;
+    uint32_t n_chunks;            // chunks per row
+    uint32_t hb_mul, hb_add2;     // CTA b reads half-blocks hb_mul*b (rows "1") and hb_mul*b+hb_add2 ("2")
+    uint32_t m;                   // valid output rows (per tensor)
+    uint32_t chunks_per_split, ksplit;
+    const uint16_t *x; uint32_t x_stride;
+    uint16_t *y; uint32_t y_stride;
+    const uint16_t *resid;
+    float *partials;              // [batch][ksplit][n_blocks*64]
+    unsigned int *counters;       // [batch][n_blocks]
+};
+
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg128_stream(const uint8_t *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// One 32-weight chunk of two rows: 8 tensor-core steps of 4 k each.
+// tbl1/tbl2: shared addresses of this lane's table slots (row "1" / row "2").
+__device__ __forceinline__ void mma_chunk(float (&acc)[2][4], const uint4 &w1, const uint4 &w2,
+                                          uint32_t tbl1, uint32_t tbl2, uint32_t lane_off,
+                                          uint32_t x_addr) {
+    const uint32_t a1w[4] = {w1.x, w1.y, w1.z, w1.w};
+    const uint32_t a2w[4] = {w2.x, w2.y, w2.z, w2.w};
+#pragma unroll
+    for (int h = 0; h < 4; h++) {  // one 32-bit index word per row = 2 steps
+        const uint4 xb = lds128(x_addr + h * 16);  // x[k0+8h .. k0+8h+7] on diagonal lanes, 0 elsewhere
+        // byte j of the word -> (byte << 8) | lane*4 : offset of table entry `byte` in this lane's bank
+        const uint32_t o10 = __byte_perm(a1w[h], lane_off, 0x7704);
+        const uint32_t o11 = __byte_perm(a1w[h], lane_off, 0x7714);
+        const uint32_t o12 = __byte_perm(a1w[h], lane_off, 0x7724);
+        const uint32_t o13 = __byte_perm(a1w[h], lane_off, 0x7734);
+        const uint32_t o20 = __byte_perm(a2w[h], lane_off, 0x7704);
+        const uint32_t o21 = __byte_perm(a2w[h], lane_off, 0x7714);
+        const uint32_t o22 = __byte_perm(a2w[h], lane_off, 0x7724);
+        const uint32_t o23 = __byte_perm(a2w[h], lane_off, 0x7734);
+        // step 2h: bytes 0,1 (k0+8h .. +3); step 2h+1: bytes 2,3 (k0+8h+4 .. +7)
+        mma_m16n8k16(acc[0], lds32(tbl1 + o10), lds32(tbl2 + o20), lds32(tbl1 + o11), lds32(tbl2 + o21),
+                     xb.x, xb.y);
+        mma_m16n8k16(acc[1], lds32(tbl1 + o12), lds32(tbl2 + o22), lds32(tbl1 + o13), lds32(tbl2 + o23),
+                     xb.z, xb.w);
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaGemvArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint32_t *tbl = reinterpret_cast<uint32_t *>(smem);
+    uint16_t *xs = reinterpret_cast<uint16_t *>(smem + MMA_TBL_BYTES);
+    uint8_t *zero = smem + MMA_TBL_BYTES + MMA_MAX_KSLICE * 2;            // 64 B of zeros
+    float *red = reinterpret_cast<float *>(zero + 64);                    // [MMA_WARPS][64]
+    __shared__ unsigned int s_last;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t blk = blockIdx.x, ks = blockIdx.y, bat = blockIdx.z;
+    const uint32_t n_blocks = gridDim.x;
+    const uint32_t c_begin = ks * a.chunks_per_split;
+    const uint32_t c_end = min(a.n_chunks, c_begin + a.chunks_per_split);
+    const uint32_t hb1 = a.hb_mul * blk, hb2 = hb1 + a.hb_add2;
+
+    // ---- stage the x slice (fp16) and the zero block --------------------------------------
+    {
+        const uint32_t n16 = (c_end - c_begin) * 4;  // 16-byte units: 32 halves per chunk
+        const uint4 *xg = reinterpret_cast<const uint4 *>(a.x + (size_t)bat * a.x_stride + (size_t)c_begin * 32);
+        uint4 *xd = reinterpret_cast<uint4 *>(xs);
+        for (uint32_t i = tid; i < n16; i += MMA_THREADS) xd[i] = xg[i];
+        if (tid < 4) reinterpret_cast<uint4 *>(zero)[tid] = make_uint4(0, 0, 0, 0);
+    }
+    // ---- build the pair tables: entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]} -----------
+    // warp w writes the entries with hi in {2w, 2w+1}; lane L writes its own bank.
+#pragma unroll
+    for (int t = 0; t < 2; t++) {
+        const uint32_t row = (t == 0 ? hb1 : hb2) * 32 + lane;
+        const uint16_t *prow = (t == 0 ? a.pal1 : a.pal2) + (size_t)row * 16;
+        const uint4 p0 = *reinterpret_cast<const uint4 *>(prow);
+        const uint4 p1 = *reinterpret_cast<const uint4 *>(prow + 8);
+        const uint32_t cbp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        const uint32_t hi_pair = reinterpret_cast<const uint32_t *>(prow)[warp];  // {pal[2w], pal[2w+1]}
+#pragma unroll
+        for (int lo = 0; lo < 16; lo++) {
+#pragma unroll
+            for (int hs = 0; hs < 2; hs++) {
+                const uint32_t sel = ((hs ? 0x76u : 0x54u) << 8) | ((lo & 1) ? 0x32u : 0x10u);
+                const uint32_t v = __byte_perm(cbp[lo >> 1], hi_pair, sel);
+                const uint32_t e = (uint32_t)lo + 16u * (2u * warp + (uint32_t)hs);
+                tbl[e * 64 + t * 32 + lane] = v;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- stream the index chunks ------------------------------------------------------------
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+        const uint8_t *s1 = a.idx1 + (size_t)hb1 * a.n_chunks * 512 + lane * 16;
+        const uint8_t *s2 = a.idx2 + (size_t)hb2 * a.n_chunks * 512 + lane * 16;
+        const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+        const uint32_t lane_off = lane * 4;
+        const uint32_t tbl1 = smem_base, tbl2 = smem_base + 128;
+        const bool diag = (lane >> 2) == (lane & 3);
+        const uint32_t x_base = diag ? smem_base + MMA_TBL_BYTES : smem_base + MMA_TBL_BYTES + MMA_MAX_KSLICE * 2;
+        const uint32_t x_step = diag ? 64u : 0u;
+
+        uint4 q1[MMA_PF], q2[MMA_PF];
+        uint32_t c = c_begin + warp;
+#pragma unroll
+        for (int i = 0; i < MMA_PF; i++) {
+            const uint32_t cc = c + i * MMA_WARPS;
+            if (cc < c_end) {
+                q1[i] = ldg128_stream(s1 + (size_t)cc * 512);
+                q2[i] = ldg128_stream(s2 + (size_t)cc * 512);
+            }
+        }
+        for (; c < c_end; c += MMA_WARPS * MMA_PF) {
+#pragma unroll
+            for (int i = 0; i < MMA_PF; i++) {
+                const uint32_t cc = c + i * MMA_WARPS;
+                if (cc < c_end) {
+                    const uint4 w1 = q1[i], w2 = q2[i];
+                    const uint32_t nc = cc + MMA_WARPS * MMA_PF;
+                    if (nc < c_end) {
+                        q1[i] = ldg128_stream(s1 + (size_t)nc * 512);
+                        q2[i] = ldg128_stream(s2 + (size_t)nc * 512);
+                    }
+                    mma_chunk(acc, w1, w2, tbl1, tbl2, lane_off, x_base + (cc - c_begin) * x_step);
+                }
+            }
+        }
+    }
+
+    // ---- reduce across warps ---------------------------------------------------------------
+    // accumulator column n = 2j, 2j+1 (j = lane%4) of MMA row g = lane/4 (and g+8):
+    // column n is the dot product of the lane (g, n); only n < 4 is populated.
+    if ((lane & 3) < 2) {
+        const uint32_t r = (lane >> 2) * 4 + (lane & 3) * 2;  // lane index the column belongs to
+        float *rw = red + warp * 64;
+        rw[r] = acc[0][0] + acc[1][0];
+        rw[r + 1] = acc[0][1] + acc[1][1];
+        rw[32 + r] = acc[0][2] + acc[1][2];
+        rw[32 + r + 1] = acc[0][3] + acc[1][3];
+    }
+    __syncthreads();
+
+    float sum = 0.0f;  // thread tid < 64: row (tid>>5 ? "2" : "1"), lane tid&31
+    if (tid < 64) {
+#pragma unroll
+        for (int w = 0; w < MMA_WARPS; w++) sum += red[w * 64 + tid];
+    }
+    if (a.ksplit > 1) {
+        // deterministic split-K: every CTA stores its partial, the last one to arrive adds
+        // them in split order.
+        float *part = a.partials + ((size_t)bat * a.ksplit) * n_blocks * 64;
+        if (tid < 64) part[((size_t)ks * n_blocks + blk) * 64 + tid] = sum;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            unsigned int *ctr = a.counters + (size_t)bat * n_blocks + blk;
+            const unsigned int prev = atomicAdd(ctr, 1u);
+            s_last = (prev + 1 == a.ksplit) ? 1u : 0u;
+            if (s_last) *ctr = 0;  // ready for the next launch on this stream
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        if (tid < 64) {
+            sum = 0.0f;
+            for (uint32_t s = 0; s < a.ksplit; s++)
+                sum += __ldcg(part + ((size_t)s * n_blocks + blk) * 64 + tid);
+        }
+    }
+
+    // ---- epilogue ---------------------------------------------------------------------------
+    if (MODE == GEMV_SWIGLU) {
+        // rows "1" are gate rows, rows "2" the up rows of the same output index
+        __syncthreads();
+        if (tid < 64) red[tid] = sum;
+        __syncthreads();
+        if (tid < 32) {
+            const uint32_t row = blk * 32 + tid;
+            if (row < a.m) {
+                const float g = __half2float(__float2half_rn(red[tid]));
+                const float u = __half2float(__float2half_rn(red[32 + tid]));
+                const float s = __half2float(__float2half_rn(g / (1.0f + expf(-g))));
+                a.y[(size_t)bat * a.y_stride + row] = __half_as_ushort(__float2half_rn(s * u));
+            }
+        }
+    } else {
+        if (tid < 64) {
+            const uint32_t row = ((tid >> 5) ? hb2 : hb1) * 32 + (tid & 31);
+            if (MODE == GEMV_F32) {
+                if (row < a.m) reinterpret_cast<float *>(a.y)[(size_t)bat * a.y_stride + row] = sum;
+            } else if (row < a.m) {
+                __half hv = __float2half_rn(sum);
+                if (MODE == GEMV_RESID) {
+                    const float r = __half2float(__ushort_as_half(a.resid[(size_t)bat * a.y_stride + row]));
+                    hv = __float2half_rn(__half2float(hv) + r);
+                }
+                a.y[(size_t)bat * a.y_stride + row] = __half_as_ushort(hv);
+            }
+        }
+    }
+}
+
+constexpr size_t MMA_SMEM_BYTES = MMA_TBL_BYTES + MMA_MAX_KSLICE * 2 + 64 + MMA_WARPS * 64 * 4;
+
+template <int MODE>
+static int launch_mma(prism_cuda_ctx *ctx, const MmaGemvArgs &a, dim3 grid) {
+    static bool configured[8] = {false};
+    if (!configured[ctx->device & 7]) {
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_mma_kernel<MODE>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)MMA_SMEM_BYTES));
+        configured[ctx->device & 7] = true;
+    }
+    lut_gemv_mma_kernel<MODE><<<grid, MMA_THREADS, MMA_SMEM_BYTES, ctx->stream>>>(a);
+    return after_launch(ctx, "lut_gemv_mma_kernel");
+}
+
+static bool mma_eligible(const LutTensor &t) {
+    return t.bits == 4 && t.k % 32 == 0 && t.k >= 32;
+}
+
+int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2,
+                const uint16_t *x, uint32_t x_stride, uint16_t *y, uint32_t y_stride,
+                const uint16_t *resid, uint32_t batch) {
+    if (batch == 0) return PRISM_OK;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || ((size_t)x_stride * 2) % 16)
+        return fail(ctx, PRISM_E_ARG, "gemv: activation must be 16-byte aligned");
+    if (mode == GEMV_SWIGLU) {
+        if (!t2 || t2->m != t.m || t2->k != t.k || t2->bits != t.bits)
+            return fail(ctx, PRISM_E_ARG, "fused_gate_up: gate and up must have identical shape");
+    }
+    const bool use_mma = ctx->gemv_variant == 1 && mma_eligible(t);
+    if (!use_mma) {
+        // plain kernel + separate elementwise kernels keep the same rounding points
+        if (mode == GEMV_SWIGLU) {
+            const size_t st = t.m_pad;
+            PRISM_TRY(ensure_tmp(ctx, 2 * (size_t)batch * st));
+            uint16_t *g = ctx->tmp_scratch, *u = g + (size_t)batch * st;
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, t, nullptr, x, x_stride, g, (uint32_t)st, nullptr, batch));
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, *t2, nullptr, x, x_stride, u, (uint32_t)st, nullptr, batch));
+            for (uint32_t b = 0; b < batch; b++)
+                PRISM_TRY(launch_silu_mul(ctx, y + (size_t)b * y_stride, g + b * st, u + b * st, t.m));
+            return PRISM_OK;
+        }
+        if (mode == GEMV_F32) return fail(ctx, PRISM_E_ARG, "fp32 partial output needs the tensor-core GEMV (4-bit, K % 32 == 0)");
+        dim3 grid(t.n_hb, batch);
+        if (t.bits == 4)
+            lut_gemv_simple_kernel<4><<<grid, SIMPLE_WARPS * 32, 0, ctx->stream>>>(
+                t.idx, t.pal, t.m, t.k, t.n_chunks, x, x_stride, y, y_stride);
+        else
+            lut_gemv_simple_kernel<2><<<grid, SIMPLE_WARPS * 32, 0, ctx->stream>>>(
+                t.idx, t.pal, t.m, t.k, t.n_chunks, x, x_stride, y, y_stride);
+        PRISM_TRY(after_launch(ctx, "lut_gemv_simple_kernel"));
+        if (mode == GEMV_RESID) {
+            for (uint32_t b = 0; b < batch; b++)
+                PRISM_TRY(launch_vec_add(ctx, y + (size_t)b * y_stride, resid + (size_t)b * y_stride, t.m));
+        }
+        return PRISM_OK;
+    }
+
+    MmaGemvArgs a{};
+    a.n_chunks = t.n_chunks;
+    a.m = t.m;
+    a.x = x; a.x_stride = x_stride; a.y = y; a.y_stride = y_stride; a.resid = resid;
+    uint32_t n_blocks;
+    if (mode == GEMV_SWIGLU) {
+        a.idx1 = t.idx; a.pal1 = t.pal; a.idx2 = t2->idx; a.pal2 = t2->pal;
+        a.hb_mul = 1; a.hb_add2 = 0;
+        n_blocks = t.n_hb;
+    } else {
+        a.idx1 = a.idx2 = t.idx; a.pal1 = a.pal2 = t.pal;
+        a.hb_mul = 2; a.hb_add2 = 1;
+        n_blocks = t.n_hb / 2;
+    }
+    // split K so that (a) a slice of x fits the staging buffer, (b) the grid fills the GPU
+    const uint32_t max_chunks = MMA_MAX_KSLICE / 32;
+    uint32_t ksplit = (t.n_chunks + max_chunks - 1) / max_chunks;
+    const uint32_t target = (uint32_t)ctx->sm_count * 3;
+    while (n_blocks * batch * ksplit < target && t.n_chunks / (ksplit * 2) >= 8) ksplit *= 2;
+    uint32_t cps = (t.n_chunks + ksplit - 1) / ksplit;
+    ksplit = (t.n_chunks + cps - 1) / cps;
+    a.chunks_per_split = cps;
+    a.ksplit = ksplit;
+    if (ksplit > 1) {
+        PRISM_TRY(ensure_splitk(ctx, (size_t)batch * ksplit * n_blocks * 64, (size_t)batch * n_blocks));
+        a.partials = ctx->splitk_partials;
+        a.counters = ctx->splitk_counters;
+    }
+    dim3 grid(n_blocks, ksplit, batch);
+    switch (mode) {
+    case GEMV_PLAIN: return launch_mma<GEMV_PLAIN>(ctx, a, grid);
+    case GEMV_RESID: return launch_mma<GEMV_RESID>(ctx, a, grid);
+    case GEMV_F32: return launch_mma<GEMV_F32>(ctx, a, grid);
+    default: return launch_mma<GEMV_SWIGLU>(ctx, a, grid);
+    }
+}
+
+}  // namespace prism

@@ -1,0 +1,107 @@
+"""Palettized GEMV / fused SwiGLU / MLP / GEMM parity against the CPU oracle, through the C ABI.
+
+Tolerance: 1e-3 relative L2 on fp16 outputs of fp32-accumulated sums (the
+summation order differs from the oracle's strictly serial one); exact equality
+is required wherever the sum has a single non-zero term.
+"""
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+from prism_engine_b200 import synth
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+GEMV_SHAPES = [(64, 32), (33, 64), (100, 96), (4864, 896), (896, 4864), (128, 896), (896, 896), (1000, 8),
+               (72, 40), (8192, 1024), (2368, 8192), (3712, 256)]
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("m,k", GEMV_SHAPES)
+def test_gemv_matches_oracle(backend, oracle, variant, m, k):
+    backend.set_option("gemv_variant", variant)
+    pay = synth.make_payload(m, k, 4, seed=m * 7 + k)
+    x = synth.make_activation(k, seed=k)
+    h = backend.upload("g", pay, m, k)
+    y = backend.gemv(h, x)
+    want = oracle.lut_gemv(x, pay, m, k, threads=8)
+    assert rel_l2(y, want) <= TOL
+    # fp32 accumulation error is far below an fp16 ulp: almost every element is bit-identical
+    assert np.mean(y == want) > 0.9
+    big = (want & 0x7FFF) > 0x2800  # |y| > 2^-5: one fp16 ulp there dwarfs the fp32 summation error
+    if big.any():
+        assert np.max(np.abs(y.astype(np.int64) - want.astype(np.int64))[big]) <= 1
+    backend.free(h)
+    backend.set_option("gemv_variant", 1)
+
+
+@pytest.mark.parametrize("m,k", [(65, 64), (512, 3584), (96, 128)])
+def test_gemv_2bit(backend, oracle, m, k):
+    pay = synth.make_payload(m, k, 2, seed=m + k)
+    x = synth.make_activation(k, seed=3)
+    h = backend.upload("g2", pay, m, k, bits=2)
+    assert rel_l2(backend.gemv(h, x), oracle.lut_gemv(x, pay, m, k, bits=2)) <= TOL
+    backend.free(h)
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+def test_gemv_one_hot_is_exact(backend, oracle, variant):
+    """x = e_j picks column j of the dequantised matrix: a single-term sum, so bit-exact at full size."""
+    backend.set_option("gemv_variant", variant)
+    m, k = 4864, 896
+    pay = synth.make_payload(m, k, 4, seed=42)
+    W = oracle.dequant(pay, m, k)
+    h = backend.upload("oh", pay, m, k)
+    for j in (0, 1, 31, 32, 445, 895):
+        x = np.zeros(k, np.uint16)
+        x[j] = 0x3C00
+        y = backend.gemv(h, x)
+        # +0.0 sums: a column entry of -0.0 reads back as +0.0 after accumulation with zeros
+        want = W[:, j].copy()
+        want[want == 0x8000] = 0
+        assert np.array_equal(y, want), j
+    backend.free(h)
+    backend.set_option("gemv_variant", 1)
+
+
+def test_gemv_linearity_full_size(backend, oracle):
+    """GEMV(2x) == 2*GEMV(x) exactly (scaling by two is exact in fp16 and fp32)."""
+    m, k = 4864, 896
+    h = backend.synth("lin", m, k, seed=5)
+    x = synth.make_activation(k, seed=8, scale=0.25)
+    x2 = (x.view(np.float16) * np.float16(2)).view(np.uint16)
+    y, y2 = backend.gemv(h, x), backend.gemv(h, x2)
+    assert np.array_equal((y.view(np.float16) * np.float16(2)).view(np.uint16), y2)
+    backend.free(h)
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("hidden,inter", [(64, 96), (896, 4864), (256, 1000 // 8 * 8)])
+def test_fused_gate_up_and_mlp(backend, oracle, variant, hidden, inter):
+    backend.set_option("gemv_variant", variant)
+    wg, wu = synth.make_payload(inter, hidden, seed=1), synth.make_payload(inter, hidden, seed=2)
+    wd = synth.make_payload(hidden, inter, seed=3)
+    x = synth.make_activation(hidden, seed=4)
+    hg, hu, hd = backend.upload("gate", wg, inter, hidden), backend.upload("up", wu, inter, hidden), \
+        backend.upload("down", wd, hidden, inter)
+    want_out, want_act = oracle.mlp(wg, wu, wd, x, hidden, inter, threads=8)
+    act = backend.fused_gate_up("gate", "up", x)
+    assert rel_l2(act, want_act) <= TOL
+    assert np.mean(act == want_act) > 0.9
+    out = backend.mlp(hg, hu, hd, x)
+    assert rel_l2(out, want_out) <= TOL
+    for h in (hg, hu, hd):
+        backend.free(h)
+    backend.set_option("gemv_variant", 1)
+
+
+def test_gemm_rows_are_gemvs(backend, oracle):
+    m, k, m_tok = 192, 256, 37
+    pay = synth.make_payload(m, k, seed=6)
+    X = synth.make_activation((m_tok, k), seed=6)
+    h = backend.upload("gm", pay, m, k)
+    Y = backend.gemm(h, X)
+    want = oracle.lut_gemm(X, pay, m, k, threads=8)
+    assert Y.shape == (m_tok, m) and rel_l2(Y.reshape(-1), want.reshape(-1)) <= TOL
+    backend.free(h)
