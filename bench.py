@@ -213,7 +213,7 @@ def run_ours(args):
     arch = arch_dict(args.workload)
     if args.layers:
         arch["num_layers"] = args.layers
-    ctx_len = WORKLOADS[args.workload][1]
+    ctx_len = WORKLOADS[args.workload][1] if args.ctx < 0 else args.ctx
     B = args.batch
     total_steps = ctx_len + 2 * (args.warmup + args.steps) + 8
     mc = p.model_config(**arch, max_seq=total_steps, max_batch=B, profile="baseline")
@@ -352,7 +352,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qwen2.5-72b-decode", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only)")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling/debugging only)")
+    ap.add_argument("--ctx", type=int, default=-1, help="override the prompt context length (profiling/debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemv-shapes", action="store_true")
     args = ap.parse_args()

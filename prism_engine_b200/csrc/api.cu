@@ -81,8 +81,8 @@ LutTensor *get_tensor(prism_cuda_ctx *ctx, int32_t handle) {
     return &ctx->tensors[handle];
 }
 
-static int alloc_tensor(prism_cuda_ctx *ctx, const char *name, uint32_t m, uint32_t k, uint32_t bits,
-                        int32_t *handle) {
+int alloc_tensor(prism_cuda_ctx *ctx, const char *name, uint32_t m, uint32_t k, uint32_t bits,
+                 int32_t *handle) {
     if (bits != 2 && bits != 4) return fail(ctx, PRISM_E_ARG, "bits must be 2 or 4");
     if (m == 0 || k == 0) return fail(ctx, PRISM_E_ARG, "empty tensor");
     if (((uint64_t)k * bits) % 32 != 0)
@@ -511,7 +511,7 @@ int prism_cuda_rope(prism_cuda_ctx *ctx, uint16_t *x, uint32_t n, int64_t pos, u
     if (head_dim == 0 || (head_dim & 1)) return fail(ctx, PRISM_E_ARG, "rope: head_dim must be even");
     if (n == 0) return PRISM_OK;
     PRISM_TRY(host_call_begin(ctx, x, (size_t)n * 2, 0));
-    PRISM_TRY(launch_rope(ctx, (uint16_t *)ctx->stage_in, n, nullptr, pos, head_dim, base, 1));
+    PRISM_TRY(launch_rope(ctx, (uint16_t *)ctx->stage_in, n, nullptr, pos, head_dim, base, 1, n));
     PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(x, ctx->stage_in, (size_t)n * 2, cudaMemcpyDeviceToHost, ctx->stream));
     PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     return PRISM_OK;
@@ -566,7 +566,7 @@ int prism_cuda_attention(prism_cuda_ctx *ctx, const uint16_t *q, const uint16_t 
         PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(dv, v, kvb, cudaMemcpyHostToDevice, ctx->stream));
     }
     AttnArgs a{};
-    a.q = (const uint16_t *)dq; a.k = dk; a.v = dv; a.out = (uint16_t *)ctx->stage_out;
+    a.q = (const uint16_t *)dq; a.q_stride = num_heads * head_dim; a.k = dk; a.v = dv; a.out = (uint16_t *)ctx->stage_out;
     if (seq_len == 0) return fail(ctx, PRISM_E_ARG, "attention: seq_len must be > 0");
     a.pos_dev = nullptr; a.pos_host = (int32_t)seq_len - 1; a.slot_mul = 1; a.slot_add = 0;
     a.nh = num_heads; a.nkv = kv_heads; a.hd = head_dim; a.batch = 1;

@@ -138,7 +138,7 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
 int launch_rms_norm(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint32_t n, float eps,
                     uint32_t batch);
 int launch_rope(prism_cuda_ctx *ctx, uint16_t *x, uint32_t n, const int32_t *pos_dev, int64_t pos_host,
-                uint32_t head_dim, float base, uint32_t batch);
+                uint32_t head_dim, float base, uint32_t batch, uint32_t x_stride);
 int launch_vec_add(prism_cuda_ctx *ctx, uint16_t *a, const uint16_t *b, uint32_t n);
 int launch_silu(prism_cuda_ctx *ctx, uint16_t *x, uint32_t n);
 int launch_silu_mul(prism_cuda_ctx *ctx, uint16_t *out, const uint16_t *g, const uint16_t *u, uint32_t n);
@@ -146,7 +146,8 @@ int launch_softmax(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint3
 int launch_argmax(prism_cuda_ctx *ctx, const uint16_t *logits, uint32_t n, uint32_t stride, uint32_t batch,
                   uint32_t *out_dev);
 struct AttnArgs {
-    const uint16_t *q;      // [batch][nh*hd]
+    const uint16_t *q;      // [batch] rows of nh*hd, q_stride halfs apart
+    uint32_t q_stride;
     const void *k, *v;      // cache base of this layer slot
     uint16_t *out;          // [batch][nh*hd]
     // cached positions = pos*slot_mul + slot_add + 1, pos read from pos_dev (device scalar,
@@ -159,7 +160,8 @@ struct AttnArgs {
 };
 int launch_attention(prism_cuda_ctx *ctx, const AttnArgs &a);
 struct KvAppendArgs {
-    const uint16_t *k, *v;  // [batch][kvd]
+    const uint16_t *k, *v;  // [batch] rows of kvd, src_stride halfs apart
+    uint32_t src_stride;
     void *kc, *vc;
     const int32_t *pos_dev; int32_t pos_host; uint32_t slot_mul, slot_add;  // slot = pos*mul+add
     uint32_t kvd, batch; uint64_t seq_stride; uint32_t int8; uint32_t max_seq;
@@ -169,6 +171,8 @@ int launch_kv_append(prism_cuda_ctx *ctx, const KvAppendArgs &a);
 }  // namespace prism
 
 namespace prism {
+// Allocates an empty tensor of the device layout (indices and palettes uninitialised).
+int alloc_tensor(prism_cuda_ctx *ctx, const char *name, uint32_t m, uint32_t k, uint32_t bits, int32_t *handle);
 int synth_shard(prism_cuda_ctx *ctx, const char *name, uint32_t rows, uint32_t cols, uint32_t bits,
                 uint64_t seed, float sigma, uint32_t row0, uint32_t col0, int32_t *handle);
 // gemm.cu: Y[m_tok][m] = X[m_tok][k] * W^T (fp16 in/out, fp32 accumulate)

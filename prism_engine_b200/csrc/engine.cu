@@ -28,6 +28,10 @@ struct prism_cuda_engine {
     uint32_t H = 0, nh_l = 0, nkv_l = 0, hd = 0, qd_l = 0, kvd_l = 0, I_l = 0, V_l = 0;
     uint32_t head0 = 0, kvhead0 = 0, i0 = 0, v0 = 0;  // first local q head / kv head / inter row / vocab row
     std::vector<int32_t> wq, wk, wv, wo, wg, wu, wd;
+    std::vector<int32_t> wqkv;   // q, k, v rows stacked into one tensor (one launch instead of three)
+    bool fused_ready = false;
+    uint16_t *qkv = nullptr;     // [B][qkv_stride]: q | k | v of a sequence side by side
+    uint32_t qkv_stride = 0;
     int32_t embed = -1, lm_head = -1;
     // activations
     uint16_t *h = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr,
@@ -149,21 +153,26 @@ static int enqueue_step(prism_cuda_engine *e) {
         const LutTensor &tq = ctx->tensors[e->wq[l]], &tk = ctx->tensors[e->wk[l]], &tv = ctx->tensors[e->wv[l]],
                         &to = ctx->tensors[e->wo[l]], &tg = ctx->tensors[e->wg[l]], &tu = ctx->tensors[e->wu[l]];
         PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
-        PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tq, nullptr, e->xn, H, e->q, e->qd_l, nullptr, B));
-        PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, e->kvd_l, nullptr, B));
-        PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, e->kvd_l, nullptr, B));
-        if (c.rope_k) PRISM_TRY(launch_rope(ctx, e->k, e->kvd_l, pos_dev, 0, e->hd, base, B));
+        const uint32_t qs = e->qkv_stride;
+        if (e->wqkv[l] >= 0) {
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, ctx->tensors[e->wqkv[l]], nullptr, e->xn, H, e->qkv, qs, nullptr, B));
+        } else {
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tq, nullptr, e->xn, H, e->q, qs, nullptr, B));
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, qs, nullptr, B));
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, qs, nullptr, B));
+        }
+        if (c.rope_k) PRISM_TRY(launch_rope(ctx, e->k, e->kvd_l, pos_dev, 0, e->hd, base, B, qs));
         const uint32_t slot_mul = e->guard_skip ? c.num_layers : 1, slot_add = e->guard_skip ? l : 0;
         KvAppendArgs ka{};
-        ka.k = e->k; ka.v = e->v;
+        ka.k = e->k; ka.v = e->v; ka.src_stride = qs;
         ka.kc = (char *)e->kc + (size_t)li * e->kv_layer_bytes;
         ka.vc = (char *)e->vc + (size_t)li * e->kv_layer_bytes;
         ka.pos_dev = pos_dev; ka.slot_mul = slot_mul; ka.slot_add = slot_add;
         ka.kvd = e->kvd_l; ka.batch = B; ka.seq_stride = e->kv_seq_stride; ka.int8 = c.kv_int8; ka.max_seq = e->kv_slots;
         PRISM_TRY(launch_kv_append(ctx, ka));
-        PRISM_TRY(launch_rope(ctx, e->q, e->qd_l, pos_dev, 0, e->hd, base, B));
+        PRISM_TRY(launch_rope(ctx, e->q, e->qd_l, pos_dev, 0, e->hd, base, B, qs));
         AttnArgs aa{};
-        aa.q = e->q; aa.k = ka.kc; aa.v = ka.vc; aa.out = e->att;
+        aa.q = e->q; aa.q_stride = qs; aa.k = ka.kc; aa.v = ka.vc; aa.out = e->att;
         aa.pos_dev = pos_dev; aa.slot_mul = slot_mul; aa.slot_add = slot_add;
         aa.nh = e->nh_l; aa.nkv = e->nkv_l; aa.hd = e->hd; aa.batch = B;
         aa.seq_stride = e->kv_seq_stride; aa.int8 = c.kv_int8; aa.max_seq = e->kv_slots;
@@ -215,12 +224,44 @@ static int enqueue_step(prism_cuda_engine *e) {
     return after_launch(ctx, "advance_kernel");
 }
 
+// Stacks the rows of q, k and v of a layer into one tensor (device-to-device copies of
+// whole half-blocks), so the three projections of the same activation are one launch.
+static int build_fused_qkv(prism_cuda_engine *e) {
+    prism_cuda_ctx *ctx = e->ctx;
+    for (uint32_t l = 0; l < e->cfg.num_layers; l++) {
+        if (e->wqkv[l] >= 0) continue;
+        const LutTensor tq = ctx->tensors[e->wq[l]], tk = ctx->tensors[e->wk[l]], tv = ctx->tensors[e->wv[l]];
+        if (tq.m % 32 || tk.m % 32 || tv.m % 32) continue;  // rows must fill whole half-blocks
+        if (tk.k != tq.k || tv.k != tq.k || tk.bits != tq.bits || tv.bits != tq.bits) continue;
+        int32_t h;
+        PRISM_TRY(alloc_tensor(ctx, "", tq.m + tk.m + tv.m, tq.k, tq.bits, &h));
+        LutTensor &f = ctx->tensors[h];
+        uint8_t *di = f.idx;
+        uint16_t *dp = f.pal;
+        PRISM_CUDA_TRY(ctx, cudaMemsetAsync(f.idx, 0, f.idx_bytes, ctx->stream));
+        PRISM_CUDA_TRY(ctx, cudaMemsetAsync(f.pal, 0, f.pal_bytes, ctx->stream));
+        for (const LutTensor *t : {&tq, &tk, &tv}) {
+            const size_t ib = (size_t)(t->m / 32) * t->n_chunks * 512, pb = (size_t)t->m * t->n_ent() * 2;
+            PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(di, t->idx, ib, cudaMemcpyDeviceToDevice, ctx->stream));
+            PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(dp, t->pal, pb, cudaMemcpyDeviceToDevice, ctx->stream));
+            di += ib;
+            dp += (size_t)t->m * t->n_ent();
+        }
+        e->wqkv[l] = h;
+    }
+    return PRISM_OK;
+}
+
 static int check_bound(prism_cuda_engine *e) {
     if (e->embed < 0) return fail(e->ctx, PRISM_E_STATE, "emb miss: no embedding tensor bound");
     for (uint32_t l = 0; l < e->cfg.num_layers; l++) {
         if (e->wq[l] < 0 || e->wk[l] < 0 || e->wv[l] < 0 || e->wo[l] < 0 || e->wg[l] < 0 || e->wu[l] < 0 ||
             (!e->guard_skip && e->wd[l] < 0))
             return fail(e->ctx, PRISM_E_STATE, "layer " + std::to_string(l) + " has unbound tensors");
+    }
+    if (!e->fused_ready) {
+        PRISM_TRY(build_fused_qkv(e));
+        e->fused_ready = true;
     }
     return PRISM_OK;
 }
@@ -332,13 +373,14 @@ int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg,
     }
     e->guard_skip = c.down_guard && c.intermediate_size != c.hidden_size;
     e->kv_slots = e->guard_skip ? c.max_seq * c.num_layers : c.max_seq;
-    if ((size_t)e->kv_slots * 4 > 200 * 1024) {
+    if ((size_t)e->kv_slots * 4 > 160 * 1024) {
         delete e;
-        return fail(ctx, PRISM_E_ARG, "max_seq too large for the attention score buffer (<= 51200 cached positions per layer slot)");
+        return fail(ctx, PRISM_E_ARG, "max_seq too large for the attention score buffer (<= 40960 cached positions per layer slot)");
     }
     const uint32_t L = c.num_layers, B = c.max_batch;
     e->wq.assign(L, -1); e->wk.assign(L, -1); e->wv.assign(L, -1); e->wo.assign(L, -1);
-    e->wg.assign(L, -1); e->wu.assign(L, -1); e->wd.assign(L, -1);
+    e->wg.assign(L, -1); e->wu.assign(L, -1); e->wd.assign(L, -1); e->wqkv.assign(L, -1);
+    e->qkv_stride = round_up_u32(e->qd_l + 2 * e->kvd_l, 8);
     e->act_stride = round_up_u32(round_up_u32(e->I_l, 64), 8);
     e->out_cap = c.max_seq;
     const uint32_t kv_layers = e->guard_skip ? 1 : L;
@@ -354,9 +396,7 @@ int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg,
 #define ALLOC(ptr, bytes) if (ce == cudaSuccess) ce = A((void **)&(ptr), (bytes))
     ALLOC(e->h, (size_t)B * e->H * 2);
     ALLOC(e->xn, (size_t)B * e->H * 2);
-    ALLOC(e->q, (size_t)B * e->qd_l * 2);
-    ALLOC(e->k, (size_t)B * e->kvd_l * 2);
-    ALLOC(e->v, (size_t)B * e->kvd_l * 2);
+    ALLOC(e->qkv, (size_t)B * e->qkv_stride * 2);
     ALLOC(e->att, (size_t)B * e->qd_l * 2);
     ALLOC(e->act, (size_t)B * e->act_stride * 2);
     ALLOC(e->logits, (size_t)B * round_up_u32(e->V_l, 8) * 2);
@@ -370,6 +410,9 @@ int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg,
     ALLOC(e->kc, e->kv_layer_bytes * kv_layers);
     ALLOC(e->vc, e->kv_layer_bytes * kv_layers);
 #undef ALLOC
+    e->q = e->qkv;
+    e->k = e->qkv ? e->qkv + e->qd_l : nullptr;
+    e->v = e->qkv ? e->qkv + e->qd_l + e->kvd_l : nullptr;
     if (ce == cudaSuccess) ce = cudaEventCreate(&e->ev0);
     if (ce == cudaSuccess) ce = cudaEventCreate(&e->ev1);
     if (ce == cudaSuccess) ce = cudaEventCreate(&e->ev2);
@@ -390,7 +433,9 @@ void prism_cuda_engine_destroy(prism_cuda_engine *e) {
     cudaSetDevice(e->ctx->device);
     cudaStreamSynchronize(e->ctx->stream);
     if (e->graph) cudaGraphExecDestroy(e->graph);
-    void *ptrs[] = {e->h, e->xn, e->q, e->k, e->v, e->att, e->act, e->logits, e->part, e->tok, e->next,
+    for (int32_t h : e->wqkv)
+        if (h >= 0) prism_cuda_free_tensor(e->ctx, h);
+    void *ptrs[] = {e->h, e->xn, e->qkv, e->att, e->act, e->logits, e->part, e->tok, e->next,
                     e->out_tokens, e->prompts, e->pairs_send, e->pairs_recv, e->scalars, e->kc, e->vc};
     for (void *p : ptrs) cudaFree(p);
     if (e->ev0) cudaEventDestroy(e->ev0);
@@ -424,7 +469,14 @@ int prism_cuda_engine_bind(prism_cuda_engine *e, uint32_t role, uint32_t layer, 
     if (t->m != want_m || t->k != want_k || t->bits != c.bits)
         return fail(ctx, PRISM_E_ARG, "tensor " + t->name + " is " + std::to_string(t->m) + "x" + std::to_string(t->k) +
                                           ", role needs " + std::to_string(want_m) + "x" + std::to_string(want_k));
-    if (slot) (*slot)[layer] = handle;
+    if (slot) {
+        (*slot)[layer] = handle;
+        if (role <= PRISM_ROLE_V && e->wqkv[layer] >= 0) {  // rebinding q/k/v: the stacked copy is stale
+            prism_cuda_free_tensor(ctx, e->wqkv[layer]);
+            e->wqkv[layer] = -1;
+        }
+        if (role <= PRISM_ROLE_V) e->fused_ready = false;
+    }
     else if (role == PRISM_ROLE_EMBED) e->embed = handle;
     else e->lm_head = handle;
     if (e->graph) {  // pointers baked into the graph are stale
@@ -647,9 +699,14 @@ extern "C" int prism_cuda_engine_profile_gemv(prism_cuda_engine *e, uint32_t rep
         for (uint32_t l = 0; l < e->cfg.num_layers; l++) {
             const LutTensor &tq = ctx->tensors[e->wq[l]], &tk = ctx->tensors[e->wk[l]], &tv = ctx->tensors[e->wv[l]],
                             &to = ctx->tensors[e->wo[l]], &tg = ctx->tensors[e->wg[l]], &tu = ctx->tensors[e->wu[l]];
-            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tq, nullptr, e->xn, H, e->q, e->qd_l, nullptr, B));
-            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, e->kvd_l, nullptr, B));
-            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, e->kvd_l, nullptr, B));
+            if (e->wqkv[l] >= 0) {
+                PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, ctx->tensors[e->wqkv[l]], nullptr, e->xn, H, e->qkv, e->qkv_stride, nullptr, B));
+                if (count) launches -= 2;
+            } else {
+                PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tq, nullptr, e->xn, H, e->q, e->qkv_stride, nullptr, B));
+                PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, e->qkv_stride, nullptr, B));
+                PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, e->qkv_stride, nullptr, B));
+            }
             PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, to, nullptr, e->att, e->qd_l, e->xn, H, nullptr, B));
             PRISM_TRY(launch_gemv(ctx, GEMV_SWIGLU, tg, &tu, e->xn, H, e->act, e->act_stride, nullptr, B));
             if (count) {

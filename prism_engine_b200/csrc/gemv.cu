@@ -110,16 +110,6 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
 __device__ __forceinline__ uint4 ldg128_stream(const uint8_t *p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
@@ -129,15 +119,18 @@ __device__ __forceinline__ uint4 ldg128_stream(const uint8_t *p) {
 }
 
 // One 32-weight chunk of two rows: 8 tensor-core steps of 4 k each.
-// tbl1/tbl2: shared addresses of this lane's table slots (row "1" / row "2").
+// `tb` is the table (start of dynamic shared memory, so the compiler folds its address into the
+// immediate field of every lookup), `xk` the 64 bytes of x for this chunk.  Every lane reads
+// the same x words (one broadcast wavefront); `dmask` keeps them only on the diagonal lanes.
 __device__ __forceinline__ void mma_chunk(float (&acc)[2][4], const uint4 &w1, const uint4 &w2,
-                                          uint32_t tbl1, uint32_t tbl2, uint32_t lane_off,
-                                          uint32_t x_addr) {
+                                          const uint8_t *tb, uint32_t lane_off, const uint8_t *xk,
+                                          uint32_t dmask) {
     const uint32_t a1w[4] = {w1.x, w1.y, w1.z, w1.w};
     const uint32_t a2w[4] = {w2.x, w2.y, w2.z, w2.w};
 #pragma unroll
     for (int h = 0; h < 4; h++) {  // one 32-bit index word per row = 2 steps
-        const uint4 xb = lds128(x_addr + h * 16);  // x[k0+8h .. k0+8h+7] on diagonal lanes, 0 elsewhere
+        uint4 xb = *reinterpret_cast<const uint4 *>(xk + h * 16);  // x[k0+8h .. k0+8h+7]
+        xb.x &= dmask; xb.y &= dmask; xb.z &= dmask; xb.w &= dmask;
         // byte j of the word -> (byte << 8) | lane*4 : offset of table entry `byte` in this lane's bank
         const uint32_t o10 = __byte_perm(a1w[h], lane_off, 0x7704);
         const uint32_t o11 = __byte_perm(a1w[h], lane_off, 0x7714);
@@ -147,11 +140,13 @@ __device__ __forceinline__ void mma_chunk(float (&acc)[2][4], const uint4 &w1, c
         const uint32_t o21 = __byte_perm(a2w[h], lane_off, 0x7714);
         const uint32_t o22 = __byte_perm(a2w[h], lane_off, 0x7724);
         const uint32_t o23 = __byte_perm(a2w[h], lane_off, 0x7734);
+#define TBL1(o) (*reinterpret_cast<const uint32_t *>(tb + (o)))
+#define TBL2(o) (*reinterpret_cast<const uint32_t *>(tb + (o) + 128))
         // step 2h: bytes 0,1 (k0+8h .. +3); step 2h+1: bytes 2,3 (k0+8h+4 .. +7)
-        mma_m16n8k16(acc[0], lds32(tbl1 + o10), lds32(tbl2 + o20), lds32(tbl1 + o11), lds32(tbl2 + o21),
-                     xb.x, xb.y);
-        mma_m16n8k16(acc[1], lds32(tbl1 + o12), lds32(tbl2 + o22), lds32(tbl1 + o13), lds32(tbl2 + o23),
-                     xb.z, xb.w);
+        mma_m16n8k16(acc[0], TBL1(o10), TBL2(o20), TBL1(o11), TBL2(o21), xb.x, xb.y);
+        mma_m16n8k16(acc[1], TBL1(o12), TBL2(o22), TBL1(o13), TBL2(o23), xb.z, xb.w);
+#undef TBL1
+#undef TBL2
     }
 }
 
@@ -160,9 +155,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaG
     extern __shared__ __align__(16) uint8_t smem[];
     uint32_t *tbl = reinterpret_cast<uint32_t *>(smem);
     uint16_t *xs = reinterpret_cast<uint16_t *>(smem + MMA_TBL_BYTES);
-    uint8_t *zero = smem + MMA_TBL_BYTES + MMA_MAX_KSLICE * 2;            // 64 B of zeros
-    float *red = reinterpret_cast<float *>(zero + 64);                    // [MMA_WARPS][64]
-    __shared__ unsigned int s_last;
+    float *red = reinterpret_cast<float *>(smem + MMA_TBL_BYTES + MMA_MAX_KSLICE * 2);  // [MMA_WARPS][64]
+    unsigned int &s_last = *reinterpret_cast<unsigned int *>(red + MMA_WARPS * 64);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t blk = blockIdx.x, ks = blockIdx.y, bat = blockIdx.z;
@@ -171,13 +165,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaG
     const uint32_t c_end = min(a.n_chunks, c_begin + a.chunks_per_split);
     const uint32_t hb1 = a.hb_mul * blk, hb2 = hb1 + a.hb_add2;
 
-    // ---- stage the x slice (fp16) and the zero block --------------------------------------
+    // ---- stage the x slice (fp16) -----------------------------------------------------------
     {
         const uint32_t n16 = (c_end - c_begin) * 4;  // 16-byte units: 32 halves per chunk
         const uint4 *xg = reinterpret_cast<const uint4 *>(a.x + (size_t)bat * a.x_stride + (size_t)c_begin * 32);
         uint4 *xd = reinterpret_cast<uint4 *>(xs);
         for (uint32_t i = tid; i < n16; i += MMA_THREADS) xd[i] = xg[i];
-        if (tid < 4) reinterpret_cast<uint4 *>(zero)[tid] = make_uint4(0, 0, 0, 0);
     }
     // ---- build the pair tables: entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]} -----------
     // warp w writes the entries with hi in {2w, 2w+1}; lane L writes its own bank.
@@ -207,12 +200,9 @@ __global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaG
     {
         const uint8_t *s1 = a.idx1 + (size_t)hb1 * a.n_chunks * 512 + lane * 16;
         const uint8_t *s2 = a.idx2 + (size_t)hb2 * a.n_chunks * 512 + lane * 16;
-        const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
         const uint32_t lane_off = lane * 4;
-        const uint32_t tbl1 = smem_base, tbl2 = smem_base + 128;
-        const bool diag = (lane >> 2) == (lane & 3);
-        const uint32_t x_base = diag ? smem_base + MMA_TBL_BYTES : smem_base + MMA_TBL_BYTES + MMA_MAX_KSLICE * 2;
-        const uint32_t x_step = diag ? 64u : 0u;
+        const uint32_t dmask = ((lane >> 2) == (lane & 3)) ? 0xFFFFFFFFu : 0u;  // lanes 0, 5, 10, 15
+        const uint8_t *xbytes = smem + MMA_TBL_BYTES;
 
         uint4 q1[MMA_PF], q2[MMA_PF];
         uint32_t c = c_begin + warp;
@@ -235,7 +225,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaG
                         q1[i] = ldg128_stream(s1 + (size_t)nc * 512);
                         q2[i] = ldg128_stream(s2 + (size_t)nc * 512);
                     }
-                    mma_chunk(acc, w1, w2, tbl1, tbl2, lane_off, x_base + (cc - c_begin) * x_step);
+                    mma_chunk(acc, w1, w2, smem, lane_off, xbytes + (cc - c_begin) * 64, dmask);
                 }
             }
         }
@@ -314,7 +304,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaG
     }
 }
 
-constexpr size_t MMA_SMEM_BYTES = MMA_TBL_BYTES + MMA_MAX_KSLICE * 2 + 64 + MMA_WARPS * 64 * 4;
+constexpr size_t MMA_SMEM_BYTES = MMA_TBL_BYTES + MMA_MAX_KSLICE * 2 + MMA_WARPS * 64 * 4 + 16;
 
 template <int MODE>
 static int launch_mma(prism_cuda_ctx *ctx, const MmaGemvArgs &a, dim3 grid) {

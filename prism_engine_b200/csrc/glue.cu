@@ -67,10 +67,10 @@ int launch_rms_norm(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint
 // rope_inplace (cpu_fallback.rs:131-143): pairs (j, j+hd/2) of every head chunk.
 // The position comes from device memory when pos_dev is set (graph replay).
 __global__ void rope_kernel(uint16_t *__restrict__ x, uint32_t n, const int32_t *__restrict__ pos_dev,
-                            int64_t pos_host, uint32_t hd, float base) {
+                            int64_t pos_host, uint32_t hd, float base, uint32_t x_stride) {
     const uint32_t half = hd / 2;
     const uint32_t pairs = (n / hd) * half;
-    uint16_t *xb = x + (size_t)blockIdx.y * n;
+    uint16_t *xb = x + (size_t)blockIdx.y * x_stride;
     const float pos = pos_dev ? (float)(*pos_dev) : (float)pos_host;
     for (uint32_t p = blockIdx.x * blockDim.x + threadIdx.x; p < pairs; p += gridDim.x * blockDim.x) {
         const uint32_t head = p / half, j = p % half;
@@ -85,10 +85,10 @@ __global__ void rope_kernel(uint16_t *__restrict__ x, uint32_t n, const int32_t 
 }
 
 int launch_rope(prism_cuda_ctx *ctx, uint16_t *x, uint32_t n, const int32_t *pos_dev, int64_t pos_host,
-                uint32_t head_dim, float base, uint32_t batch) {
+                uint32_t head_dim, float base, uint32_t batch, uint32_t x_stride) {
     const uint32_t pairs = (n / head_dim) * (head_dim / 2);
     dim3 grid((pairs + 127) / 128, batch);
-    rope_kernel<<<grid, 128, 0, ctx->stream>>>(x, n, pos_dev, pos_host, head_dim, base);
+    rope_kernel<<<grid, 128, 0, ctx->stream>>>(x, n, pos_dev, pos_host, head_dim, base, x_stride);
     return after_launch(ctx, "rope_kernel");
 }
 
@@ -203,7 +203,7 @@ int launch_argmax(prism_cuda_ctx *ctx, const uint16_t *logits, uint32_t n, uint3
 __global__ void kv_append_kernel(KvAppendArgs a) {
     __shared__ float sh[32];
     const uint32_t b = blockIdx.x, which = blockIdx.y;
-    const uint16_t *src = (which ? a.v : a.k) + (size_t)b * a.kvd;
+    const uint16_t *src = (which ? a.v : a.k) + (size_t)b * a.src_stride;
     const int64_t slot = (int64_t)(a.pos_dev ? *a.pos_dev : a.pos_host) * a.slot_mul + a.slot_add;
     if (slot < 0 || slot >= (int64_t)a.max_seq) return;  // full cache: host checks before launch
     if (!a.int8) {
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(AttnArgs a) {
     uint32_t sl = (uint32_t)((a.pos_dev ? *a.pos_dev : a.pos_host) * (int32_t)a.slot_mul + (int32_t)a.slot_add + 1);
     if (sl > a.max_seq) sl = a.max_seq;  // never index past the score buffer / cache
     const uint32_t g = a.nh / (a.nkv ? a.nkv : 1), kh = h / g, kvd = a.nkv * a.hd, hd = a.hd;
-    const uint16_t *q = a.q + (size_t)b * a.nh * hd + (size_t)h * hd;
+    const uint16_t *q = a.q + (size_t)b * a.q_stride + (size_t)h * hd;
     const char *kb = reinterpret_cast<const char *>(a.k) + (size_t)b * a.seq_stride * (a.int8 ? 1 : 2);
     const char *vb = reinterpret_cast<const char *>(a.v) + (size_t)b * a.seq_stride * (a.int8 ? 1 : 2);
     for (uint32_t d = threadIdx.x; d < hd; d += blockDim.x) qs[d] = h2f(q[d]);
@@ -304,18 +304,122 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(AttnArgs a) {
     }
 }
 
+// Same computation for fp16 caches with head_dim = 32*VEC: each lane owns VEC consecutive
+// elements of the head, one warp works on one cached position at a time (four in flight), so K
+// and V rows are read with coalesced vector loads and the loop over positions is spread over
+// all warps of the block.  Partial outputs of the warps are combined in warp order.
+template <int VEC>
+__global__ void __launch_bounds__(ATTN_THREADS) attention_f16_kernel(AttnArgs a) {
+    extern __shared__ float sc[];  // [sl] scores, then exp
+    __shared__ float sh[32];
+    __shared__ float part[(ATTN_THREADS / 32) * 32 * VEC];
+    constexpr uint32_t hd = 32 * VEC;
+    const uint32_t h = blockIdx.x, b = blockIdx.y;
+    uint32_t sl = (uint32_t)((a.pos_dev ? *a.pos_dev : a.pos_host) * (int32_t)a.slot_mul + (int32_t)a.slot_add + 1);
+    if (sl > a.max_seq) sl = a.max_seq;
+    const uint32_t g = a.nh / (a.nkv ? a.nkv : 1), kh = h / g, kvd = a.nkv * hd;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr uint32_t nw = ATTN_THREADS / 32;
+    const uint16_t *q = a.q + (size_t)b * a.q_stride + (size_t)h * hd + lane * VEC;
+    const uint16_t *kb = reinterpret_cast<const uint16_t *>(a.k) + (size_t)b * a.seq_stride + (size_t)kh * hd + lane * VEC;
+    const uint16_t *vb = reinterpret_cast<const uint16_t *>(a.v) + (size_t)b * a.seq_stride + (size_t)kh * hd + lane * VEC;
+    float qf[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; i++) qf[i] = h2f(q[i]);
+    const float div = sqrtf((float)hd);
+    struct alignas(2 * VEC) Row { uint16_t e[VEC]; };
+    for (uint32_t p0 = warp; p0 < sl; p0 += 4 * nw) {
+        Row r[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const uint32_t p = p0 + u * nw;
+            if (p < sl) r[u] = *reinterpret_cast<const Row *>(kb + (size_t)p * kvd);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const uint32_t p = p0 + u * nw;
+            if (p < sl) {  // warp-uniform
+                float s = 0.0f;
+#pragma unroll
+                for (int i = 0; i < VEC; i++) s += qf[i] * h2f(r[u].e[i]);
+                s = warp_sum(s);
+                if (lane == 0) sc[p] = s / div;
+            }
+        }
+    }
+    __syncthreads();
+    float mx = -INFINITY;
+    for (uint32_t p = threadIdx.x; p < sl; p += blockDim.x) mx = fmaxf(mx, sc[p]);
+    mx = block_max(mx, sh);
+    float es = 0.0f;
+    for (uint32_t p = threadIdx.x; p < sl; p += blockDim.x) {
+        float e = expf(sc[p] - mx);
+        sc[p] = e;
+        es += e;
+    }
+    es = block_sum(es, sh);
+    const float inv = 1.0f / (es + 1e-10f);
+    float ac[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; i++) ac[i] = 0.0f;
+    for (uint32_t p0 = warp; p0 < sl; p0 += 4 * nw) {
+        Row r[4];
+        float e[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const uint32_t p = p0 + u * nw;
+            e[u] = 0.0f;
+            if (p < sl) {
+                r[u] = *reinterpret_cast<const Row *>(vb + (size_t)p * kvd);
+                e[u] = sc[p];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (p0 + u * nw < sl) {
+#pragma unroll
+                for (int i = 0; i < VEC; i++) ac[i] += __fmul_rn(__fmul_rn(e[u], h2f(r[u].e[i])), inv);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; i++) part[warp * hd + lane * VEC + i] = ac[i];
+    __syncthreads();
+    if (threadIdx.x < hd) {
+        float t = 0.0f;
+#pragma unroll
+        for (uint32_t w = 0; w < nw; w++) t += part[w * hd + threadIdx.x];
+        a.out[(size_t)b * a.nh * hd + (size_t)h * hd + threadIdx.x] = f2h(t);
+    }
+}
+
 int launch_attention(prism_cuda_ctx *ctx, const AttnArgs &a) {
     if (a.hd > 256 || a.hd == 0 || ATTN_THREADS % a.hd != 0)
         return fail(ctx, PRISM_E_ARG, "attention: head_dim must divide 256");
     static bool configured[8] = {false};
     const size_t smem = (size_t)a.max_seq * sizeof(float);
-    if (smem > 200 * 1024) return fail(ctx, PRISM_E_ARG, "attention: max_seq too large for the score buffer");
-    if (smem > 48 * 1024 && !configured[ctx->device & 7]) {
-        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 200 * 1024));
+    if (smem > 160 * 1024) return fail(ctx, PRISM_E_ARG, "attention: max_seq too large for the score buffer");
+    if (smem > 32 * 1024 && !configured[ctx->device & 7]) {
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_f16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_f16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_f16_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_f16_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         configured[ctx->device & 7] = true;
     }
     dim3 grid(a.nh, a.batch);
+    const bool vec_ok = !a.int8 && (a.hd == 32 || a.hd == 64 || a.hd == 128 || a.hd == 256) &&
+                        (reinterpret_cast<uintptr_t>(a.k) % 16 == 0) && (reinterpret_cast<uintptr_t>(a.v) % 16 == 0) &&
+                        (a.seq_stride * 2) % 16 == 0;
+    if (vec_ok) {
+        switch (a.hd) {
+        case 32: attention_f16_kernel<1><<<grid, ATTN_THREADS, smem, ctx->stream>>>(a); break;
+        case 64: attention_f16_kernel<2><<<grid, ATTN_THREADS, smem, ctx->stream>>>(a); break;
+        case 128: attention_f16_kernel<4><<<grid, ATTN_THREADS, smem, ctx->stream>>>(a); break;
+        default: attention_f16_kernel<8><<<grid, ATTN_THREADS, smem, ctx->stream>>>(a); break;
+        }
+        return after_launch(ctx, "attention_f16_kernel");
+    }
     attention_kernel<<<grid, ATTN_THREADS, smem, ctx->stream>>>(a);
     return after_launch(ctx, "attention_kernel");
 }

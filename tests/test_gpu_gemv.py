@@ -66,13 +66,16 @@ def test_gemv_one_hot_is_exact(backend, oracle, variant):
 
 
 def test_gemv_linearity_full_size(backend, oracle):
-    """GEMV(2x) == 2*GEMV(x) exactly (scaling by two is exact in fp16 and fp32)."""
+    """GEMV(2x) == 2*GEMV(x) exactly: scaling by two is exact in fp16 and fp32 as long as the fp16
+    result is a normal number (a subnormal result has already lost bits the doubled sum keeps)."""
     m, k = 4864, 896
     h = backend.synth("lin", m, k, seed=5)
     x = synth.make_activation(k, seed=8, scale=0.25)
     x2 = (x.view(np.float16) * np.float16(2)).view(np.uint16)
     y, y2 = backend.gemv(h, x), backend.gemv(h, x2)
-    assert np.array_equal((y.view(np.float16) * np.float16(2)).view(np.uint16), y2)
+    normal = (y & 0x7C00) != 0
+    assert normal.mean() > 0.99
+    assert np.array_equal((y.view(np.float16) * np.float16(2)).view(np.uint16)[normal], y2[normal])
     backend.free(h)
 
 
