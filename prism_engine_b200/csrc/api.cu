@@ -73,6 +73,18 @@ int ensure_tmp(prism_cuda_ctx *ctx, size_t halfs) {
     return PRISM_OK;
 }
 
+int check_device_error(prism_cuda_ctx *ctx) {
+    unsigned int v = 0;
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(&v, ctx->dev_err, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (v != 0) {
+        cudaMemsetAsync(ctx->dev_err, 0, 4, ctx->stream);
+        return fail(ctx, PRISM_E_STATE, "a kernel refused to run: shared-memory layout assumption does not hold (code " +
+                                            std::to_string(v) + ")");
+    }
+    return PRISM_OK;
+}
+
 LutTensor *get_tensor(prism_cuda_ctx *ctx, int32_t handle) {
     if (!ctx || handle < 0 || (size_t)handle >= ctx->tensors.size() || !ctx->tensors[handle].live) {
         if (ctx) ctx->err = "miss handle " + std::to_string(handle);
@@ -152,6 +164,17 @@ int prism_cuda_create(int device, prism_cuda_ctx **out) {
         delete ctx;
         return cuda_fail(nullptr, e, "cudaStreamCreate");
     }
+    if ((e = cudaMalloc((void **)&ctx->dev_err, 64)) != cudaSuccess) {
+        cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return cuda_fail(nullptr, e, "cudaMalloc");
+    }
+    int rc = probe_smem_base(ctx);
+    if (rc != PRISM_OK) {
+        g_create_err = ctx->err;
+        prism_cuda_destroy(ctx);
+        return rc;
+    }
     *out = ctx;
     return PRISM_OK;
 }
@@ -172,6 +195,7 @@ void prism_cuda_destroy(prism_cuda_ctx *ctx) {
     cudaFree(ctx->splitk_counters);
     cudaFree(ctx->act_scratch);
     cudaFree(ctx->tmp_scratch);
+    cudaFree(ctx->dev_err);
     extern void prism_tp_shutdown(prism_cuda_ctx *);
     prism_tp_shutdown(ctx);
     cudaStreamDestroy(ctx->stream);
@@ -184,8 +208,7 @@ void *prism_cuda_stream(prism_cuda_ctx *ctx) { return ctx ? (void *)ctx->stream 
 
 int prism_cuda_synchronize(prism_cuda_ctx *ctx) {
     if (!ctx) return PRISM_E_NULL;
-    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    return PRISM_OK;
+    return check_device_error(ctx);
 }
 
 int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
@@ -338,8 +361,7 @@ static int host_call_begin(prism_cuda_ctx *ctx, const void *in, size_t in_bytes,
 static int host_call_end(prism_cuda_ctx *ctx, void *out, size_t out_bytes) {
     if (out_bytes)
         PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(out, ctx->stage_out, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
-    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    return PRISM_OK;
+    return check_device_error(ctx);
 }
 
 int prism_cuda_gemv(prism_cuda_ctx *ctx, int32_t handle, const uint16_t *x, uint16_t *y) {

@@ -80,6 +80,9 @@ struct prism_cuda_ctx {
     size_t act_halfs = 0;
     uint16_t *tmp_scratch = nullptr;  // gate/up outputs of the unfused SwiGLU path
     size_t tmp_halfs = 0;
+    // device error word [0] (kernels set it instead of trapping) and probe result [1]
+    unsigned int *dev_err = nullptr;
+    int smem_base = -1;  // offset of dynamic shared memory in the shared window, probed at create
     // tensor parallel
     int tp_world = 1, tp_rank = 0;
     void *nccl_comm = nullptr;
@@ -111,6 +114,9 @@ int ensure_splitk(prism_cuda_ctx *ctx, size_t floats, size_t counters);
 int ensure_act(prism_cuda_ctx *ctx, size_t halfs);
 int ensure_tmp(prism_cuda_ctx *ctx, size_t halfs);
 LutTensor *get_tensor(prism_cuda_ctx *ctx, int32_t handle);
+int probe_smem_base(prism_cuda_ctx *ctx);
+// Reads the device error word; a non-zero value becomes PRISM_E_STATE.
+int check_device_error(prism_cuda_ctx *ctx);
 
 // ---- kernels' host-side launchers (device pointers, context stream) -------
 

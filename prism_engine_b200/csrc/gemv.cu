@@ -99,6 +99,7 @@ struct MmaGemvArgs {
     const uint16_t *resid;
     float *partials;              // [batch][ksplit][n_blocks*64]
     unsigned int *counters;       // [batch][n_blocks]
+    unsigned int *err;            // device error word (set when a layout assumption does not hold)
 };
 
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -118,41 +119,79 @@ __device__ __forceinline__ uint4 ldg128_stream(const uint8_t *p) {
     return v;
 }
 
-// One 32-weight chunk of two rows: 8 tensor-core steps of 4 k each.
-// `tb` is the table (start of dynamic shared memory, so the compiler folds its address into the
-// immediate field of every lookup), `xk` the 64 bytes of x for this chunk.  Every lane reads
-// the same x words (one broadcast wavefront); `dmask` keeps them only on the diagonal lanes.
+// Shared-memory loads whose address is `register + immediate`.  SBASE is the offset of the
+// kernel's dynamic shared memory inside the shared window when it is known at compile time
+// (probed once per context): the table base then rides in the instruction's immediate field and a
+// lookup needs no address arithmetic beyond the byte-permute that forms the offset.  SBASE < 0
+// is the portable variant (base added at run time).
+template <int SBASE, int IMM>
+__device__ __forceinline__ uint32_t lds_u32(uint32_t off, uint32_t base) {
+    uint32_t v;
+    if (SBASE >= 0) asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(off), "n"(SBASE >= 0 ? SBASE + IMM : 0));
+    else asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(off + base), "n"(IMM));
+    return v;
+}
+template <int SBASE, int IMM>
+__device__ __forceinline__ uint4 lds_u128(uint32_t off, uint32_t base) {
+    uint4 v;
+    if (SBASE >= 0)
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                     : "r"(off), "n"(SBASE >= 0 ? SBASE + IMM : 0));
+    else
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                     : "r"(off + base), "n"(IMM));
+    return v;
+}
+
+// The eight table lookups of one 32-bit index word per row (= two tensor-core steps).
+// byte j of the word -> (byte << 8) | lane*4: offset of table entry `byte` in this lane's bank.
+template <int SBASE>
+__device__ __forceinline__ void lookup_word(uint32_t (&A)[8], uint32_t w1, uint32_t w2, uint32_t lane_off,
+                                            uint32_t base) {
+    const uint32_t o10 = __byte_perm(w1, lane_off, 0x7704), o11 = __byte_perm(w1, lane_off, 0x7714);
+    const uint32_t o12 = __byte_perm(w1, lane_off, 0x7724), o13 = __byte_perm(w1, lane_off, 0x7734);
+    const uint32_t o20 = __byte_perm(w2, lane_off, 0x7704), o21 = __byte_perm(w2, lane_off, 0x7714);
+    const uint32_t o22 = __byte_perm(w2, lane_off, 0x7724), o23 = __byte_perm(w2, lane_off, 0x7734);
+    A[0] = lds_u32<SBASE, 0>(o10, base);   A[1] = lds_u32<SBASE, 128>(o20, base);
+    A[2] = lds_u32<SBASE, 0>(o11, base);   A[3] = lds_u32<SBASE, 128>(o21, base);
+    A[4] = lds_u32<SBASE, 0>(o12, base);   A[5] = lds_u32<SBASE, 128>(o22, base);
+    A[6] = lds_u32<SBASE, 0>(o13, base);   A[7] = lds_u32<SBASE, 128>(o23, base);
+}
+
+// One 32-weight chunk of two rows: 8 tensor-core steps of 4 k each.  x_off is the byte offset of
+// the chunk's 64 bytes of x inside the staged slice.  Every lane reads the same x words (a
+// broadcast); `dmask` keeps them only on the diagonal lanes.  Lookups of word h+1 are issued
+// before the tensor-core steps of word h.
+template <int SBASE>
 __device__ __forceinline__ void mma_chunk(float (&acc)[2][4], const uint4 &w1, const uint4 &w2,
-                                          const uint8_t *tb, uint32_t lane_off, const uint8_t *xk,
-                                          uint32_t dmask) {
+                                          uint32_t lane_off, uint32_t x_off, uint32_t dmask, uint32_t base) {
     const uint32_t a1w[4] = {w1.x, w1.y, w1.z, w1.w};
     const uint32_t a2w[4] = {w2.x, w2.y, w2.z, w2.w};
+    uint4 xb[4];
+    xb[0] = lds_u128<SBASE, MMA_TBL_BYTES + 0>(x_off, base);
+    xb[1] = lds_u128<SBASE, MMA_TBL_BYTES + 16>(x_off, base);
+    xb[2] = lds_u128<SBASE, MMA_TBL_BYTES + 32>(x_off, base);
+    xb[3] = lds_u128<SBASE, MMA_TBL_BYTES + 48>(x_off, base);
+    uint32_t A[2][8];
+    lookup_word<SBASE>(A[0], a1w[0], a2w[0], lane_off, base);
 #pragma unroll
-    for (int h = 0; h < 4; h++) {  // one 32-bit index word per row = 2 steps
-        uint4 xb = *reinterpret_cast<const uint4 *>(xk + h * 16);  // x[k0+8h .. k0+8h+7]
-        xb.x &= dmask; xb.y &= dmask; xb.z &= dmask; xb.w &= dmask;
-        // byte j of the word -> (byte << 8) | lane*4 : offset of table entry `byte` in this lane's bank
-        const uint32_t o10 = __byte_perm(a1w[h], lane_off, 0x7704);
-        const uint32_t o11 = __byte_perm(a1w[h], lane_off, 0x7714);
-        const uint32_t o12 = __byte_perm(a1w[h], lane_off, 0x7724);
-        const uint32_t o13 = __byte_perm(a1w[h], lane_off, 0x7734);
-        const uint32_t o20 = __byte_perm(a2w[h], lane_off, 0x7704);
-        const uint32_t o21 = __byte_perm(a2w[h], lane_off, 0x7714);
-        const uint32_t o22 = __byte_perm(a2w[h], lane_off, 0x7724);
-        const uint32_t o23 = __byte_perm(a2w[h], lane_off, 0x7734);
-#define TBL1(o) (*reinterpret_cast<const uint32_t *>(tb + (o)))
-#define TBL2(o) (*reinterpret_cast<const uint32_t *>(tb + (o) + 128))
+    for (int h = 0; h < 4; h++) {
+        if (h < 3) lookup_word<SBASE>(A[(h + 1) & 1], a1w[h + 1], a2w[h + 1], lane_off, base);
+        const uint32_t(&a)[8] = A[h & 1];
         // step 2h: bytes 0,1 (k0+8h .. +3); step 2h+1: bytes 2,3 (k0+8h+4 .. +7)
-        mma_m16n8k16(acc[0], TBL1(o10), TBL2(o20), TBL1(o11), TBL2(o21), xb.x, xb.y);
-        mma_m16n8k16(acc[1], TBL1(o12), TBL2(o22), TBL1(o13), TBL2(o23), xb.z, xb.w);
-#undef TBL1
-#undef TBL2
+        mma_m16n8k16(acc[0], a[0], a[1], a[2], a[3], xb[h].x & dmask, xb[h].y & dmask);
+        mma_m16n8k16(acc[1], a[4], a[5], a[6], a[7], xb[h].z & dmask, xb[h].w & dmask);
     }
 }
 
-template <int MODE>
+template <int MODE, int SBASE>
 __global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaGemvArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    if (SBASE >= 0 && smem_base != (uint32_t)SBASE) {  // layout assumption broken: refuse to compute
+        if (threadIdx.x == 0) atomicExch(a.err, 1u);
+        return;
+    }
     uint32_t *tbl = reinterpret_cast<uint32_t *>(smem);
     uint16_t *xs = reinterpret_cast<uint16_t *>(smem + MMA_TBL_BYTES);
     float *red = reinterpret_cast<float *>(smem + MMA_TBL_BYTES + MMA_MAX_KSLICE * 2);  // [MMA_WARPS][64]
@@ -202,7 +241,6 @@ __global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaG
         const uint8_t *s2 = a.idx2 + (size_t)hb2 * a.n_chunks * 512 + lane * 16;
         const uint32_t lane_off = lane * 4;
         const uint32_t dmask = ((lane >> 2) == (lane & 3)) ? 0xFFFFFFFFu : 0u;  // lanes 0, 5, 10, 15
-        const uint8_t *xbytes = smem + MMA_TBL_BYTES;
 
         uint4 q1[MMA_PF], q2[MMA_PF];
         uint32_t c = c_begin + warp;
@@ -225,7 +263,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaG
                         q1[i] = ldg128_stream(s1 + (size_t)nc * 512);
                         q2[i] = ldg128_stream(s2 + (size_t)nc * 512);
                     }
-                    mma_chunk(acc, w1, w2, smem, lane_off, xbytes + (cc - c_begin) * 64, dmask);
+                    mma_chunk<SBASE>(acc, w1, w2, lane_off, (cc - c_begin) * 64, dmask, smem_base);
                 }
             }
         }
@@ -306,17 +344,43 @@ __global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaG
 
 constexpr size_t MMA_SMEM_BYTES = MMA_TBL_BYTES + MMA_MAX_KSLICE * 2 + MMA_WARPS * 64 * 4 + 16;
 
-template <int MODE>
-static int launch_mma(prism_cuda_ctx *ctx, const MmaGemvArgs &a, dim3 grid) {
+constexpr int MMA_KNOWN_SBASE = 1024;  // dynamic shared memory starts after the 1 KB the driver reserves
+
+template <int MODE, int SBASE>
+static int launch_mma_v(prism_cuda_ctx *ctx, const MmaGemvArgs &a, dim3 grid) {
     static bool configured[8] = {false};
     if (!configured[ctx->device & 7]) {
-        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_mma_kernel<MODE>,
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_mma_kernel<MODE, SBASE>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)MMA_SMEM_BYTES));
         configured[ctx->device & 7] = true;
     }
-    lut_gemv_mma_kernel<MODE><<<grid, MMA_THREADS, MMA_SMEM_BYTES, ctx->stream>>>(a);
+    lut_gemv_mma_kernel<MODE, SBASE><<<grid, MMA_THREADS, MMA_SMEM_BYTES, ctx->stream>>>(a);
     return after_launch(ctx, "lut_gemv_mma_kernel");
+}
+
+template <int MODE>
+static int launch_mma(prism_cuda_ctx *ctx, const MmaGemvArgs &a, dim3 grid) {
+    if (ctx->smem_base == MMA_KNOWN_SBASE) return launch_mma_v<MODE, MMA_KNOWN_SBASE>(ctx, a, grid);
+    return launch_mma_v<MODE, -1>(ctx, a, grid);
+}
+
+// Reports where dynamic shared memory starts inside the shared window for a kernel without
+// static shared memory (run once per context).
+__global__ void probe_smem_base_kernel(unsigned int *out) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    if (threadIdx.x == 0) *out = (unsigned int)__cvta_generic_to_shared(smem);
+}
+
+int probe_smem_base(prism_cuda_ctx *ctx) {
+    PRISM_CUDA_TRY(ctx, cudaMemsetAsync(ctx->dev_err, 0, 8, ctx->stream));
+    probe_smem_base_kernel<<<1, 32, 4096, ctx->stream>>>(ctx->dev_err + 1);
+    PRISM_TRY(after_launch(ctx, "probe_smem_base_kernel"));
+    unsigned int v = 0;
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(&v, ctx->dev_err + 1, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->smem_base = (int)v;
+    return PRISM_OK;
 }
 
 static bool mma_eligible(const LutTensor &t) {
@@ -366,6 +430,7 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
     a.n_chunks = t.n_chunks;
     a.m = t.m;
     a.x = x; a.x_stride = x_stride; a.y = y; a.y_stride = y_stride; a.resid = resid;
+    a.err = ctx->dev_err;
     uint32_t n_blocks;
     if (mode == GEMV_SWIGLU) {
         a.idx1 = t.idx; a.pal1 = t.pal; a.idx2 = t2->idx; a.pal2 = t2->pal;
