@@ -115,6 +115,16 @@ int prism_cuda_gemv(prism_cuda_ctx *ctx, int32_t handle, const uint16_t *x, uint
 int prism_cuda_gemv_key(prism_cuda_ctx *ctx, const char *key, const uint16_t *x, size_t x_len,
                         uint16_t *y, size_t y_len);
 int prism_cuda_gemv_dev(prism_cuda_ctx *ctx, int32_t handle, const void *x_dev, void *y_dev);
+/* (No counterpart in the reference.)  The same GEMV for hosts that cannot allocate on this
+ * path -- a server whose own pools already hold all of HBM, or a decode loop with a fixed
+ * memory budget: split-K scratch comes from a fixed 2 MiB + 16 KiB array inside the
+ * library instead of cudaMalloc, and nothing is allocated or freed.  4-bit tensors with
+ * dim_n % 32 == 0 only; a shape whose split-K scratch exceeds the array (more than 524 288
+ * partial sums or 4096 row blocks) returns PRISM_E_ARG.  All calls on a device share the array:
+ * calls on one context are stream-ordered and safe, kernels overlapping from different
+ * streams/contexts of one device race.  The first call on a device looks up the array's
+ * address; make that call before any stream capture. */
+int prism_cuda_gemv_static_dev(prism_cuda_ctx *ctx, int32_t handle, const void *x_dev, void *y_dev);
 /* y = f16( f32(f16(W x)) + f32(resid) ): GEMV followed by vec_add_inplace, the
  * OProj / DownProj arms of step() (engine_impl.rs:1158-1162, 1196-1203). */
 int prism_cuda_gemv_residual_dev(prism_cuda_ctx *ctx, int32_t handle, const void *x_dev,

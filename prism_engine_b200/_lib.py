@@ -60,6 +60,7 @@ SIGNATURES = {
     "prism_cuda_gemv": (C.c_int, [_vp, _i32, _vp, _vp]),
     "prism_cuda_gemv_key": (C.c_int, [_vp, _cp, _vp, _sz, _vp, _sz]),
     "prism_cuda_gemv_dev": (C.c_int, [_vp, _i32, _vp, _vp]),
+    "prism_cuda_gemv_static_dev": (C.c_int, [_vp, _i32, _vp, _vp]),
     "prism_cuda_gemv_residual_dev": (C.c_int, [_vp, _i32, _vp, _vp, _vp]),
     "prism_cuda_fused_gate_up": (C.c_int, [_vp, _i32, _i32, _vp, _vp]),
     "prism_cuda_fused_gate_up_key": (C.c_int, [_vp, _cp, _cp, _vp, _sz, _vp, _sz]),

@@ -184,6 +184,11 @@ class CudaBackend:
     def gemv_dev(self, handle: int, x_dev: int, y_dev: int) -> None:
         self._ck(self.L.prism_cuda_gemv_dev(self.ctx, handle, x_dev, y_dev))
 
+    def gemv_static_dev(self, handle: int, x_dev: int, y_dev: int) -> None:
+        """GEMV that never allocates: split-K scratch comes from a fixed array inside the library
+        (for hosts whose own pools already own all of HBM).  Rejects shapes beyond that array."""
+        self._ck(self.L.prism_cuda_gemv_static_dev(self.ctx, handle, x_dev, y_dev))
+
     def fused_gate_up_dev(self, gate: int, up: int, x_dev: int, out_dev: int) -> None:
         self._ck(self.L.prism_cuda_fused_gate_up_dev(self.ctx, gate, up, x_dev, out_dev))
 

@@ -464,4 +464,88 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
     }
 }
 
+// ---------------------------------------------------------------------------
+// GEMV for callers that must not allocate
+// ---------------------------------------------------------------------------
+// Some hosts of this library cannot tolerate a device allocation on the GEMV path: an
+// inference server that has already handed every free byte of HBM to its own weight and
+// KV-cache pools (so a later cudaMalloc can fail, or stall the whole device while it
+// runs), or a real-time decode loop with a fixed memory budget.  prism_cuda_gemv_dev may
+// grow the context's split-K scratch with cudaMalloc the first time a shape needs it;
+// prism_cuda_gemv_static_dev below never does.  Its split-K partial sums and arrival
+// counters live in the fixed array that follows, which every GPU that loads this library
+// holds (2 MiB + 16 KiB) until the process exits.
+//
+//  * All calls on a device share the array; it keeps whatever the previous call left.
+//    The arrival counters are cleared on the stream before every launch; partial sums are
+//    always fully written before they are read, so they need no clearing.
+//  * Two calls whose kernels overlap on the GPU (different streams / contexts of the same
+//    device) race on the array.  Calls on one context are stream-ordered and safe.
+//  * The first call on a device resolves the array's device address (cudaGetSymbolAddress);
+//    make that first call outside any stream capture.
+//  * Shapes whose split-K scratch would exceed the array are rejected with PRISM_E_ARG.
+constexpr size_t STATIC_PARTIAL_FLOATS = 512 * 1024;  // 2 MiB of fp32 partial sums
+constexpr size_t STATIC_COUNTERS = 4096;              // one arrival counter per 64-row block
+static __device__ __align__(256) float g_static_splitk[STATIC_PARTIAL_FLOATS + STATIC_COUNTERS];
+
+// In host code `g_static_splitk` is only a stand-in for the symbol; the device address has to be
+// asked for, once per device, with that device current.
+static float *g_static_splitk_dev[64] = {nullptr};
+
+static int static_scratch_ptr(prism_cuda_ctx *ctx, float **out) {
+    if (ctx->device < 0 || ctx->device >= 64) return fail(ctx, PRISM_E_ARG, "device index above 63");
+    if (!g_static_splitk_dev[ctx->device]) {
+        void *p = nullptr;
+        PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        PRISM_CUDA_TRY(ctx, cudaGetSymbolAddress(&p, g_static_splitk));
+        g_static_splitk_dev[ctx->device] = static_cast<float *>(p);
+    }
+    *out = g_static_splitk_dev[ctx->device];
+    return PRISM_OK;
+}
+
 }  // namespace prism
+
+using namespace prism;
+
+extern "C" int prism_cuda_gemv_static_dev(prism_cuda_ctx *ctx, int32_t handle, const void *x_dev, void *y_dev) {
+    LutTensor *tp = get_tensor(ctx, handle);
+    if (!tp) return ctx ? PRISM_E_NOTFOUND : PRISM_E_NULL;
+    if (!x_dev || !y_dev) return fail(ctx, PRISM_E_NULL, "null vector");
+    const LutTensor &t = *tp;
+    if (!mma_eligible(t))
+        return fail(ctx, PRISM_E_ARG, "gemv_static: needs a 4-bit tensor with dim_n a multiple of 32");
+    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(ctx, PRISM_E_ARG, "gemv_static: x must be 16-byte aligned");
+    float *scratch = nullptr;
+    PRISM_TRY(static_scratch_ptr(ctx, &scratch));
+    MmaGemvArgs a{};
+    a.n_chunks = t.n_chunks;
+    a.m = t.m;
+    a.x = static_cast<const uint16_t *>(x_dev); a.x_stride = round_up_u32(t.k, 8);
+    a.y = static_cast<uint16_t *>(y_dev); a.y_stride = t.m;
+    a.err = ctx->dev_err;
+    a.idx1 = a.idx2 = t.idx; a.pal1 = a.pal2 = t.pal;
+    a.hb_mul = 2; a.hb_add2 = 1;
+    const uint32_t n_blocks = t.n_hb / 2;
+    // same split rule as the allocating path: x slice fits its staging buffer, grid fills the GPU
+    const uint32_t max_chunks = MMA_MAX_KSLICE / 32;
+    uint32_t ksplit = (t.n_chunks + max_chunks - 1) / max_chunks;
+    const uint32_t target = (uint32_t)ctx->sm_count * 3;
+    while (n_blocks * ksplit < target && t.n_chunks / (ksplit * 2) >= 8) ksplit *= 2;
+    const uint32_t cps = (t.n_chunks + ksplit - 1) / ksplit;
+    ksplit = (t.n_chunks + cps - 1) / cps;
+    a.chunks_per_split = cps;
+    a.ksplit = ksplit;
+    if (ksplit > 1) {
+        const size_t need = (size_t)ksplit * n_blocks * 64;
+        if (need > STATIC_PARTIAL_FLOATS || n_blocks > STATIC_COUNTERS)
+            return fail(ctx, PRISM_E_ARG,
+                        "gemv_static: this shape needs " + std::to_string(need) + " partial sums and " +
+                            std::to_string(n_blocks) + " counters; the fixed scratch holds " +
+                            std::to_string(STATIC_PARTIAL_FLOATS) + " and " + std::to_string(STATIC_COUNTERS));
+        a.partials = scratch;
+        a.counters = reinterpret_cast<unsigned int *>(scratch + STATIC_PARTIAL_FLOATS);
+        PRISM_CUDA_TRY(ctx, cudaMemsetAsync(a.counters, 0, (size_t)n_blocks * sizeof(unsigned int), ctx->stream));
+    }
+    return launch_mma<GEMV_PLAIN>(ctx, a, dim3(n_blocks, ksplit, 1));
+}
