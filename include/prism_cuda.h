@@ -57,8 +57,9 @@ const char *prism_cuda_last_error(prism_cuda_ctx *ctx);
 /* The CUDA stream (cudaStream_t) the context launches on. */
 void *prism_cuda_stream(prism_cuda_ctx *ctx);
 int prism_cuda_synchronize(prism_cuda_ctx *ctx);
-/* Tunables: "gemv_variant" (0 = plain CUDA-core kernel, 1 = pair-table
- * tensor-core kernel, default), "fuse" (0/1, default 1: fused epilogues). */
+/* Tunables: "gemv_variant" (0 = plain CUDA-core kernel, 1 = pair-table mma.sync
+ * kernel, default, 2 = pair-table tcgen05/TMEM kernel), "fuse" (0/1, default 1:
+ * fused epilogues). */
 int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value);
 /* Number of kernels this library has launched on the context so far. */
 uint64_t prism_cuda_launch_count(prism_cuda_ctx *ctx);

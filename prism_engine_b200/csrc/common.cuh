@@ -140,6 +140,11 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
                 const uint16_t *x, uint32_t x_stride, uint16_t *y, uint32_t y_stride,
                 const uint16_t *resid, uint32_t batch);
 
+// gemv_tc5.cu: tcgen05/TMEM GEMV (4-bit, K % 32 == 0, one activation vector)
+bool tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t batch);
+int launch_gemv_tc5(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
+                    void *y, const uint16_t *resid);
+
 // glue.cu
 int launch_rms_norm(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint32_t n, float eps,
                     uint32_t batch);

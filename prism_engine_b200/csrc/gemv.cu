@@ -397,7 +397,8 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
         if (!t2 || t2->m != t.m || t2->k != t.k || t2->bits != t.bits)
             return fail(ctx, PRISM_E_ARG, "fused_gate_up: gate and up must have identical shape");
     }
-    const bool use_mma = ctx->gemv_variant == 1 && mma_eligible(t);
+    if (ctx->gemv_variant == 2 && tc5_eligible(ctx, t, batch)) return launch_gemv_tc5(ctx, mode, t, t2, x, y, resid);
+    const bool use_mma = ctx->gemv_variant >= 1 && mma_eligible(t);
     if (!use_mma) {
         // plain kernel + separate elementwise kernels keep the same rounding points
         if (mode == GEMV_SWIGLU) {

@@ -27,7 +27,7 @@ def test_reference_kat_payload(backend):
     h = backend.upload("kat", p, 2, 8)
     y = backend.gemv(h, np.full(8, 0x3C00, np.uint16))
     assert y.tolist() == [0x4800, 0x4C00]
-    for variant in (0, 1):
+    for variant in (0, 1, 2):
         backend.set_option("gemv_variant", variant)
         assert backend.gemv("kat", np.full(8, 0x3C00, np.uint16)).tolist() == [0x4800, 0x4C00]
     backend.free(h)
