@@ -35,6 +35,8 @@ WORKLOADS = {
     # name: (architecture dict key, prompt context, description)
     "qwen2.5-72b-decode": ("QWEN25_72B", 512),
     "qwen2.5-0.5b-decode": ("QWEN25_0P5B", 128),
+    # prefill: the palettized linears of one Qwen2.5-7B layer on M = 2048 tokens (tensor-core GEMM)
+    "qwen2.5-7b-prefill-gemm": ("QWEN25_7B", 2048),
 }
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
@@ -344,6 +346,77 @@ def small_shape_bandwidth(be, peak):
     return out
 
 
+def measured_tensor_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops_sustained"]), float(d["bf16_tflops"]), "measured"
+    except Exception:
+        return 1400.0, 1590.0, "fallback"
+
+
+def run_gemm(args):
+    """Prefill GEMM workload: q, k, v, gate, up, down of one Qwen2.5-7B layer, 4-bit palettized, on
+    M = 2048 tokens of fp16 activations.  A step is the six GEMMs once; the metric is TFLOP/s."""
+    import torch
+
+    import prism_engine_b200 as p
+
+    torch.cuda.set_device(0)
+    be = p.CudaBackend(device=0)
+    arch = arch_dict(args.workload)
+    H, I = arch["hidden_size"], arch["intermediate_size"]
+    kvd = arch["num_kv_heads"] * arch["head_dim"]
+    m_tok = WORKLOADS[args.workload][1]
+    shapes = [("q", H, H), ("k", kvd, H), ("v", kvd, H), ("gate", I, H), ("up", I, H), ("down", H, I)]
+    sampler = ClockSampler(0)
+    per = {}
+    total_ms, total_flop = 0.0, 0.0
+    hs = {n: be.synth(f"gemm.{n}", m, k, seed=i) for i, (n, m, k) in enumerate(shapes)}
+    for n, m, k in shapes:
+        be.bench_gemm(hs[n], m_tok, max(args.warmup, 3))
+    sampler.start()
+    l0 = be.launch_count()
+    for n, m, k in shapes:
+        ms = be.bench_gemm(hs[n], m_tok, args.steps) / args.steps
+        flop = 2.0 * m_tok * m * k
+        per[n] = {"shape": f"{m}x{k}", "ms": ms, "tflops": flop / ms / 1e9}
+        total_ms += ms
+        total_flop += flop
+    launches = be.launch_count() - l0
+    clocks = sampler.stop()
+    sustained, burst, kind = measured_tensor_peak()
+    value = total_flop / total_ms / 1e9
+    big = per["gate"]["tflops"]
+    # end to end: host activations in, host result out, through the public GEMM call
+    from prism_engine_b200 import synth
+
+    X = synth.make_activation((m_tok, H), seed=1)
+    be.gemm(hs["gate"], X)
+    t0 = time.perf_counter()
+    reps = 3
+    for _ in range(reps):
+        be.gemm(hs["gate"], X)
+    e2e_s = (time.perf_counter() - t0) / reps
+    line = {
+        "metric": "prefill_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": total_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 operands / f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: q/k/v/gate/up/down of one layer, M = {m_tok} tokens, 4-bit indices + "
+                               "16-entry fp16 palette per row", "l2_policy": "operands of consecutive GEMMs exceed L2"},
+        "roofline": {"bound": "tensor", "achieved": big, "peak": sustained, "unit": "TFLOP/s", "frac": big / sustained,
+                     "peak_kind": f"of {kind} (sustained bf16 cuBLAS; burst {burst})", "kernel": "lut_gemm_tc5_kernel",
+                     "launch": "gate 18944x3584, M=2048", "traffic": None},
+        "per_gemm": per,
+        "e2e": {"value": 2.0 * m_tok * I * H / e2e_s / 1e12, "unit": "TFLOP/s (gate GEMM through prism_cuda_gemm, host buffers)",
+                "h2d_bytes_per_step": int(X.nbytes), "d2h_bytes_per_step": m_tok * I * 2},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    print(json.dumps(line))
+    be.close()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -359,6 +432,11 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
+    if args.workload.endswith("prefill-gemm"):
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm times decode; run the decode workloads"}))
+            return 0
+        return run_gemm(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

@@ -58,8 +58,9 @@ const char *prism_cuda_last_error(prism_cuda_ctx *ctx);
 void *prism_cuda_stream(prism_cuda_ctx *ctx);
 int prism_cuda_synchronize(prism_cuda_ctx *ctx);
 /* Tunables: "gemv_variant" (0 = plain CUDA-core kernel, 1 = pair-table mma.sync
- * kernel, default, 2 = pair-table tcgen05/TMEM kernel), "fuse" (0/1, default 1:
- * fused epilogues). */
+ * kernel, default, 2 = pair-table tcgen05/TMEM kernel), "gemm_variant" (1 = tcgen05/TMEM
+ * prefill GEMM, default; 0 = activation rows through the GEMV kernel), "fuse" (0/1,
+ * default 1: fused epilogues). */
 int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value);
 /* Number of kernels this library has launched on the context so far. */
 uint64_t prism_cuda_launch_count(prism_cuda_ctx *ctx);
@@ -258,6 +259,10 @@ int prism_cuda_engine_profile_gemv(prism_cuda_engine *eng, uint32_t reps, double
  * gate/up (gate, up), 2 = MLP (gate, up, down). */
 int prism_cuda_bench_cycle(prism_cuda_ctx *ctx, int kind, const int32_t *handles, uint32_t n_sets,
                            uint32_t reps, double *ms_out);
+/* Measurement: `reps` prefill GEMMs of m_tok activation rows against one tensor between two
+ * events on the context stream (activations are pattern data made on the device). */
+int prism_cuda_bench_gemm(prism_cuda_ctx *ctx, int32_t handle, uint32_t m_tok, uint32_t reps,
+                          double *ms_out);
 
 /* ---- tensor parallelism (not in the reference; column/row-sharded linears
  *      with an all-reduce after each row-parallel matmul) ------------------- */

@@ -94,6 +94,7 @@ SIGNATURES = {
     "prism_cuda_engine_profile_gemv": (C.c_int, [_vp, _u32, C.POINTER(C.c_double), C.POINTER(_u64), _pu32]),
     "prism_cuda_bench_cycle": (C.c_int, [_vp, C.c_int, _pi32, _u32, _u32, C.POINTER(C.c_double)]),
     "prism_cuda_load_cimage": (C.c_int, [_vp, _cp, _pu32]),
+    "prism_cuda_bench_gemm": (C.c_int, [_vp, _i32, _u32, _u32, C.POINTER(C.c_double)]),
     "prism_cuda_tp_unique_id": (C.c_int, [_vp]),
     "prism_cuda_tp_init": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
     "prism_cuda_tp_world": (C.c_int, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),

@@ -252,6 +252,12 @@ class CudaBackend:
                                                hs.size // per, reps, C.byref(ms)))
         return ms.value
 
+    def bench_gemm(self, handle: int, m_tok: int, reps: int) -> float:
+        """ms for `reps` prefill GEMMs of m_tok rows against one tensor (see prism_cuda_bench_gemm)."""
+        ms = C.c_double()
+        self._ck(self.L.prism_cuda_bench_gemm(self.ctx, handle, m_tok, reps, C.byref(ms)))
+        return ms.value
+
     def load_cimage(self, path: str) -> int:
         n = C.c_uint32()
         self._ck(self.L.prism_cuda_load_cimage(self.ctx, path.encode(), C.byref(n)))

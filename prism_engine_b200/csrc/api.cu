@@ -216,6 +216,9 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
     if (!strcmp(key, "gemv_variant")) {
         if (value < 0 || value > 2) return fail(ctx, PRISM_E_ARG, "gemv_variant must be 0, 1 or 2");
         ctx->gemv_variant = (int)value;
+    } else if (!strcmp(key, "gemm_variant")) {
+        if (value != 0 && value != 1) return fail(ctx, PRISM_E_ARG, "gemm_variant must be 0 or 1");
+        ctx->gemm_variant = (int)value;
     } else if (!strcmp(key, "fuse")) {
         ctx->fuse = value ? 1 : 0;
     } else {
@@ -516,6 +519,36 @@ int prism_cuda_bench_cycle(prism_cuda_ctx *ctx, int kind, const int32_t *handles
     if (ce != cudaSuccess) return cuda_fail(ctx, ce, "bench cycle");
     *ms_out = ms;
     return PRISM_OK;
+}
+
+// Measurement: `reps` prefill GEMMs of m_tok activation rows (fp16 pattern data generated on the
+// device) against one tensor, between two events on the context stream.
+int prism_cuda_bench_gemm(prism_cuda_ctx *ctx, int32_t handle, uint32_t m_tok, uint32_t reps, double *ms_out) {
+    LutTensor *t = get_tensor(ctx, handle);
+    if (!t) return ctx ? PRISM_E_NOTFOUND : PRISM_E_NULL;
+    if (!ms_out || m_tok == 0 || reps == 0) return fail(ctx, PRISM_E_ARG, "bad bench arguments");
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const size_t in_b = (size_t)m_tok * t->k * 2, out_b = (size_t)m_tok * t->m * 2;
+    PRISM_TRY(ensure_stage(ctx, in_b, out_b));
+    PRISM_CUDA_TRY(ctx, cudaMemsetAsync(ctx->stage_in, 0x2C, in_b, ctx->stream));  // fp16 0x2C2C ~ 0.065
+    PRISM_TRY(launch_gemm(ctx, *t, (const uint16_t *)ctx->stage_in, m_tok, (uint16_t *)ctx->stage_out));  // warm-up
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0, ctx->stream);
+    int rc = PRISM_OK;
+    for (uint32_t r = 0; r < reps && rc == PRISM_OK; r++)
+        rc = launch_gemm(ctx, *t, (const uint16_t *)ctx->stage_in, m_tok, (uint16_t *)ctx->stage_out);
+    cudaEventRecord(e1, ctx->stream);
+    cudaError_t ce = cudaStreamSynchronize(ctx->stream);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (rc != PRISM_OK) return rc;
+    if (ce != cudaSuccess) return cuda_fail(ctx, ce, "bench gemm");
+    *ms_out = ms;
+    return check_device_error(ctx);
 }
 
 // ---- glue ops on host slices (MetalBackend::{norm_metal,...}) ---------------------------------------

@@ -66,6 +66,7 @@ struct prism_cuda_ctx {
     std::unordered_map<std::string, int32_t> by_name;
     // options
     int gemv_variant = 1;
+    int gemm_variant = 1;  // 1: tcgen05/TMEM kernel where eligible, 0: activation rows through the GEMV kernel
     int fuse = 1;
     uint64_t launches = 0;
     // staging for host-pointer entry points (grown on demand)
@@ -144,6 +145,10 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
 bool tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t batch);
 int launch_gemv_tc5(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
                     void *y, const uint16_t *resid);
+
+// gemm_tc5.cu: tcgen05/TMEM prefill GEMM (4-bit, K % 32 == 0, >= 32 tokens)
+bool gemm_tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t m_tok);
+int launch_gemm_tc5(prism_cuda_ctx *ctx, const LutTensor &t, const uint16_t *X, uint32_t m_tok, uint16_t *Y);
 
 // glue.cu
 int launch_rms_norm(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint32_t n, float eps,

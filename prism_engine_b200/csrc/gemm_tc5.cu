@@ -1,0 +1,287 @@
+// Prefill palettized GEMM on tcgen05 / TMEM:  Y[t][r] = f16( sum_k f32(X[t][k]) * f32(W[r][k]) )
+// -- one lut_gemv_cpu per activation row (prefill_cpu, src/lut/engine_impl.rs:1046-1053; the
+// reference's never-dispatched kernel for the same job is templates/palettized_gemm.metal:16-117).
+//
+// One persistent CTA per SM computes tiles of 128 weight rows x 256 tokens over the whole K:
+//  * weights: 16 warps dequantise with the lane-private pair tables of gemv.cu / gemv_tc5.cu
+//    (one row per lane = one TMEM lane) and store 32 k at a time into a ring of TMEM stages --
+//    the A operand never touches shared memory;
+//  * activations: X is re-laid once per call into 16-byte units [k/8][token][8] so that a
+//    256-token x 32-k stage is four contiguous 4 KB runs, fetched by one thread with 1-D bulk
+//    copies that complete on an mbarrier; in shared memory the runs are exactly the K-major,
+//    no-swizzle core-matrix layout the B operand descriptor addresses;
+//  * one thread issues two tcgen05.mma (M = 128, N = 256, K = 16) per 32-k chunk; the fp32
+//    accumulators (256 TMEM columns) are read back with tcgen05.ld, rounded to fp16 and stored.
+// Every mbarrier wait is bounded; a wait that gives up raises the context's device error word.
+#include <algorithm>
+
+#include "common.cuh"
+#include "tc5_ptx.cuh"
+
+namespace prism {
+
+constexpr int GM_DEQ_WARPS = 16;
+constexpr int GM_MMA_WARP = 16, GM_X_WARP = 17;
+constexpr int GM_THREADS = 18 * 32;
+constexpr int GM_NT = 256;                    // tokens per tile = N of the MMA
+constexpr int GM_TBL_BYTES = 2 * 65536;
+constexpr int GM_SA = 8;                      // A stages (16 TMEM columns each)
+constexpr int GM_SX = 4;                      // X stages (256 tokens x 32 k fp16 = 16 KB each)
+constexpr int GM_XSTAGE_BYTES = GM_NT * 32 * 2;
+constexpr int GM_D_COL = GM_SA * 16;          // accumulator: 256 columns after the A stages
+constexpr int GM_TMEM_COLS = 512;
+constexpr int GM_PF = 4;
+constexpr int GM_SBASE = 1024;
+constexpr int GM_X_OFF = GM_TBL_BYTES;
+constexpr int GM_BAR_OFF = GM_X_OFF + GM_SX * GM_XSTAGE_BYTES;
+// barriers (8 B each): afull[SA], aempty[SA], xfull[SX], xempty[SX], dfull, dempty
+constexpr int GM_STATE_OFF = GM_BAR_OFF + 8 * (2 * GM_SA + 2 * GM_SX + 2);
+constexpr size_t GM_SMEM_BYTES = GM_STATE_OFF + 64;
+
+struct GemmArgs {
+    const uint8_t *idx;
+    const uint16_t *pal;
+    uint32_t n_chunks, n_hb, m;       // chunks per row (K/32), half-blocks, valid weight rows
+    uint32_t n_rt, n_tt;              // row tiles (128 rows), token tiles (256 tokens)
+    uint32_t m_tok, m_tok_pad;
+    const uint8_t *xc;                // [K/8][m_tok_pad][16 B]
+    uint16_t *y;                      // [m_tok][m]
+    unsigned int *err;
+};
+
+// X [m_tok][k] fp16 -> Xc [k/8][m_tok_pad][8]; padded token rows are zero.
+__global__ void gemm_relay_x_kernel(const uint16_t *__restrict__ x, uint32_t m_tok, uint32_t m_tok_pad, uint32_t k,
+                                    uint4 *__restrict__ xc) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)(k / 8) * m_tok_pad;
+    if (i >= total) return;
+    const uint32_t t = (uint32_t)(i % m_tok_pad), k8 = (uint32_t)(i / m_tok_pad);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < m_tok) v = *reinterpret_cast<const uint4 *>(x + (size_t)t * k + (size_t)k8 * 8);
+    xc[i] = v;
+}
+
+__device__ __forceinline__ uint32_t gm_lds(uint32_t off, int slot) {
+    uint32_t v;
+    if (slot == 0) asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(off), "n"(GM_SBASE));
+    else asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(off), "n"(GM_SBASE + 128));
+    return v;
+}
+
+__global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    if (smem_base != (uint32_t)GM_SBASE) {  // layout assumption broken: refuse to compute
+        if (threadIdx.x == 0) atomicExch(a.err, 4u);
+        return;
+    }
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t bar = smem_base + GM_BAR_OFF;
+    const uint32_t b_afull = bar, b_aempty = bar + 8 * GM_SA, b_xfull = bar + 16 * GM_SA,
+                   b_xempty = b_xfull + 8 * GM_SX, b_dfull = b_xempty + 8 * GM_SX, b_dempty = b_dfull + 8;
+    volatile uint32_t *err_flag = reinterpret_cast<volatile uint32_t *>(smem + GM_STATE_OFF);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + GM_STATE_OFF + 8);
+    const uint32_t nch = a.n_chunks;
+    const uint32_t n_items = a.n_rt * a.n_tt;  // item w: row tile w % n_rt, token tile w / n_rt
+
+    if (tid == 0) {
+        for (int s = 0; s < GM_SA; s++) { t5::mbar_init(b_afull + 8 * s, 4); t5::mbar_init(b_aempty + 8 * s, 1); }
+        for (int s = 0; s < GM_SX; s++) { t5::mbar_init(b_xfull + 8 * s, 1); t5::mbar_init(b_xempty + 8 * s, 1); }
+        t5::mbar_init(b_dfull, 1);
+        t5::mbar_init(b_dempty, GM_DEQ_WARPS);
+        *err_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == GM_MMA_WARP) t5::tmem_alloc(smem_base + GM_STATE_OFF + 8, GM_TMEM_COLS);
+    t5::fence_before();
+    __syncthreads();
+    t5::fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < GM_DEQ_WARPS) {
+        // =============================== dequantising warps ===============================
+        const uint32_t q = warp & 3, j = warp >> 2;      // TMEM lane quarter, slot within the quarter
+        const uint32_t pair = q & 1, slot = q >> 1;      // table area, row slot inside its entries
+        const uint32_t laneq = (pair << 16) | (lane * 4);
+        const uint32_t tmem_lane = tmem_base + ((q * 32) << 16);
+        uint32_t n_base = 0, ti = 0, cur_rt = 0xFFFFFFFFu;
+        for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x, ti++) {
+            const uint32_t rt = w % a.n_rt, tt = w / a.n_rt;
+            const uint32_t hb = 4 * rt + q;
+            const bool ok = hb < a.n_hb;
+            const uint32_t h = ok ? hb : a.n_hb - 1;
+            const uint8_t *sp = a.idx + (size_t)h * nch * 512 + lane * 16;
+            uint4 r[GM_PF];
+#pragma unroll
+            for (int i = 0; i < GM_PF; i++) {
+                const uint32_t c = j + 4 * i;
+                if (c < nch) r[i] = t5::ldg128_nc(sp + (size_t)c * 512);
+            }
+            if (rt != cur_rt) {  // same decision in all warps: they walk the same item list
+                cur_rt = rt;
+                asm volatile("bar.sync %0, 256;\n" ::"r"(1 + pair) : "memory");  // lookups of the previous tile are done
+                const uint16_t *prow = a.pal + ((size_t)h * 32 + lane) * 16;
+                const uint4 p0 = *reinterpret_cast<const uint4 *>(prow);
+                const uint4 p1 = *reinterpret_cast<const uint4 *>(prow + 8);
+                const uint32_t cbp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                const uint32_t hp0 = reinterpret_cast<const uint32_t *>(prow)[2 * j];
+                const uint32_t hp1 = reinterpret_cast<const uint32_t *>(prow)[2 * j + 1];
+                uint8_t *tb = smem + pair * 65536 + j * 16384 + lane * 4 + slot * 128;
+#pragma unroll
+                for (int lo = 0; lo < 16; lo++) {
+#pragma unroll
+                    for (int hs = 0; hs < 4; hs++) {
+                        const uint32_t sel = (((hs & 1) ? 0x76u : 0x54u) << 8) | ((lo & 1) ? 0x32u : 0x10u);
+                        *reinterpret_cast<uint32_t *>(tb + lo * 256 + hs * 4096) =
+                            __byte_perm(cbp[lo >> 1], (hs & 2) ? hp1 : hp0, sel);
+                    }
+                }
+                asm volatile("bar.sync %0, 256;\n" ::"r"(1 + pair) : "memory");
+            }
+            // ---- K loop: lookups -> TMEM stage -> signal the MMA thread ----
+            for (uint32_t c0 = j; c0 < nch; c0 += 4 * GM_PF) {
+#pragma unroll
+                for (int i = 0; i < GM_PF; i++) {
+                    const uint32_t c = c0 + 4 * i;
+                    if (c < nch) {
+                        const uint4 wv = r[i];
+                        const uint32_t nc = c + 4 * GM_PF;
+                        if (nc < nch) r[i] = t5::ldg128_nc(sp + (size_t)nc * 512);
+                        const uint32_t aw[4] = {wv.x, wv.y, wv.z, wv.w};
+                        uint32_t A[16];
+                        if (slot == 0) {
+#pragma unroll
+                            for (int hh = 0; hh < 4; hh++) {
+                                A[4 * hh + 0] = gm_lds(__byte_perm(aw[hh], laneq, 0x7604), 0);
+                                A[4 * hh + 1] = gm_lds(__byte_perm(aw[hh], laneq, 0x7614), 0);
+                                A[4 * hh + 2] = gm_lds(__byte_perm(aw[hh], laneq, 0x7624), 0);
+                                A[4 * hh + 3] = gm_lds(__byte_perm(aw[hh], laneq, 0x7634), 0);
+                            }
+                        } else {
+#pragma unroll
+                            for (int hh = 0; hh < 4; hh++) {
+                                A[4 * hh + 0] = gm_lds(__byte_perm(aw[hh], laneq, 0x7604), 1);
+                                A[4 * hh + 1] = gm_lds(__byte_perm(aw[hh], laneq, 0x7614), 1);
+                                A[4 * hh + 2] = gm_lds(__byte_perm(aw[hh], laneq, 0x7624), 1);
+                                A[4 * hh + 3] = gm_lds(__byte_perm(aw[hh], laneq, 0x7634), 1);
+                            }
+                        }
+                        const uint32_t n = n_base + c, stage = n % GM_SA, ph = (n / GM_SA) & 1;
+                        t5::mbar_wait_bounded(b_aempty + 8 * stage, ph ^ 1, err_flag);
+                        t5::fence_after();
+                        t5::st16(tmem_lane + stage * 16, A);
+                        t5::wait_st();
+                        t5::fence_before();
+                        if (lane == 0) t5::mbar_arrive(b_afull + 8 * stage);
+                    }
+                }
+            }
+            n_base += nch;
+            // ---- epilogue: warp (q, j) converts token columns [64j, 64j+64) of its 32 rows ----
+            t5::mbar_wait_bounded(b_dfull, ti & 1, err_flag);
+            t5::fence_after();
+            const uint32_t row = hb * 32 + lane;
+            const bool row_ok = ok && row < a.m;
+#pragma unroll 1
+            for (int g = 0; g < 4; g++) {
+                uint32_t v[16];
+                t5::ld16(tmem_lane + GM_D_COL + j * 64 + g * 16, v);
+                t5::wait_ld();
+                const uint32_t t0 = tt * GM_NT + j * 64 + g * 16;
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const uint32_t t = t0 + i;
+                    if (row_ok && t < a.m_tok)
+                        a.y[(size_t)t * a.m + row] = __half_as_ushort(__float2half_rn(__uint_as_float(v[i])));
+                }
+            }
+            t5::fence_before();
+            if (lane == 0) t5::mbar_arrive(b_dempty);
+        }
+    } else if (warp == GM_MMA_WARP && lane == 0) {
+        // =============================== MMA issuing thread ===============================
+        const uint32_t idesc = t5::idesc_f16(128, GM_NT);
+        const uint32_t x_addr = smem_base + GM_X_OFF;
+        uint32_t n = 0, ti = 0;
+        for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x, ti++) {
+            t5::mbar_wait_bounded(b_dempty, (ti & 1) ^ 1, err_flag);  // epilogue of the previous tile has read D
+            t5::fence_after();
+            const uint32_t dcol = tmem_base + GM_D_COL;
+            for (uint32_t c = 0; c < nch; c++, n++) {
+                const uint32_t sa = n % GM_SA, pa = (n / GM_SA) & 1, sx = n % GM_SX, px = (n / GM_SX) & 1;
+                t5::mbar_wait_bounded(b_xfull + 8 * sx, px, err_flag);
+                t5::mbar_wait_bounded(b_afull + 8 * sa, pa, err_flag);
+                t5::fence_after();
+                const uint32_t acol = tmem_base + sa * 16, xs = x_addr + sx * GM_XSTAGE_BYTES;
+                // B: 256 tokens x 16 k; core matrices of 8 tokens are 128 B apart, the two k-halves 4 KB apart
+                t5::mma_ts(dcol, acol, t5::smem_desc(xs, 4096, 128), idesc, c > 0);
+                t5::mma_ts(dcol, acol + 8, t5::smem_desc(xs + 8192, 4096, 128), idesc, 1);
+                t5::commit(b_aempty + 8 * sa);
+                t5::commit(b_xempty + 8 * sx);
+            }
+            t5::commit(b_dfull);
+        }
+    } else if (warp == GM_X_WARP && lane == 0) {
+        // =============================== activation loader ===============================
+        const uint32_t x_addr = smem_base + GM_X_OFF;
+        uint32_t n = 0;
+        for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x) {
+            const uint32_t tt = w / a.n_rt;
+            const uint8_t *src0 = a.xc + (size_t)tt * GM_NT * 16;
+            for (uint32_t c = 0; c < nch; c++, n++) {
+                const uint32_t sx = n % GM_SX, px = (n / GM_SX) & 1;
+                t5::mbar_wait_bounded(b_xempty + 8 * sx, px ^ 1, err_flag);
+                t5::mbar_arrive_expect_tx(b_xfull + 8 * sx, GM_XSTAGE_BYTES);
+#pragma unroll
+                for (int kb = 0; kb < 4; kb++)
+                    t5::bulk_g2s(x_addr + sx * GM_XSTAGE_BYTES + kb * 4096,
+                                 src0 + (size_t)(4 * c + kb) * a.m_tok_pad * 16, 4096, b_xfull + 8 * sx);
+            }
+        }
+    }
+    t5::fence_before();
+    __syncthreads();
+    if (warp == GM_MMA_WARP) t5::tmem_dealloc(tmem_base, GM_TMEM_COLS);
+    if (tid == 0 && *err_flag) atomicExch(a.err, 5u);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+bool gemm_tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t m_tok) {
+    return ctx->smem_base == GM_SBASE && t.bits == 4 && t.k % 32 == 0 && t.k >= 64 && m_tok >= 32;
+}
+
+int launch_gemm_tc5(prism_cuda_ctx *ctx, const LutTensor &t, const uint16_t *X, uint32_t m_tok, uint16_t *Y) {
+    static bool configured[8] = {false};
+    if (!configured[ctx->device & 7]) {
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)GM_SMEM_BYTES));
+        configured[ctx->device & 7] = true;
+    }
+    if (reinterpret_cast<uintptr_t>(X) & 15) return fail(ctx, PRISM_E_ARG, "gemm: X must be 16-byte aligned");
+    GemmArgs a{};
+    a.idx = t.idx; a.pal = t.pal;
+    a.n_chunks = t.n_chunks; a.n_hb = t.n_hb; a.m = t.m;
+    a.n_rt = (t.n_hb + 3) / 4;
+    a.m_tok = m_tok;
+    a.m_tok_pad = round_up_u32(m_tok, GM_NT);
+    a.n_tt = a.m_tok_pad / GM_NT;
+    a.y = Y; a.err = ctx->dev_err;
+    // X -> [k/8][token][8] (context scratch)
+    const size_t xc_halfs = (size_t)t.k * a.m_tok_pad;
+    PRISM_TRY(ensure_tmp(ctx, xc_halfs));
+    const size_t units = xc_halfs / 8;
+    gemm_relay_x_kernel<<<(unsigned)((units + 255) / 256), 256, 0, ctx->stream>>>(X, m_tok, a.m_tok_pad, t.k,
+                                                                                reinterpret_cast<uint4 *>(ctx->tmp_scratch));
+    PRISM_TRY(after_launch(ctx, "gemm_relay_x_kernel"));
+    a.xc = reinterpret_cast<const uint8_t *>(ctx->tmp_scratch);
+    // one row tile per CTA when possible, so its tables are built once
+    const uint32_t G = (uint32_t)ctx->sm_count;
+    uint32_t grid;
+    if (a.n_rt <= G) grid = a.n_rt * std::max(1u, std::min(G / a.n_rt, a.n_tt));
+    else grid = G;
+    lut_gemm_tc5_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, ctx->stream>>>(a);
+    return after_launch(ctx, "lut_gemm_tc5_kernel");
+}
+
+}  // namespace prism

@@ -99,12 +99,29 @@ def test_fused_gate_up_and_mlp(backend, oracle, variant, hidden, inter):
     backend.set_option("gemv_variant", 1)
 
 
-def test_gemm_rows_are_gemvs(backend, oracle):
-    m, k, m_tok = 192, 256, 37
+@pytest.mark.parametrize("gemm_variant", [0, 1])
+@pytest.mark.parametrize("m,k,m_tok", [(192, 256, 37), (256, 512, 300), (130, 64, 32), (512, 3584, 96)])
+def test_gemm_rows_are_gemvs(backend, oracle, gemm_variant, m, k, m_tok):
+    backend.set_option("gemm_variant", gemm_variant)
     pay = synth.make_payload(m, k, seed=6)
     X = synth.make_activation((m_tok, k), seed=6)
     h = backend.upload("gm", pay, m, k)
     Y = backend.gemm(h, X)
     want = oracle.lut_gemm(X, pay, m, k, threads=8)
     assert Y.shape == (m_tok, m) and rel_l2(Y.reshape(-1), want.reshape(-1)) <= TOL
+    assert np.mean(Y == want) > 0.9
+    backend.free(h)
+    backend.set_option("gemm_variant", 1)
+
+
+def test_gemm_full_size_rows_match_gemv(backend):
+    """Qwen2.5-7B q-projection shape, M = 2048 tokens: sampled rows of the tensor-core GEMM equal the GEMV
+    of the same activation row up to fp32 summation order."""
+    m, k, m_tok = 3584, 3584, 2048
+    h = backend.synth("gm.full", m, k, seed=3)
+    X = synth.make_activation((m_tok, k), seed=4)
+    Y = backend.gemm(h, X)
+    for t in (0, 1, 255, 256, 1000, 2047):
+        y = backend.gemv(h, X[t])
+        assert rel_l2(Y[t], y) <= TOL and np.mean(Y[t] == y) > 0.9, t
     backend.free(h)
