@@ -30,6 +30,7 @@ struct prism_cuda_engine {
     std::vector<int32_t> wq, wk, wv, wo, wg, wu, wd;
     std::vector<int32_t> wqkv;   // q, k, v rows stacked into one tensor (one launch instead of three)
     bool fused_ready = false;
+    uint16_t *gu = nullptr;      // [2][B][max(I_l, H)] scratch of the batched (GEMM) path
     uint16_t *qkv = nullptr;     // [B][qkv_stride]: q | k | v of a sequence side by side
     uint32_t qkv_stride = 0;
     int32_t embed = -1, lm_head = -1;
@@ -138,6 +139,30 @@ __global__ void final_pair_kernel(const uint64_t *__restrict__ pairs, uint32_t b
     next[b] = best ? ~(uint32_t)(best & 0xFFFFFFFFu) : 0u;
 }
 
+// One palettized linear of the step.  A batch of 8 or more sequences goes through the tensor-core
+// GEMM (weights streamed once for the whole batch) followed by the same elementwise kernels the
+// unfused path uses, so the fp16 rounding points stay those of the reference; smaller batches use
+// the GEMV kernels with their fused epilogues.
+static int linear(prism_cuda_engine *e, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
+                  uint32_t xs, uint16_t *y, uint32_t ys, const uint16_t *resid, uint32_t B) {
+    prism_cuda_ctx *ctx = e->ctx;
+    const bool gemm_ok = B >= 8 && ctx->gemm_variant == 1 && e->gu && gemm_tc5_eligible(ctx, t, B) && xs == t.k &&
+                         (mode == GEMV_SWIGLU ? ys == t.m : ys == t.m);
+    if (!gemm_ok) return launch_gemv(ctx, mode, t, t2, x, xs, y, ys, resid, B);
+    if (mode == GEMV_PLAIN) return launch_gemm(ctx, t, x, B, y);
+    if (mode == GEMV_RESID) {  // y (== resid, in place) = f16( f16(W x) + resid )
+        PRISM_TRY(launch_gemm(ctx, t, x, B, e->gu));
+        PRISM_TRY(launch_vec_add(ctx, e->gu, resid, B * t.m));
+        PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(y, e->gu, (size_t)B * t.m * 2, cudaMemcpyDeviceToDevice, ctx->stream));
+        return PRISM_OK;
+    }
+    // SwiGLU: gate and up GEMMs, then f16(f16(silu(g)) * u)
+    uint16_t *g = e->gu, *u = e->gu + (size_t)B * t.m;
+    PRISM_TRY(launch_gemm(ctx, t, x, B, g));
+    PRISM_TRY(launch_gemm(ctx, *t2, x, B, u));
+    return launch_silu_mul(ctx, y, g, u, B * t.m);
+}
+
 static int enqueue_step(prism_cuda_engine *e) {
     prism_cuda_ctx *ctx = e->ctx;
     const prism_model_config &c = e->cfg;
@@ -155,11 +180,11 @@ static int enqueue_step(prism_cuda_engine *e) {
         PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
         const uint32_t qs = e->qkv_stride;
         if (e->wqkv[l] >= 0) {
-            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, ctx->tensors[e->wqkv[l]], nullptr, e->xn, H, e->qkv, qs, nullptr, B));
+            PRISM_TRY(linear(e, GEMV_PLAIN, ctx->tensors[e->wqkv[l]], nullptr, e->xn, H, e->qkv, qs, nullptr, B));
         } else {
-            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tq, nullptr, e->xn, H, e->q, qs, nullptr, B));
-            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, qs, nullptr, B));
-            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, qs, nullptr, B));
+            PRISM_TRY(linear(e, GEMV_PLAIN, tq, nullptr, e->xn, H, e->q, qs, nullptr, B));
+            PRISM_TRY(linear(e, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, qs, nullptr, B));
+            PRISM_TRY(linear(e, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, qs, nullptr, B));
         }
         if (c.rope_k) PRISM_TRY(launch_rope(ctx, e->k, e->kvd_l, pos_dev, 0, e->hd, base, B, qs));
         const uint32_t slot_mul = e->guard_skip ? c.num_layers : 1, slot_add = e->guard_skip ? l : 0;
@@ -183,14 +208,14 @@ static int enqueue_step(prism_cuda_engine *e) {
             round_add_resid_kernel<<<(B * H + 255) / 256, 256, 0, ctx->stream>>>(e->part, e->h, B * H);
             PRISM_TRY(after_launch(ctx, "round_add_resid_kernel"));
         } else if (fused) {
-            PRISM_TRY(launch_gemv(ctx, GEMV_RESID, to, nullptr, e->att, e->qd_l, e->h, H, e->h, B));
+            PRISM_TRY(linear(e, GEMV_RESID, to, nullptr, e->att, e->qd_l, e->h, H, e->h, B));
         } else {
-            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, to, nullptr, e->att, e->qd_l, e->xn, H, nullptr, B));
+            PRISM_TRY(linear(e, GEMV_PLAIN, to, nullptr, e->att, e->qd_l, e->xn, H, nullptr, B));
             PRISM_TRY(launch_vec_add(ctx, e->xn, e->h, B * H));  // xn = f16(o + hr)
             PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->h, e->xn, (size_t)B * H * 2, cudaMemcpyDeviceToDevice, ctx->stream));
         }
         PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
-        PRISM_TRY(launch_gemv(ctx, GEMV_SWIGLU, tg, &tu, e->xn, H, e->act, e->act_stride, nullptr, B));
+        PRISM_TRY(linear(e, GEMV_SWIGLU, tg, &tu, e->xn, H, e->act, e->act_stride, nullptr, B));
         if (e->guard_skip) continue;  // DownProj skipped by the dim test (engine_impl.rs:1124-1126)
         const LutTensor &td = ctx->tensors[e->wd[l]];
         if (tp) {
@@ -199,9 +224,9 @@ static int enqueue_step(prism_cuda_engine *e) {
             round_add_resid_kernel<<<(B * H + 255) / 256, 256, 0, ctx->stream>>>(e->part, e->h, B * H);
             PRISM_TRY(after_launch(ctx, "round_add_resid_kernel"));
         } else if (fused) {
-            PRISM_TRY(launch_gemv(ctx, GEMV_RESID, td, nullptr, e->act, e->act_stride, e->h, H, e->h, B));
+            PRISM_TRY(linear(e, GEMV_RESID, td, nullptr, e->act, e->act_stride, e->h, H, e->h, B));
         } else {
-            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, td, nullptr, e->act, e->act_stride, e->xn, H, nullptr, B));
+            PRISM_TRY(linear(e, GEMV_PLAIN, td, nullptr, e->act, e->act_stride, e->xn, H, nullptr, B));
             PRISM_TRY(launch_vec_add(ctx, e->xn, e->h, B * H));
             PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->h, e->xn, (size_t)B * H * 2, cudaMemcpyDeviceToDevice, ctx->stream));
         }
@@ -210,7 +235,7 @@ static int enqueue_step(prism_cuda_engine *e) {
     PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
     const LutTensor &head = ctx->tensors[(c.tie_word_embeddings || e->lm_head < 0) ? e->embed : e->lm_head];
     const uint32_t lstride = round_up_u32(e->V_l, 8);
-    PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, head, nullptr, e->xn, H, e->logits, lstride, nullptr, B));
+    PRISM_TRY(linear(e, GEMV_PLAIN, head, nullptr, e->xn, H, e->logits, lstride, nullptr, B));
     if (tp) {
         local_pair_kernel<<<B, 1024, 0, ctx->stream>>>(e->logits, e->V_l, lstride, e->v0, e->pairs_send);
         PRISM_TRY(after_launch(ctx, "local_pair_kernel"));
@@ -397,6 +422,7 @@ int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg,
     ALLOC(e->h, (size_t)B * e->H * 2);
     ALLOC(e->xn, (size_t)B * e->H * 2);
     ALLOC(e->qkv, (size_t)B * e->qkv_stride * 2);
+    if (B >= 8) ALLOC(e->gu, 2 * (size_t)B * std::max(e->act_stride, e->H) * 2);
     ALLOC(e->att, (size_t)B * e->qd_l * 2);
     ALLOC(e->act, (size_t)B * e->act_stride * 2);
     ALLOC(e->logits, (size_t)B * round_up_u32(e->V_l, 8) * 2);
@@ -435,7 +461,7 @@ void prism_cuda_engine_destroy(prism_cuda_engine *e) {
     if (e->graph) cudaGraphExecDestroy(e->graph);
     for (int32_t h : e->wqkv)
         if (h >= 0) prism_cuda_free_tensor(e->ctx, h);
-    void *ptrs[] = {e->h, e->xn, e->qkv, e->att, e->act, e->logits, e->part, e->tok, e->next,
+    void *ptrs[] = {e->gu, e->h, e->xn, e->qkv, e->att, e->act, e->logits, e->part, e->tok, e->next,
                     e->out_tokens, e->prompts, e->pairs_send, e->pairs_recv, e->scalars, e->kc, e->vc};
     for (void *p : ptrs) cudaFree(p);
     if (e->ev0) cudaEventDestroy(e->ev0);

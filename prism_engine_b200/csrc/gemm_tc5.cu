@@ -23,11 +23,11 @@ namespace prism {
 constexpr int GM_DEQ_WARPS = 16;
 constexpr int GM_MMA_WARP = 16, GM_X_WARP = 17;
 constexpr int GM_THREADS = 18 * 32;
-constexpr int GM_NT = 256;                    // tokens per tile = N of the MMA
+constexpr int GM_NT_MAX = 256;                // largest token tile = N of the MMA (template parameter NT <= 256)
 constexpr int GM_TBL_BYTES = 2 * 65536;
 constexpr int GM_SA = 8;                      // A stages (16 TMEM columns each)
 constexpr int GM_SX = 4;                      // X stages (256 tokens x 32 k fp16 = 16 KB each)
-constexpr int GM_XSTAGE_BYTES = GM_NT * 32 * 2;
+constexpr int GM_XSTAGE_BYTES = GM_NT_MAX * 32 * 2;  // stage slot size (a tile of NT tokens uses NT*64 bytes of it)
 constexpr int GM_D_COL = GM_SA * 16;          // accumulator: 256 columns after the A stages
 constexpr int GM_TMEM_COLS = 512;
 constexpr int GM_PF = 4;
@@ -68,6 +68,7 @@ __device__ __forceinline__ uint32_t gm_lds(uint32_t off, int slot) {
     return v;
 }
 
+template <int NT>
 __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmArgs a) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
                             }
                         }
                         const uint32_t n = n_base + c, stage = n % GM_SA, ph = (n / GM_SA) & 1;
-                        t5::mbar_wait_bounded(b_aempty + 8 * stage, ph ^ 1, err_flag);
+                        t5::mbar_wait_warp(b_aempty + 8 * stage, ph ^ 1, err_flag);
                         t5::fence_after();
                         t5::st16(tmem_lane + stage * 16, A);
                         t5::wait_st();
@@ -178,21 +179,24 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
             }
             n_base += nch;
             // ---- epilogue: warp (q, j) converts token columns [64j, 64j+64) of its 32 rows ----
-            t5::mbar_wait_bounded(b_dfull, ti & 1, err_flag);
+            t5::mbar_wait_warp(b_dfull, ti & 1, err_flag);
             t5::fence_after();
             const uint32_t row = hb * 32 + lane;
             const bool row_ok = ok && row < a.m;
+            constexpr int CW = NT / 4 > 16 ? NT / 4 : 16;  // accumulator columns (tokens) per warp of a quarter
+            if ((int)j * CW < NT) {
 #pragma unroll 1
-            for (int g = 0; g < 4; g++) {
-                uint32_t v[16];
-                t5::ld16(tmem_lane + GM_D_COL + j * 64 + g * 16, v);
-                t5::wait_ld();
-                const uint32_t t0 = tt * GM_NT + j * 64 + g * 16;
+                for (int g = 0; g < CW / 16; g++) {
+                    uint32_t v[16];
+                    t5::ld16(tmem_lane + GM_D_COL + j * CW + g * 16, v);
+                    t5::wait_ld();
+                    const uint32_t t0 = tt * NT + j * CW + g * 16;
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const uint32_t t = t0 + i;
-                    if (row_ok && t < a.m_tok)
-                        a.y[(size_t)t * a.m + row] = __half_as_ushort(__float2half_rn(__uint_as_float(v[i])));
+                    for (int i = 0; i < 16; i++) {
+                        const uint32_t t = t0 + i;
+                        if (row_ok && t < a.m_tok)
+                            a.y[(size_t)t * a.m + row] = __half_as_ushort(__float2half_rn(__uint_as_float(v[i])));
+                    }
                 }
             }
             t5::fence_before();
@@ -200,7 +204,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
         }
     } else if (warp == GM_MMA_WARP && lane == 0) {
         // =============================== MMA issuing thread ===============================
-        const uint32_t idesc = t5::idesc_f16(128, GM_NT);
+        const uint32_t idesc = t5::idesc_f16(128, NT);
         const uint32_t x_addr = smem_base + GM_X_OFF;
         uint32_t n = 0, ti = 0;
         for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x, ti++) {
@@ -213,9 +217,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
                 t5::mbar_wait_bounded(b_afull + 8 * sa, pa, err_flag);
                 t5::fence_after();
                 const uint32_t acol = tmem_base + sa * 16, xs = x_addr + sx * GM_XSTAGE_BYTES;
-                // B: 256 tokens x 16 k; core matrices of 8 tokens are 128 B apart, the two k-halves 4 KB apart
-                t5::mma_ts(dcol, acol, t5::smem_desc(xs, 4096, 128), idesc, c > 0);
-                t5::mma_ts(dcol, acol + 8, t5::smem_desc(xs + 8192, 4096, 128), idesc, 1);
+                // B: NT tokens x 16 k; core matrices of 8 tokens are 128 B apart, k-blocks of 8 are NT*16 B apart
+                t5::mma_ts(dcol, acol, t5::smem_desc(xs, NT * 16, 128), idesc, c > 0);
+                t5::mma_ts(dcol, acol + 8, t5::smem_desc(xs + 2 * NT * 16, NT * 16, 128), idesc, 1);
                 t5::commit(b_aempty + 8 * sa);
                 t5::commit(b_xempty + 8 * sx);
             }
@@ -227,15 +231,15 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
         uint32_t n = 0;
         for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x) {
             const uint32_t tt = w / a.n_rt;
-            const uint8_t *src0 = a.xc + (size_t)tt * GM_NT * 16;
+            const uint8_t *src0 = a.xc + (size_t)tt * NT * 16;
             for (uint32_t c = 0; c < nch; c++, n++) {
                 const uint32_t sx = n % GM_SX, px = (n / GM_SX) & 1;
                 t5::mbar_wait_bounded(b_xempty + 8 * sx, px ^ 1, err_flag);
-                t5::mbar_arrive_expect_tx(b_xfull + 8 * sx, GM_XSTAGE_BYTES);
+                t5::mbar_arrive_expect_tx(b_xfull + 8 * sx, NT * 64);
 #pragma unroll
                 for (int kb = 0; kb < 4; kb++)
-                    t5::bulk_g2s(x_addr + sx * GM_XSTAGE_BYTES + kb * 4096,
-                                 src0 + (size_t)(4 * c + kb) * a.m_tok_pad * 16, 4096, b_xfull + 8 * sx);
+                    t5::bulk_g2s(x_addr + sx * GM_XSTAGE_BYTES + kb * NT * 16,
+                                 src0 + (size_t)(4 * c + kb) * a.m_tok_pad * 16, NT * 16, b_xfull + 8 * sx);
             }
         }
     }
@@ -248,30 +252,24 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
 // ---- host side ---------------------------------------------------------------------------------
 
 bool gemm_tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t m_tok) {
-    return ctx->smem_base == GM_SBASE && t.bits == 4 && t.k % 32 == 0 && t.k >= 64 && m_tok >= 32;
+    return ctx->smem_base == GM_SBASE && t.bits == 4 && t.k % 32 == 0 && t.k >= 64 && m_tok >= 8;
 }
 
-int launch_gemm_tc5(prism_cuda_ctx *ctx, const LutTensor &t, const uint16_t *X, uint32_t m_tok, uint16_t *Y) {
+template <int NT>
+static int launch_gemm_nt(prism_cuda_ctx *ctx, GemmArgs &a, const LutTensor &t, const uint16_t *X) {
     static bool configured[8] = {false};
     if (!configured[ctx->device & 7]) {
-        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemm_tc5_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)GM_SMEM_BYTES));
         configured[ctx->device & 7] = true;
     }
-    if (reinterpret_cast<uintptr_t>(X) & 15) return fail(ctx, PRISM_E_ARG, "gemm: X must be 16-byte aligned");
-    GemmArgs a{};
-    a.idx = t.idx; a.pal = t.pal;
-    a.n_chunks = t.n_chunks; a.n_hb = t.n_hb; a.m = t.m;
-    a.n_rt = (t.n_hb + 3) / 4;
-    a.m_tok = m_tok;
-    a.m_tok_pad = round_up_u32(m_tok, GM_NT);
-    a.n_tt = a.m_tok_pad / GM_NT;
-    a.y = Y; a.err = ctx->dev_err;
+    a.m_tok_pad = round_up_u32(a.m_tok, NT);
+    a.n_tt = a.m_tok_pad / NT;
     // X -> [k/8][token][8] (context scratch)
     const size_t xc_halfs = (size_t)t.k * a.m_tok_pad;
     PRISM_TRY(ensure_tmp(ctx, xc_halfs));
     const size_t units = xc_halfs / 8;
-    gemm_relay_x_kernel<<<(unsigned)((units + 255) / 256), 256, 0, ctx->stream>>>(X, m_tok, a.m_tok_pad, t.k,
+    gemm_relay_x_kernel<<<(unsigned)((units + 255) / 256), 256, 0, ctx->stream>>>(X, a.m_tok, a.m_tok_pad, t.k,
                                                                                 reinterpret_cast<uint4 *>(ctx->tmp_scratch));
     PRISM_TRY(after_launch(ctx, "gemm_relay_x_kernel"));
     a.xc = reinterpret_cast<const uint8_t *>(ctx->tmp_scratch);
@@ -280,8 +278,24 @@ int launch_gemm_tc5(prism_cuda_ctx *ctx, const LutTensor &t, const uint16_t *X, 
     uint32_t grid;
     if (a.n_rt <= G) grid = a.n_rt * std::max(1u, std::min(G / a.n_rt, a.n_tt));
     else grid = G;
-    lut_gemm_tc5_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, ctx->stream>>>(a);
+    lut_gemm_tc5_kernel<NT><<<grid, GM_THREADS, GM_SMEM_BYTES, ctx->stream>>>(a);
     return after_launch(ctx, "lut_gemm_tc5_kernel");
+}
+
+int launch_gemm_tc5(prism_cuda_ctx *ctx, const LutTensor &t, const uint16_t *X, uint32_t m_tok, uint16_t *Y) {
+    if (reinterpret_cast<uintptr_t>(X) & 15) return fail(ctx, PRISM_E_ARG, "gemm: X must be 16-byte aligned");
+    GemmArgs a{};
+    a.idx = t.idx; a.pal = t.pal;
+    a.n_chunks = t.n_chunks; a.n_hb = t.n_hb; a.m = t.m;
+    a.n_rt = (t.n_hb + 3) / 4;
+    a.m_tok = m_tok;
+    a.y = Y; a.err = ctx->dev_err;
+    // token tile = N of the MMA: as small as the batch allows (the activation tile is the operand
+    // that has to come through L2 for every 32-k chunk)
+    if (m_tok <= 32) return launch_gemm_nt<32>(ctx, a, t, X);
+    if (m_tok <= 64) return launch_gemm_nt<64>(ctx, a, t, X);
+    if (m_tok <= 128) return launch_gemm_nt<128>(ctx, a, t, X);
+    return launch_gemm_nt<256>(ctx, a, t, X);
 }
 
 }  // namespace prism

@@ -37,6 +37,7 @@ constexpr int T5_TBL_BYTES = 2 * 65536;      // two lane quarters x (256 entries
 constexpr int T5_KSLICE = 4096;              // k per CTA slice (x staged as 64 KB of core matrices)
 constexpr int T5_XB_BYTES = T5_KSLICE / 8 * 128;
 constexpr int T5_STAGES = 16;                // A stages of 16 TMEM columns (32 k of 128 rows)
+constexpr int T5_GROUP = 1;                  // stages released by one tcgen05.commit
 constexpr int T5_TMEM_COLS = 512;
 constexpr int T5_NACC = 4;                   // independent accumulators per tile (MMAs into one are serialised)
 constexpr int T5_D_COL = T5_STAGES * 16;     // accumulators: 2 buffers x T5_NACC x 16 columns
@@ -101,6 +102,18 @@ __device__ __forceinline__ void mbar_wait(uint32_t addr, uint32_t parity, volati
         if ((i & 63) == 63 && *err_flag) return;
     }
     *err_flag = 1;
+}
+// Whole-warp wait: lane 0 polls (with a short back-off), the other lanes park at the warp barrier.
+__device__ __forceinline__ void mbar_wait_warp(uint32_t addr, uint32_t parity, volatile uint32_t *err_flag) {
+    if ((threadIdx.x & 31) == 0) {
+        for (uint32_t i = 0; i < (16u << 20); i++) {
+            if (mbar_try_wait(addr, parity)) break;
+            if ((i & 63) == 63 && *err_flag) break;
+            if (i + 1 == (16u << 20)) *err_flag = 1;
+            __nanosleep(32);
+        }
+    }
+    __syncwarp();
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -301,7 +314,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
                         const uint32_t n = n_base + c, stage = n % T5_STAGES, ph = (n / T5_STAGES) & 1;
                         { T5_T0(); asm volatile("" :: "r"(A[0]), "r"(A[15])); T5_ACC(1); }
                         { T5_T0();
-                        mbar_wait(bar_empty + 8 * stage, ph ^ 1, err_flag);  // MMAs that read this stage are done
+#ifndef T5_NO_EMPTYWAIT
+                        mbar_wait_warp(bar_empty + 8 * (stage / T5_GROUP), ph ^ 1, err_flag);  // MMAs that read this stage group are done
+#endif
                         T5_ACC(2); }
                         tc_fence_after();
                         { T5_T0();
@@ -329,7 +344,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
             // ---- epilogue (warps 0..3 = the 128 rows of the tile): accumulator column 0 ----
             const uint32_t d = ti & 1;
             const uint32_t te = q * 32 + lane;  // row inside the tile
-            mbar_wait(bar_dfull + 8 * d, (ti >> 1) & 1, err_flag);
+            mbar_wait_warp(bar_dfull + 8 * d, (ti >> 1) & 1, err_flag);
             tc_fence_after();
             // consecutive MMAs went to T5_NACC accumulators in turn; add the ones that were used
             const uint32_t n_used = min((uint32_t)T5_NACC, 2 * nch);
@@ -407,7 +422,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
             for (uint32_t c = 0; c < nch; c++, n++) {
                 const uint32_t stage = n % T5_STAGES, ph = (n / T5_STAGES) & 1;
                 { T5_T0(); mbar_wait(bar_full + 8 * stage, ph, err_flag); T5_ACC(0); }
+#ifndef T5_NO_FENCE
                 tc_fence_after();
+#endif
                 T5_T0();
                 const uint32_t acol = tmem_base + stage * 16;
                 const uint32_t m0 = 2 * c, m1 = 2 * c + 1;  // MMA number inside the tile
@@ -417,7 +434,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
 #else
                 (void)m0; (void)m1; (void)acol; (void)xb_addr; (void)idesc;
 #endif
-                tc_commit(bar_empty + 8 * stage);  // arrives when these MMAs have consumed the stage
+                // one commit per group of stages: a tcgen05.commit costs several hundred cycles of the
+                // tensor pipe's command stream, far more than the two small MMAs of a chunk
+#ifndef T5_NO_COMMIT
+                if (stage % T5_GROUP == T5_GROUP - 1) tc_commit(bar_empty + 8 * (stage / T5_GROUP));
+#endif
                 T5_ACC(1);
             }
             tc_commit(bar_dfull + 8 * d);

@@ -43,11 +43,45 @@ __device__ float block_max(float v, float *sh) {
 }
 
 // rms_norm_inplace (cpu_fallback.rs:39-54): x * 1/sqrt(mean(x^2)+eps), no weight.
-__global__ void rms_norm_kernel(const uint16_t *__restrict__ in, uint16_t *__restrict__ out, uint32_t n,
-                                float eps) {
+// One block per sequence; each thread keeps its (up to 16) elements in registers between the
+// sum of squares and the scaling, so the vector is read once.
+constexpr int RMS_THREADS = 1024;
+__global__ void __launch_bounds__(RMS_THREADS) rms_norm_kernel(const uint16_t *__restrict__ in,
+                                                               uint16_t *__restrict__ out, uint32_t n, float eps) {
     __shared__ float sh[32];
     const uint16_t *x = in + (size_t)blockIdx.x * n;
     uint16_t *y = out + (size_t)blockIdx.x * n;
+    const bool vec = (n % 8 == 0) && n <= RMS_THREADS * 16 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16 == 0);
+    if (vec) {
+        uint4 v[2];
+        float ss = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const uint32_t i = (threadIdx.x + u * RMS_THREADS) * 8;
+            v[u] = make_uint4(0, 0, 0, 0);
+            if (i < n) {
+                v[u] = *reinterpret_cast<const uint4 *>(x + i);
+                const uint16_t *e = reinterpret_cast<const uint16_t *>(&v[u]);
+#pragma unroll
+                for (int k = 0; k < 8; k++) { const float f = h2f(e[k]); ss += f * f; }
+            }
+        }
+        ss = block_sum(ss, sh);
+        const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const uint32_t i = (threadIdx.x + u * RMS_THREADS) * 8;
+            if (i < n) {
+                uint4 o;
+                const uint16_t *e = reinterpret_cast<const uint16_t *>(&v[u]);
+                uint16_t *d = reinterpret_cast<uint16_t *>(&o);
+#pragma unroll
+                for (int k = 0; k < 8; k++) d[k] = f2h(h2f(e[k]) * inv);
+                *reinterpret_cast<uint4 *>(y + i) = o;
+            }
+        }
+        return;
+    }
     float ss = 0.0f;
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
         float f = h2f(x[i]);
@@ -60,7 +94,7 @@ __global__ void rms_norm_kernel(const uint16_t *__restrict__ in, uint16_t *__res
 
 int launch_rms_norm(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint32_t n, float eps,
                     uint32_t batch) {
-    rms_norm_kernel<<<batch, 256, 0, ctx->stream>>>(in, out, n, eps);
+    rms_norm_kernel<<<batch, RMS_THREADS, 0, ctx->stream>>>(in, out, n, eps);
     return after_launch(ctx, "rms_norm_kernel");
 }
 

@@ -38,6 +38,20 @@ __device__ __forceinline__ void mbar_wait_bounded(uint32_t addr, uint32_t parity
     }
     *err_flag = 1;
 }
+// Whole-warp wait: lane 0 polls (with a short back-off), the other lanes park at the warp barrier.
+// Thirty-two lanes polling one barrier word multiply the traffic on it and delay the arrivals.
+__device__ __forceinline__ void mbar_wait_warp(uint32_t addr, uint32_t parity, volatile uint32_t *err_flag,
+                                               uint32_t limit = 16u << 20) {
+    if ((threadIdx.x & 31) == 0) {
+        for (uint32_t i = 0; i < limit; i++) {
+            if (mbar_test(addr, parity)) break;
+            if ((i & 63) == 63 && *err_flag) break;
+            if (i + 1 == limit) *err_flag = 1;
+            __nanosleep(32);
+        }
+    }
+    __syncwarp();
+}
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void commit(uint32_t mbar_addr) {

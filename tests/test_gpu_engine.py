@@ -154,6 +154,25 @@ def test_batched_sequences_match_single(oracle):
     eng.close(); be.close()
 
 
+def test_batch8_goes_through_the_gemm_and_matches_the_oracle(oracle):
+    """Eight sequences per step: every linear is one tensor-core GEMM over the batch; tokens of each sequence
+    must still be the oracle's."""
+    cfg = dict(TINY, hidden_size=128, intermediate_size=256, head_dim=32, vocab_size=1024)
+    be = p.CudaBackend(device=0)
+    mc = p.model_config(**cfg, max_seq=64, max_batch=8, profile="baseline")
+    eng = p.PrismEngine(be, mc)
+    eng.synth_weights(seed=13)
+    prompts = np.stack([synth.make_prompt(5, cfg["vocab_size"], seed=s) for s in range(8)])
+    l0 = be.launch_count()
+    got = eng.generate(prompts, 33)
+    assert be.launch_count() > l0
+    twin = oracle_twin(oracle, be, cfg, mc)
+    for b in (0, 3, 7):
+        want, margins = twin.generate(prompts[b], 33)
+        assert np.array_equal(got[b][:32], want[:32]), (b, float(margins.min()))
+    eng.close(); twin.close(); be.close()
+
+
 @pytest.mark.timeout(1500)
 def test_qwen25_0p5b_first_32_tokens(oracle):
     """The 0.5B-architecture model of the benchmark configuration: identical greedy tokens for 32 steps."""
