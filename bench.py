@@ -315,9 +315,10 @@ def run_ours(args):
     return 0
 
 
-# DRAM bytes per algorithmic byte of lut_gemv_mma_kernel from the ncu capture summarised under
-# profiles/ (None until a capture exists).
-TRAFFIC_PER_ALGORITHMIC_BYTE = None
+# DRAM bytes per algorithmic byte of lut_gemv_mma_kernel, from the ncu capture summarised in
+# profiles/lut_gemv_mma_kernel_qwen72b_shapes.md (LM-head launch: 3.30 TB/s x 191.9 us = 633 MB of
+# DRAM traffic for 628 MB of algorithmic bytes).
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.008
 
 
 def small_shape_bandwidth(be, peak):
