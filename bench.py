@@ -173,7 +173,7 @@ def run_reference(args):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
     return 0
 
 
@@ -306,7 +306,7 @@ def run_ours(args):
                                     "sample": cs.sample + "; median of 3"}
         if world == 1 and not args.no_gemv_shapes:
             line["lut_gemv_0p5b_shapes"] = small_shape_bandwidth(be, peak)
-        print(json.dumps(line))
+        emit(line)
     eng.close()
     be.close()
     if dist is not None:
@@ -413,12 +413,31 @@ def run_gemm(args):
                 "h2d_bytes_per_step": int(X.nbytes), "d2h_bytes_per_step": m_tok * I * 2},
         "gpu_launches": launches, "clocks": clocks,
     }
-    print(json.dumps(line))
+    emit(line)
     be.close()
     return 0
 
 
+_RESULT_FD = None
+
+
+def emit(line):
+    """Writes the result line to the process's original stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    # Libraries loaded by the run (NCCL prints its version banner) write to file descriptor 1;
+    # the contract is ONE JSON line on stdout, so everything else is routed to stderr.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -435,7 +454,7 @@ def main():
         args.warmup = 3
     if args.workload.endswith("prefill-gemm"):
         if args.impl == "reference":
-            print(json.dumps({"impl": "reference", "unavailable": "the reference arm times decode; run the decode workloads"}))
+            emit({"impl": "reference", "unavailable": "the reference arm times decode; run the decode workloads"})
             return 0
         return run_gemm(args)
     if args.impl == "reference":

@@ -15,6 +15,7 @@ on the CPU.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import Dict, Optional, Tuple
 
 import numpy as np
@@ -49,12 +50,15 @@ class CudaBackend:
         self.ctx = h
         self.device = device
         self.handles: Dict[str, int] = {}
+        self._engines = weakref.WeakSet()  # engines built on this context: destroyed before it
         for key, (payload, dm, dn) in (tensors or {}).items():
             self.upload(key, payload, dm, dn, bits)
 
     # -- lifetime -----------------------------------------------------------------------------
     def close(self) -> None:
         if getattr(self, "ctx", None):
+            for eng in list(self._engines):
+                eng.close()
             self.L.prism_cuda_destroy(self.ctx)
             self.ctx = None
 
@@ -314,6 +318,7 @@ class PrismEngine:
         h = C.c_void_p()
         check(backend.ctx, self.L.prism_cuda_engine_create(backend.ctx, C.byref(cfg), C.byref(h)))
         self.h = h
+        backend._engines.add(self)
 
     @classmethod
     def load(cls, backend: CudaBackend, path: str, cfg: ModelConfig, key_prefix: str = "model") -> "PrismEngine":

@@ -66,6 +66,7 @@ struct prism_cuda_ctx {
     std::unordered_map<std::string, int32_t> by_name;
     // options
     int gemv_variant = 1;
+    float pending_norm_eps = -1.0f;  // >= 0: the next launch_gemv normalises its input row first (then clears this)
     int gemm_variant = 1;  // 1: tcgen05/TMEM kernel where eligible, 0: activation rows through the GEMV kernel
     int fuse = 1;
     uint64_t launches = 0;

@@ -177,11 +177,17 @@ static int enqueue_step(prism_cuda_engine *e) {
     for (uint32_t l = 0; l < c.num_layers; l++) {
         const LutTensor &tq = ctx->tensors[e->wq[l]], &tk = ctx->tensors[e->wk[l]], &tv = ctx->tensors[e->wv[l]],
                         &to = ctx->tensors[e->wo[l]], &tg = ctx->tensors[e->wg[l]], &tu = ctx->tensors[e->wu[l]];
-        PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
         const uint32_t qs = e->qkv_stride;
-        if (e->wqkv[l] >= 0) {
+        // the Norm node is folded into the x staging of the matmul that consumes it (small batches)
+        const bool fold = fused && B < 8;
+        if (fold && e->wqkv[l] >= 0) {
+            ctx->pending_norm_eps = c.norm_eps;
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, ctx->tensors[e->wqkv[l]], nullptr, e->h, H, e->qkv, qs, nullptr, B));
+        } else if (e->wqkv[l] >= 0) {
+            PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
             PRISM_TRY(linear(e, GEMV_PLAIN, ctx->tensors[e->wqkv[l]], nullptr, e->xn, H, e->qkv, qs, nullptr, B));
         } else {
+            PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
             PRISM_TRY(linear(e, GEMV_PLAIN, tq, nullptr, e->xn, H, e->q, qs, nullptr, B));
             PRISM_TRY(linear(e, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, qs, nullptr, B));
             PRISM_TRY(linear(e, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, qs, nullptr, B));
@@ -214,8 +220,13 @@ static int enqueue_step(prism_cuda_engine *e) {
             PRISM_TRY(launch_vec_add(ctx, e->xn, e->h, B * H));  // xn = f16(o + hr)
             PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->h, e->xn, (size_t)B * H * 2, cudaMemcpyDeviceToDevice, ctx->stream));
         }
-        PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
-        PRISM_TRY(linear(e, GEMV_SWIGLU, tg, &tu, e->xn, H, e->act, e->act_stride, nullptr, B));
+        if (fold) {
+            ctx->pending_norm_eps = c.norm_eps;
+            PRISM_TRY(launch_gemv(ctx, GEMV_SWIGLU, tg, &tu, e->h, H, e->act, e->act_stride, nullptr, B));
+        } else {
+            PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
+            PRISM_TRY(linear(e, GEMV_SWIGLU, tg, &tu, e->xn, H, e->act, e->act_stride, nullptr, B));
+        }
         if (e->guard_skip) continue;  // DownProj skipped by the dim test (engine_impl.rs:1124-1126)
         const LutTensor &td = ctx->tensors[e->wd[l]];
         if (tp) {
@@ -232,10 +243,16 @@ static int enqueue_step(prism_cuda_engine *e) {
         }
         li += 1;
     }
-    PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
+    const bool fold_head = fused && B < 8;
+    if (!fold_head) PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
     const LutTensor &head = ctx->tensors[(c.tie_word_embeddings || e->lm_head < 0) ? e->embed : e->lm_head];
     const uint32_t lstride = round_up_u32(e->V_l, 8);
-    PRISM_TRY(linear(e, GEMV_PLAIN, head, nullptr, e->xn, H, e->logits, lstride, nullptr, B));
+    if (fold_head) {
+        ctx->pending_norm_eps = c.norm_eps;
+        PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, head, nullptr, e->h, H, e->logits, lstride, nullptr, B));
+    } else {
+        PRISM_TRY(linear(e, GEMV_PLAIN, head, nullptr, e->xn, H, e->logits, lstride, nullptr, B));
+    }
     if (tp) {
         local_pair_kernel<<<B, 1024, 0, ctx->stream>>>(e->logits, e->V_l, lstride, e->v0, e->pairs_send);
         PRISM_TRY(after_launch(ctx, "local_pair_kernel"));

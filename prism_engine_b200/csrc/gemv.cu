@@ -100,6 +100,8 @@ struct MmaGemvArgs {
     float *partials;              // [batch][ksplit][n_blocks*64]
     unsigned int *counters;       // [batch][n_blocks]
     unsigned int *err;            // device error word (set when a layout assumption does not hold)
+    uint32_t norm_n;              // > 0: x is an un-normalised row of norm_n values; stage rms_norm(x) instead
+    float norm_eps;
 };
 
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -209,7 +211,41 @@ __global__ void __launch_bounds__(MMA_THREADS, 3) lut_gemv_mma_kernel(const MmaG
         const uint32_t n16 = (c_end - c_begin) * 4;  // 16-byte units: 32 halves per chunk
         const uint4 *xg = reinterpret_cast<const uint4 *>(a.x + (size_t)bat * a.x_stride + (size_t)c_begin * 32);
         uint4 *xd = reinterpret_cast<uint4 *>(xs);
-        for (uint32_t i = tid; i < n16; i += MMA_THREADS) xd[i] = xg[i];
+        if (a.norm_n == 0) {
+            for (uint32_t i = tid; i < n16; i += MMA_THREADS) xd[i] = xg[i];
+        } else {
+            // RMSNorm folded into the staging (rms_norm_inplace, src/lut/cpu_fallback.rs:39-54): every CTA
+            // sums the squares of the whole row (a few KB from L2), then scales only its own K slice.
+            const uint4 *xrow = reinterpret_cast<const uint4 *>(a.x + (size_t)bat * a.x_stride);
+            float ss = 0.0f;
+            for (uint32_t i = tid; i < a.norm_n / 8; i += MMA_THREADS) {
+                const uint4 v = xrow[i];
+                const __half2 *hp = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __half22float2(hp[e]);
+                    ss += f.x * f.x + f.y * f.y;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+            if (lane == 0) red[warp] = ss;
+            __syncthreads();
+            float tot = 0.0f;
+#pragma unroll
+            for (int w = 0; w < MMA_WARPS; w++) tot += red[w];  // fixed order: the same value in every CTA
+            const float inv = 1.0f / sqrtf(tot / (float)a.norm_n + a.norm_eps);
+            for (uint32_t i = tid; i < n16; i += MMA_THREADS) {
+                uint4 v = xg[i];
+                __half2 *hp = reinterpret_cast<__half2 *>(&v);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __half22float2(hp[e]);
+                    hp[e] = __floats2half2_rn(f.x * inv, f.y * inv);
+                }
+                xd[i] = v;
+            }
+        }
     }
     // ---- build the pair tables: entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]} -----------
     // warp w writes the entries with hi in {2w, 2w+1}; lane L writes its own bank.
@@ -397,8 +433,20 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
         if (!t2 || t2->m != t.m || t2->k != t.k || t2->bits != t.bits)
             return fail(ctx, PRISM_E_ARG, "fused_gate_up: gate and up must have identical shape");
     }
-    if (ctx->gemv_variant == 2 && tc5_eligible(ctx, t, batch)) return launch_gemv_tc5(ctx, mode, t, t2, x, y, resid);
-    const bool use_mma = ctx->gemv_variant >= 1 && mma_eligible(t);
+    // a caller may ask for RMSNorm of x to be folded in (engine: the Norm node in front of a matmul)
+    const float norm_eps = ctx->pending_norm_eps;
+    ctx->pending_norm_eps = -1.0f;
+    const bool use_tc5 = ctx->gemv_variant == 2 && tc5_eligible(ctx, t, batch);
+    const bool use_mma = !use_tc5 && ctx->gemv_variant >= 1 && mma_eligible(t);
+    if (norm_eps >= 0.0f && !(use_mma && t.k % 8 == 0 && x_stride >= t.k)) {
+        // this kernel choice cannot fold the norm: run it as its own kernel into scratch
+        PRISM_TRY(ensure_act(ctx, (size_t)batch * x_stride + 64));
+        uint16_t *xn = ctx->act_scratch;
+        for (uint32_t b = 0; b < batch; b++)
+            PRISM_TRY(launch_rms_norm(ctx, x + (size_t)b * x_stride, xn + (size_t)b * x_stride, t.k, norm_eps, 1));
+        return launch_gemv(ctx, mode, t, t2, xn, x_stride, y, y_stride, resid, batch);
+    }
+    if (use_tc5) return launch_gemv_tc5(ctx, mode, t, t2, x, y, resid);
     if (!use_mma) {
         // plain kernel + separate elementwise kernels keep the same rounding points
         if (mode == GEMV_SWIGLU) {
@@ -412,6 +460,16 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
             return PRISM_OK;
         }
         if (mode == GEMV_F32) return fail(ctx, PRISM_E_ARG, "fp32 partial output needs the tensor-core GEMV (4-bit, K % 32 == 0)");
+        if (mode == GEMV_RESID && y == resid) {
+            // in place (y is the residual stream): the product goes to scratch first, then y = f16(y + W x)
+            const size_t st = t.m_pad;
+            PRISM_TRY(ensure_tmp(ctx, (size_t)batch * st));
+            uint16_t *p = ctx->tmp_scratch;
+            PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, t, nullptr, x, x_stride, p, (uint32_t)st, nullptr, batch));
+            for (uint32_t b = 0; b < batch; b++)
+                PRISM_TRY(launch_vec_add(ctx, y + (size_t)b * y_stride, p + b * st, t.m));
+            return PRISM_OK;
+        }
         dim3 grid(t.n_hb, batch);
         if (t.bits == 4)
             lut_gemv_simple_kernel<4><<<grid, SIMPLE_WARPS * 32, 0, ctx->stream>>>(
@@ -432,6 +490,8 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
     a.m = t.m;
     a.x = x; a.x_stride = x_stride; a.y = y; a.y_stride = y_stride; a.resid = resid;
     a.err = ctx->dev_err;
+    a.norm_n = norm_eps >= 0.0f ? t.k : 0;
+    a.norm_eps = norm_eps >= 0.0f ? norm_eps : 0.0f;
     uint32_t n_blocks;
     if (mode == GEMV_SWIGLU) {
         a.idx1 = t.idx; a.pal1 = t.pal; a.idx2 = t2->idx; a.pal2 = t2->pal;
