@@ -207,6 +207,9 @@ def run_ours(args):
         dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world,
                                 device_id=torch.device("cuda", local))
     be = p.CudaBackend(device=local)
+    for kv in args.option:
+        key, val = kv.split("=")
+        be.set_option(key, int(val))
     if world > 1:
         from prism_engine_b200 import tp
 
@@ -449,6 +452,8 @@ def main():
     ap.add_argument("--ctx", type=int, default=-1, help="override the prompt context length (profiling/debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemv-shapes", action="store_true")
+    ap.add_argument("--option", action="append", default=[], metavar="KEY=INT",
+                    help="backend tunable (gemv_variant, gemm_variant, fuse, pdl); profiling/debugging only")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

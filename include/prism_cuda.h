@@ -57,10 +57,15 @@ const char *prism_cuda_last_error(prism_cuda_ctx *ctx);
 /* The CUDA stream (cudaStream_t) the context launches on. */
 void *prism_cuda_stream(prism_cuda_ctx *ctx);
 int prism_cuda_synchronize(prism_cuda_ctx *ctx);
-/* Tunables: "gemv_variant" (0 = plain CUDA-core kernel, 1 = pair-table mma.sync
- * kernel, default, 2 = pair-table tcgen05/TMEM kernel), "gemm_variant" (1 = tcgen05/TMEM
+/* Tunables: "gemv_variant" (0 = plain CUDA-core kernel, 1 = persistent stream-K pair-table
+ * mma.sync kernel, default, 2 = pair-table tcgen05/TMEM kernel, 3 = the pair-table mma.sync
+ * kernel on a (block, K split) grid), "gemm_variant" (1 = tcgen05/TMEM
  * prefill GEMM, default; 0 = activation rows through the GEMV kernel), "fuse" (0/1,
- * default 1: fused epilogues). */
+ * default 1: fused epilogues), "pdl" (0/1, default 1: programmatic dependent launch between
+ * the kernels of a decode step, so a kernel's weight-only prologue overlaps its predecessor),
+ * "sk_min_chunks" (default 8: fewest 1 KB index chunks the GEMV gives one CTA of a small matrix),
+ * "sk_stream_chunks" (default 64: chunks per CTA from which the GEMV deals contiguous, balanced
+ * ranges to a persistent grid instead of cutting every 64-row block into equal parts). */
 int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value);
 /* Number of kernels this library has launched on the context so far. */
 uint64_t prism_cuda_launch_count(prism_cuda_ctx *ctx);

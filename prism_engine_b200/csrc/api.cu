@@ -214,13 +214,21 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx) {
 int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
     if (!ctx || !key) return PRISM_E_NULL;
     if (!strcmp(key, "gemv_variant")) {
-        if (value < 0 || value > 2) return fail(ctx, PRISM_E_ARG, "gemv_variant must be 0, 1 or 2");
+        if (value < 0 || value > 3) return fail(ctx, PRISM_E_ARG, "gemv_variant must be 0, 1, 2 or 3");
         ctx->gemv_variant = (int)value;
     } else if (!strcmp(key, "gemm_variant")) {
         if (value != 0 && value != 1) return fail(ctx, PRISM_E_ARG, "gemm_variant must be 0 or 1");
         ctx->gemm_variant = (int)value;
     } else if (!strcmp(key, "fuse")) {
         ctx->fuse = value ? 1 : 0;
+    } else if (!strcmp(key, "sk_min_chunks")) {
+        if (value < 1 || value > 4096) return fail(ctx, PRISM_E_ARG, "sk_min_chunks must be in 1..4096");
+        ctx->sk_min_chunks = (int)value;
+    } else if (!strcmp(key, "sk_stream_chunks")) {
+        if (value < 8 || value > (1 << 20)) return fail(ctx, PRISM_E_ARG, "sk_stream_chunks must be in 8..2^20");
+        ctx->sk_stream_chunks = (int)value;
+    } else if (!strcmp(key, "pdl")) {
+        ctx->pdl = value ? 1 : 0;
     } else {
         return fail(ctx, PRISM_E_ARG, std::string("unknown option ") + key);
     }

@@ -69,6 +69,9 @@ struct prism_cuda_ctx {
     float pending_norm_eps = -1.0f;  // >= 0: the next launch_gemv normalises its input row first (then clears this)
     int gemm_variant = 1;  // 1: tcgen05/TMEM kernel where eligible, 0: activation rows through the GEMV kernel
     int fuse = 1;
+    int sk_min_chunks = 8;      // stream-K GEMV, small matrices: fewest 1 KB index chunks a CTA is given
+    int sk_stream_chunks = 64;  // chunks per CTA from which the balanced contiguous partition is used
+    int pdl = 1;  // programmatic dependent launch between the kernels of the decode chain
     uint64_t launches = 0;
     // staging for host-pointer entry points (grown on demand)
     uint8_t *stage_in = nullptr, *stage_out = nullptr;
@@ -111,6 +114,37 @@ int cuda_fail(prism_cuda_ctx *ctx, cudaError_t e, const char *what);
 // Checks the launch that was just issued and counts it.
 int after_launch(prism_cuda_ctx *ctx, const char *kernel);
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// Kernels of the decode chain begin with pdl_launch_dependents() (the next kernel of the stream may
+// be scheduled as soon as every CTA of this one has started) and call pdl_wait() before they touch
+// anything another kernel produces or consumes: it returns when all earlier kernels have completed
+// and their writes are visible.  What runs before pdl_wait() (index prefetch, palette loads, table
+// build: inputs that no kernel writes) overlaps the tail of the previous kernel, and the launch
+// latency between kernels is hidden.  Only kernels that call pdl_wait() may be launched with
+// launch_pdl(); a kernel that never calls pdl_launch_dependents() releases its dependents when it
+// exits, which is the ordinary stream order.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(prism_cuda_ctx *ctx, const char *name, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                      size_t smem, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    (void)name;
+    (void)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);  // a failure stays in the last-error slot: after_launch() reports it
+}
+#endif
+
 int ensure_stage(prism_cuda_ctx *ctx, size_t in_bytes, size_t out_bytes);
 int ensure_splitk(prism_cuda_ctx *ctx, size_t floats, size_t counters);
 int ensure_act(prism_cuda_ctx *ctx, size_t halfs);
@@ -141,6 +175,13 @@ enum GemvMode { GEMV_PLAIN = 0, GEMV_RESID = 1, GEMV_SWIGLU = 2, GEMV_F32 = 3 };
 int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2,
                 const uint16_t *x, uint32_t x_stride, uint16_t *y, uint32_t y_stride,
                 const uint16_t *resid, uint32_t batch);
+
+// gemv_sk.cu: persistent stream-K form of the pair-table tensor-core GEMV (4-bit, K % 32 == 0);
+// norm_eps >= 0 folds RMSNorm of x into the staging
+bool sk_eligible(const LutTensor &t);
+int launch_gemv_sk(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
+                   uint32_t x_stride, void *y, uint32_t y_stride, const uint16_t *resid, uint32_t batch,
+                   float norm_eps);
 
 // gemv_tc5.cu: tcgen05/TMEM GEMV (4-bit, K % 32 == 0, one activation vector)
 bool tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t batch);

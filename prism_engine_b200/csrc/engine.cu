@@ -68,6 +68,8 @@ static void split_units(uint32_t total_units, int T, int r, uint32_t *u0, uint32
 // vec_add_inplace with the residual (engine_impl.rs:1158-1162), applied to the
 // all-reduced fp32 sums of a row-parallel matmul.
 __global__ void round_add_resid_kernel(const float *__restrict__ sum, uint16_t *__restrict__ h, uint32_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         float y = __half2float(__float2half_rn(sum[i]));
@@ -79,6 +81,8 @@ __global__ void round_add_resid_kernel(const float *__restrict__ sum, uint16_t *
 // tok[b] = next[b] (the greedy token feeds the next step), step += 1.
 __global__ void advance_kernel(int32_t *scalars, const uint32_t *__restrict__ next, uint32_t *__restrict__ tok,
                                uint32_t *__restrict__ out_tokens, uint32_t batch, uint32_t out_cap) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int32_t step = scalars[1], record = scalars[2];
     if (record) {
         for (uint32_t b = threadIdx.x; b < batch; b += blockDim.x) {
@@ -105,6 +109,8 @@ __device__ __forceinline__ uint64_t pack_pair(float v, uint32_t idx) {
 }
 __global__ void local_pair_kernel(const uint16_t *__restrict__ logits, uint32_t n, uint32_t stride,
                                   uint32_t idx0, uint64_t *__restrict__ pairs) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ uint64_t sh[32];
     const uint16_t *lg = logits + (size_t)blockIdx.x * stride;
     uint64_t best = 0;  // below every real value; index 0 wins if nothing compares greater than -inf
@@ -129,6 +135,8 @@ __global__ void local_pair_kernel(const uint16_t *__restrict__ logits, uint32_t 
 }
 __global__ void final_pair_kernel(const uint64_t *__restrict__ pairs, uint32_t batch, int T,
                                   uint32_t *__restrict__ next) {
+    pdl_launch_dependents();
+    pdl_wait();
     uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= batch) return;
     uint64_t best = 0;
@@ -211,7 +219,7 @@ static int enqueue_step(prism_cuda_engine *e) {
         if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, to, nullptr, e->att, e->qd_l, (uint16_t *)e->part, H, nullptr, B));
             PRISM_TRY(tp_all_reduce_f32(ctx, e->part, (size_t)B * H));
-            round_add_resid_kernel<<<(B * H + 255) / 256, 256, 0, ctx->stream>>>(e->part, e->h, B * H);
+            launch_pdl(ctx, "round_add_resid_kernel", round_add_resid_kernel, (B * H + 255) / 256, 256, 0, e->part, e->h, B * H);
             PRISM_TRY(after_launch(ctx, "round_add_resid_kernel"));
         } else if (fused) {
             PRISM_TRY(linear(e, GEMV_RESID, to, nullptr, e->att, e->qd_l, e->h, H, e->h, B));
@@ -232,7 +240,7 @@ static int enqueue_step(prism_cuda_engine *e) {
         if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, td, nullptr, e->act, e->act_stride, (uint16_t *)e->part, H, nullptr, B));
             PRISM_TRY(tp_all_reduce_f32(ctx, e->part, (size_t)B * H));
-            round_add_resid_kernel<<<(B * H + 255) / 256, 256, 0, ctx->stream>>>(e->part, e->h, B * H);
+            launch_pdl(ctx, "round_add_resid_kernel", round_add_resid_kernel, (B * H + 255) / 256, 256, 0, e->part, e->h, B * H);
             PRISM_TRY(after_launch(ctx, "round_add_resid_kernel"));
         } else if (fused) {
             PRISM_TRY(linear(e, GEMV_RESID, td, nullptr, e->act, e->act_stride, e->h, H, e->h, B));
@@ -254,15 +262,15 @@ static int enqueue_step(prism_cuda_engine *e) {
         PRISM_TRY(linear(e, GEMV_PLAIN, head, nullptr, e->xn, H, e->logits, lstride, nullptr, B));
     }
     if (tp) {
-        local_pair_kernel<<<B, 1024, 0, ctx->stream>>>(e->logits, e->V_l, lstride, e->v0, e->pairs_send);
+        launch_pdl(ctx, "local_pair_kernel", local_pair_kernel, B, 1024, 0, e->logits, e->V_l, lstride, e->v0, e->pairs_send);
         PRISM_TRY(after_launch(ctx, "local_pair_kernel"));
         PRISM_TRY(tp_all_gather_bytes(ctx, e->pairs_send, e->pairs_recv, (size_t)B * 8));
-        final_pair_kernel<<<(B + 63) / 64, 64, 0, ctx->stream>>>(e->pairs_recv, B, e->T, e->next);
+        launch_pdl(ctx, "final_pair_kernel", final_pair_kernel, (B + 63) / 64, 64, 0, e->pairs_recv, B, e->T, e->next);
         PRISM_TRY(after_launch(ctx, "final_pair_kernel"));
     } else {
         PRISM_TRY(launch_argmax(ctx, e->logits, e->V_l, lstride, B, e->next));
     }
-    advance_kernel<<<1, 64, 0, ctx->stream>>>(e->scalars, e->next, e->tok, e->out_tokens, B, e->out_cap);
+    launch_pdl(ctx, "advance_kernel", advance_kernel, 1, 64, 0, e->scalars, e->next, e->tok, e->out_tokens, B, e->out_cap);
     return after_launch(ctx, "advance_kernel");
 }
 

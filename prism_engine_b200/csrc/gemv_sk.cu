@@ -1,0 +1,542 @@
+// Palettized GEMV, persistent "stream-K" form of the pair-table tensor-core kernel.
+//
+// y = W x with W stored as 4-bit palette indices + a 16-entry fp16 palette per row
+// (lut_gemv_cpu, src/lut/cpu_fallback.rs:12-35; fused gate/up: engine_impl.rs FusedGateUp).
+//
+// Work is counted in units of (block, chunk): a block is two half-blocks of 32 rows (64 output
+// rows, or 32 gate + 32 up rows), a chunk is 32 weights (16 index bytes) of every row of the block,
+// i.e. 1 KB of indices.  The U = n_blocks * n_chunks units are laid out block-major and cut into G
+// contiguous, nearly equal ranges, one per CTA, with G = 3 CTAs x SM count: every CTA streams the
+// same number of bytes, so there is no partial last wave.  A range is walked as segments (one
+// block, a run of chunks).  For each segment the CTA builds the block's pair tables in shared
+// memory, stages the matching slice of x, streams the chunks through mma.sync.m16n8k16 and
+// reduces to 64 sums.  A segment that covers a whole block writes its outputs; otherwise the sums
+// go to a partial slot and the CTA that completes the block (arrival counter in chunks) adds the
+// partials in range order, so results do not depend on scheduling.
+#include "common.cuh"
+
+namespace prism {
+
+#ifndef SK_WARPS_N
+#define SK_WARPS_N 8
+#endif
+#ifndef SK_CTAS_N
+#define SK_CTAS_N 3
+#endif
+#ifndef SK_NACC_N
+#define SK_NACC_N 2
+#endif
+constexpr int SK_WARPS = SK_WARPS_N;
+constexpr int SK_CTAS_PER_SM = SK_CTAS_N;
+constexpr int SK_NACC = SK_NACC_N;        // independent accumulator sets (2 or 4)
+constexpr int SK_THREADS = SK_WARPS * 32;
+constexpr int SK_TBL_BYTES = 256 * 256;   // 256 entries x (2 half-blocks x 32 lanes x 4 B)
+constexpr int SK_PIECE_CHUNKS = SK_WARPS * 16;  // chunks of x staged at a time (8 warps: 4096 halves, 8 KB)
+#ifndef SK_PF_N
+#define SK_PF_N 2
+#endif
+constexpr int SK_PF = SK_PF_N;           // index chunks in flight per warp (divides 16; at most 6 unrolled)
+constexpr int SK_QUANT = 8;               // segment boundaries fall on multiples of this many chunks
+constexpr int SK_KNOWN_SBASE = 1024;      // dynamic shared memory starts after the 1 KB the driver reserves
+constexpr size_t SK_SMEM_BYTES = SK_TBL_BYTES + SK_PIECE_CHUNKS * 64 + SK_WARPS * 64 * 4 + 32;
+
+// The partition of the U = n_blocks * n_chunks units over G CTAs, in one of two forms.
+//  * stream (s == 0): CTA i starts at i*q + min(i, r) (q = U / G, r = U % G), ranges as equal as
+//    integers allow, G = every resident CTA slot.  For work of many chunks per CTA.
+//  * uniform (s > 0): every block is cut into s equal parts, CTA b*s + k takes part k of block b,
+//    so a CTA never builds more than one table.  For small matrices, where the time is latency.
+// A start that falls inside a block is moved down to a multiple of SK_QUANT chunks, or up to the
+// next block when fewer than SK_QUANT chunks of the block would be left (no segment is shorter
+// than SK_QUANT chunks); with whole_blocks set it is moved down to the start of the block.
+struct SkPart {
+    uint32_t q, r, G, n_chunks, total, s, whole_blocks;
+};
+__host__ __device__ inline uint32_t sk_raw_start(const SkPart &p, uint32_t i) {
+    if (i >= p.G) return p.total;
+    if (p.s) {
+        const uint32_t b = i / p.s, k = i - b * p.s;
+        return b * p.n_chunks + k * p.n_chunks / p.s;
+    }
+    return i * p.q + (i < p.r ? i : p.r);
+}
+// snaps a position given relative to the start of its block (0 <= c < n_chunks)
+__host__ __device__ inline uint32_t sk_snap_rel(const SkPart &p, uint32_t c) {
+    if (p.whole_blocks) return 0;
+    const uint32_t s = c / SK_QUANT * SK_QUANT;
+    return (s > 0 && p.n_chunks - s < (uint32_t)SK_QUANT) ? p.n_chunks : s;
+}
+__host__ __device__ inline uint32_t sk_boundary(const SkPart &p, uint32_t i) {
+    const uint32_t u = sk_raw_start(p, i);
+    if (u >= p.total) return p.total;
+    const uint32_t b = u / p.n_chunks;
+    return b * p.n_chunks + sk_snap_rel(p, u - b * p.n_chunks);
+}
+// Start of CTA i's range clipped to the block [b0, b0 + n_chunks).
+__device__ __forceinline__ uint32_t sk_boundary_in_block(const SkPart &p, uint32_t i, uint32_t b0) {
+    const uint32_t u = sk_raw_start(p, i);
+    if (u <= b0) return b0;                       // starts in an earlier block: snapping never crosses b0
+    if (u >= b0 + p.n_chunks) return b0 + p.n_chunks;
+    return b0 + sk_snap_rel(p, u - b0);
+}
+
+struct SkArgs {
+    const uint8_t *idx1, *idx2;   // index arrays the two half-blocks of a block come from
+    const uint16_t *pal1, *pal2;
+    uint32_t n_chunks;            // chunks per row
+    uint32_t hb_mul, hb_add2;     // block b = half-blocks hb_mul*b (rows "1") and hb_mul*b+hb_add2 (rows "2")
+    uint32_t m;                   // valid output rows (per tensor)
+    uint32_t n_blocks;
+    SkPart part;                  // how the (block, chunk) units are dealt to the CTAs
+    const uint16_t *x; uint32_t x_stride;
+    uint16_t *y; uint32_t y_stride;
+    const uint16_t *resid;
+    float *partials;              // [batch][G][2][64]
+    unsigned int *counters;       // [batch][n_blocks], chunks of the block that have arrived
+    unsigned int *err;
+    uint32_t norm_n;              // > 0: stage rms_norm(x) (row of norm_n values) instead of x
+    float norm_eps;
+};
+
+__device__ __forceinline__ void sk_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int IMM>
+__device__ __forceinline__ uint4 sk_ldg(const uint8_t *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4+%5];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "n"(IMM));
+    return v;
+}
+
+// Shared-memory loads whose address is `register + immediate`.  SBASE is the offset of dynamic
+// shared memory inside the shared window when it is known at compile time (probed once per
+// context): the table base then rides in the immediate field and a lookup costs one byte-permute
+// (offset) and one load.  SBASE < 0 is the portable variant (base added at run time).
+template <int SBASE, int IMM>
+__device__ __forceinline__ uint32_t sk_lds(uint32_t off, uint32_t base) {
+    uint32_t v;
+    if (SBASE >= 0) asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(off), "n"(SBASE >= 0 ? SBASE + IMM : 0));
+    else asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(off + base), "n"(IMM));
+    return v;
+}
+
+// 16 bytes of x for the lanes that hold a non-zero part of the B operand; the other lanes keep
+// what their registers hold (zero, set once before the first chunk).  Predicated-off lanes issue
+// no shared-memory request.
+template <int SBASE, int IMM>
+__device__ __forceinline__ void sk_ldx(uint4 &v, uint32_t off, uint32_t base, uint32_t diag) {
+    if (SBASE >= 0)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t"
+            "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%6];\n\t}\n"
+            : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+            : "r"(off), "r"(diag), "n"(SBASE >= 0 ? SBASE + IMM : 0));
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t"
+            "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%6];\n\t}\n"
+            : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+            : "r"(off + base), "r"(diag), "n"(IMM));
+}
+
+// The eight table lookups of one 32-bit index word per half-block (= two tensor-core steps).
+// byte j of the word -> (byte << 8) | lane*4: offset of table entry `byte` in this lane's bank.
+template <int SBASE>
+__device__ __forceinline__ void sk_lookup(uint32_t (&A)[8], uint32_t w1, uint32_t w2, uint32_t lane_off, uint32_t base) {
+    const uint32_t o10 = __byte_perm(w1, lane_off, 0x7704), o11 = __byte_perm(w1, lane_off, 0x7714);
+    const uint32_t o12 = __byte_perm(w1, lane_off, 0x7724), o13 = __byte_perm(w1, lane_off, 0x7734);
+    const uint32_t o20 = __byte_perm(w2, lane_off, 0x7704), o21 = __byte_perm(w2, lane_off, 0x7714);
+    const uint32_t o22 = __byte_perm(w2, lane_off, 0x7724), o23 = __byte_perm(w2, lane_off, 0x7734);
+    A[0] = sk_lds<SBASE, 0>(o10, base);   A[1] = sk_lds<SBASE, 128>(o20, base);
+    A[2] = sk_lds<SBASE, 0>(o11, base);   A[3] = sk_lds<SBASE, 128>(o21, base);
+    A[4] = sk_lds<SBASE, 0>(o12, base);   A[5] = sk_lds<SBASE, 128>(o22, base);
+    A[6] = sk_lds<SBASE, 0>(o13, base);   A[7] = sk_lds<SBASE, 128>(o23, base);
+}
+
+// One 32-weight chunk of the two half-blocks: 8 tensor-core steps of 4 k each.  The MMA's 16 x 16
+// A operand is read as "row g = lanes 4g..4g+3, each lane two k-pairs of its own weight row"
+// (rows g: half-block 1, rows g+8: half-block 2), and B carries x[k..k+3] only where its k-rows
+// meet the column of the same lane (lanes 0, 5, 10, 15), so accumulator column n of MMA row g is
+// the dot product of lane (g, n).  x_off is the byte offset of the chunk's 64 bytes of x inside
+// the staged piece.  Lookups of word h+1 are issued before the tensor-core steps of word h; once
+// the last word's lookups are out, w1/w2 are dead and the chunk PF steps ahead is loaded into them.
+template <int SBASE, int NEXT_IMM>
+__device__ __forceinline__ void sk_chunk(float (&acc)[SK_NACC][4], uint4 &w1, uint4 &w2, uint4 (&xb)[2], uint32_t lane_off,
+                                         uint32_t x_off, uint32_t diag, uint32_t base, const uint8_t *n1,
+                                         uint64_t delta2, bool more) {
+    sk_ldx<SBASE, SK_TBL_BYTES + 0>(xb[0], x_off, base, diag);
+    sk_ldx<SBASE, SK_TBL_BYTES + 16>(xb[1], x_off, base, diag);
+    uint32_t A0[8], A1[8];
+    sk_lookup<SBASE>(A0, w1.x, w2.x, lane_off, base);
+    sk_lookup<SBASE>(A1, w1.y, w2.y, lane_off, base);
+    constexpr int H = SK_NACC == 4 ? 2 : 0;  // second pair of accumulator sets
+    sk_mma(acc[0], A0[0], A0[1], A0[2], A0[3], xb[0].x, xb[0].y);
+    sk_mma(acc[1], A0[4], A0[5], A0[6], A0[7], xb[0].z, xb[0].w);
+    sk_ldx<SBASE, SK_TBL_BYTES + 32>(xb[0], x_off, base, diag);
+    sk_lookup<SBASE>(A0, w1.z, w2.z, lane_off, base);
+    sk_mma(acc[H + 0], A1[0], A1[1], A1[2], A1[3], xb[1].x, xb[1].y);
+    sk_mma(acc[H + 1], A1[4], A1[5], A1[6], A1[7], xb[1].z, xb[1].w);
+    sk_ldx<SBASE, SK_TBL_BYTES + 48>(xb[1], x_off, base, diag);
+    sk_lookup<SBASE>(A1, w1.w, w2.w, lane_off, base);
+    if (more) {
+        w1 = sk_ldg<NEXT_IMM>(n1);
+        w2 = sk_ldg<NEXT_IMM>(n1 + delta2);
+    }
+    sk_mma(acc[0], A0[0], A0[1], A0[2], A0[3], xb[0].x, xb[0].y);
+    sk_mma(acc[1], A0[4], A0[5], A0[6], A0[7], xb[0].z, xb[0].w);
+    sk_mma(acc[H + 0], A1[0], A1[1], A1[2], A1[3], xb[1].x, xb[1].y);
+    sk_mma(acc[H + 1], A1[4], A1[5], A1[6], A1[7], xb[1].z, xb[1].w);
+}
+
+template <int MODE, int SBASE>
+__global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel(const SkArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    if (SBASE >= 0 && smem_base != (uint32_t)SBASE) {  // layout assumption broken: refuse to compute
+        if (threadIdx.x == 0) atomicExch(a.err, 1u);
+        return;
+    }
+    uint32_t *tbl = reinterpret_cast<uint32_t *>(smem);
+    uint16_t *xs = reinterpret_cast<uint16_t *>(smem + SK_TBL_BYTES);
+    float *red = reinterpret_cast<float *>(smem + SK_TBL_BYTES + SK_PIECE_CHUNKS * 64);  // [SK_WARPS][64]
+    unsigned int &s_last = *reinterpret_cast<unsigned int *>(red + SK_WARPS * 64);
+    float &s_inv = *reinterpret_cast<float *>(red + SK_WARPS * 64 + 1);
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t cta = blockIdx.x, G = gridDim.x, bat = blockIdx.y;
+    const uint32_t nc = a.n_chunks;
+    const uint32_t u_begin = sk_boundary(a.part, cta);
+    const uint32_t u_end = sk_boundary(a.part, cta + 1);
+    pdl_launch_dependents();
+    if (u_begin >= u_end) return;
+    const uint16_t *xrow = a.x + (size_t)bat * a.x_stride;
+    const uint32_t lane_off = lane * 4;
+    const uint32_t diag = ((lane >> 2) == (lane & 3)) ? 1u : 0u;  // lanes 0, 5, 10, 15
+    uint4 xb[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+
+    float inv = 1.0f;
+    bool waited = false;
+
+    for (uint32_t u = u_begin; u < u_end;) {
+        const uint32_t blk = u / nc;
+        const uint32_t cb = u - blk * nc;
+        const uint32_t ce = min(nc, cb + (u_end - u));
+        u += ce - cb;
+        const uint32_t hb1 = a.hb_mul * blk, hb2 = hb1 + a.hb_add2;
+
+        // ---- first index chunks of this warp: in flight while the tables are built ---------------
+        // warp w handles chunks cb + w + 8j, j < nj
+        const uint32_t span = ce - cb;
+        const uint32_t nj = span > warp ? (span - warp + SK_WARPS - 1) / SK_WARPS : 0;
+        const uint8_t *p1 = a.idx1 + ((size_t)hb1 * nc + cb + warp) * 512 + lane * 16;
+        const uint8_t *p2 = a.idx2 + ((size_t)hb2 * nc + cb + warp) * 512 + lane * 16;
+        const uint64_t delta2 = (uint64_t)(reinterpret_cast<uintptr_t>(p2) - reinterpret_cast<uintptr_t>(p1));
+        uint4 q1[SK_PF], q2[SK_PF];
+#pragma unroll
+        for (int i = 0; i < SK_PF; i++) {
+            if ((uint32_t)i < nj) {
+                q1[i] = sk_ldg<0>(p1 + (size_t)i * SK_WARPS * 512);
+                q2[i] = sk_ldg<0>(p2 + (size_t)i * SK_WARPS * 512);
+            }
+        }
+
+        __syncthreads();  // the previous segment is done with the tables, x and the reduction buffer
+        // ---- pair tables: entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]} ------------------------
+        // warp w writes the entries with hi = w, w + SK_WARPS, ...; lane L writes its own bank.
+#pragma unroll
+        for (int t = 0; t < 2; t++) {
+            const uint32_t row = (t == 0 ? hb1 : hb2) * 32 + lane;
+            const uint16_t *prow = (t == 0 ? a.pal1 : a.pal2) + (size_t)row * 16;
+            const uint4 p0 = *reinterpret_cast<const uint4 *>(prow);
+            const uint4 pp = *reinterpret_cast<const uint4 *>(prow + 8);
+            const uint32_t cbp[8] = {p0.x, p0.y, p0.z, p0.w, pp.x, pp.y, pp.z, pp.w};
+            for (uint32_t hi = warp; hi < 16; hi += SK_WARPS) {
+                const uint32_t hi_pair = reinterpret_cast<const uint32_t *>(prow)[hi >> 1];  // {pal[hi&~1], pal[hi|1]}
+                const uint32_t hsel = (hi & 1) ? 0x7600u : 0x5400u;
+#pragma unroll
+                for (int lo = 0; lo < 16; lo++) {
+                    const uint32_t v = __byte_perm(cbp[lo >> 1], hi_pair, hsel | ((lo & 1) ? 0x32u : 0x10u));
+                    tbl[((uint32_t)lo + 16u * hi) * 64 + t * 32 + lane] = v;
+                }
+            }
+        }
+
+        if (!waited) {
+            // Everything above reads only weights.  x, the partial sums, the counters and y belong to
+            // the stream order: wait for the kernels before this one.
+            pdl_wait();
+            waited = true;
+            // RMSNorm folded into the staging (rms_norm_inplace, src/lut/cpu_fallback.rs:39-54): every CTA
+            // sums the squares of the whole row once (a few KB from L2) and scales the slices it stages.
+            if (a.norm_n) {
+                const uint4 *xr = reinterpret_cast<const uint4 *>(xrow);
+                float ss = 0.0f;
+                for (uint32_t i = tid; i < a.norm_n / 8; i += SK_THREADS) {
+                    const uint4 v = xr[i];
+                    const __half2 *hp = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float2 f = __half22float2(hp[e]);
+                        ss += f.x * f.x + f.y * f.y;
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                if (lane == 0) red[warp] = ss;
+                __syncthreads();
+                if (tid == 0) {
+                    float tot = 0.0f;
+                    for (int w = 0; w < SK_WARPS; w++) tot += red[w];  // fixed order: the same value in every CTA
+                    s_inv = 1.0f / sqrtf(tot / (float)a.norm_n + a.norm_eps);
+                }
+                __syncthreads();
+                inv = s_inv;
+            }
+        }
+
+        float acc[SK_NACC][4];
+#pragma unroll
+        for (int i = 0; i < SK_NACC; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        uint32_t j = 0;
+        for (uint32_t pb = cb; pb < ce; pb += SK_PIECE_CHUNKS) {
+            // ---- stage this piece of x (fp16, normalised on the way if asked) --------------------
+            if (pb != cb) __syncthreads();  // every warp has finished reading the previous piece
+            {
+                const uint32_t n16 = (min(ce, pb + SK_PIECE_CHUNKS) - pb) * 4;  // 16-byte units
+                const uint4 *xg = reinterpret_cast<const uint4 *>(xrow + (size_t)pb * 32);
+                uint4 *xd = reinterpret_cast<uint4 *>(xs);
+                if (a.norm_n == 0) {
+                    for (uint32_t i = tid; i < n16; i += SK_THREADS) xd[i] = xg[i];
+                } else {
+                    for (uint32_t i = tid; i < n16; i += SK_THREADS) {
+                        uint4 v = xg[i];
+                        __half2 *hp = reinterpret_cast<__half2 *>(&v);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float2 f = __half22float2(hp[e]);
+                            hp[e] = __floats2half2_rn(f.x * inv, f.y * inv);
+                        }
+                        xd[i] = v;
+                    }
+                }
+            }
+            __syncthreads();
+            // ---- stream this warp's chunks of the piece: 16 per full piece ------------------------
+            const uint32_t j_end = min(nj, j + SK_PIECE_CHUNKS / SK_WARPS);
+            uint32_t x_off = warp * 64;
+            const uint8_t *n1 = p1 + (size_t)(j + SK_PF) * SK_WARPS * 512;
+#define SK_STEP(I)                                                                                              \
+    if ((I) < SK_PF && ((I) == 0 || j + (I) < j_end))                                                           \
+        sk_chunk<SBASE, (I) * SK_WARPS * 512>(acc, q1[(I) % SK_PF], q2[(I) % SK_PF], xb, lane_off,                  \
+                                              x_off + (I) * SK_WARPS * 64, diag, smem_base, n1, delta2,          \
+                                              j + (I) + SK_PF < nj);
+            for (; j < j_end; j += SK_PF) {
+                SK_STEP(0) SK_STEP(1) SK_STEP(2) SK_STEP(3) SK_STEP(4) SK_STEP(5)
+                x_off += SK_PF * SK_WARPS * 64;
+                n1 += (size_t)SK_PF * SK_WARPS * 512;
+            }
+#undef SK_STEP
+            j = j_end;
+        }
+
+        // ---- reduce across warps ---------------------------------------------------------------
+        // accumulator column n = 2q, 2q+1 (q = lane%4) of MMA row g = lane/4 (and g+8): column n is
+        // the dot product of the lane (g, n); only n < 4 is populated.
+        if ((lane & 3) < 2) {
+            const uint32_t r = (lane >> 2) * 4 + (lane & 3) * 2;  // lane index the column belongs to
+            float *rw = red + warp * 64;
+            float c0 = acc[0][0] + acc[1][0], c1 = acc[0][1] + acc[1][1];
+            float c2 = acc[0][2] + acc[1][2], c3 = acc[0][3] + acc[1][3];
+            if (SK_NACC == 4) {
+                c0 += acc[SK_NACC - 2][0] + acc[SK_NACC - 1][0]; c1 += acc[SK_NACC - 2][1] + acc[SK_NACC - 1][1];
+                c2 += acc[SK_NACC - 2][2] + acc[SK_NACC - 1][2]; c3 += acc[SK_NACC - 2][3] + acc[SK_NACC - 1][3];
+            }
+            rw[r] = c0;
+            rw[r + 1] = c1;
+            rw[32 + r] = c2;
+            rw[32 + r + 1] = c3;
+        }
+        __syncthreads();
+        float sum = 0.0f;  // thread tid < 64: rows "1" (tid < 32) or "2", lane tid & 31
+        if (tid < 64) {
+#pragma unroll
+            for (int w = 0; w < SK_WARPS; w++) sum += red[w * 64 + tid];
+        }
+
+        if (span != nc) {
+            // part of a block: leave the sums in this CTA's slot (0: the range starts inside the
+            // block, 1: it starts with the block); whoever completes the block adds the slots in
+            // range order.
+            float *part = a.partials + (size_t)bat * G * 128;
+            if (tid < 64) part[((size_t)cta * 2 + (cb > 0 ? 0 : 1)) * 64 + tid] = sum;
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                unsigned int *ctr = a.counters + (size_t)bat * a.n_blocks + blk;
+                const unsigned int prev = atomicAdd(ctr, span);
+                s_last = (prev + span == nc) ? 1u : 0u;
+                if (s_last) *ctr = 0;  // ready for the next launch on this stream
+            }
+            __syncthreads();
+            if (!s_last) continue;
+            __threadfence();
+            // The contributors of the block are consecutive CTAs.  Thread k works out what CTA
+            // c0 + k left (slot 0: its range starts inside the block, slot 1: it starts with the
+            // block); then 64 threads add the slots in that order, four loads in flight.
+            {
+                const uint32_t b0 = blk * nc, b1 = b0 + nc;
+                const SkPart &p = a.part;
+                // first contributor: the CTA whose unsnapped range holds b0, unless its snapped range ends there
+                uint32_t c0;
+                if (p.s) {
+                    c0 = blk * p.s;
+                } else {
+                    c0 = (b0 < p.r * (p.q + 1)) ? b0 / (p.q + 1) : p.r + (b0 - p.r * (p.q + 1)) / p.q;
+                    if (sk_boundary_in_block(p, c0 + 1, b0) <= b0) c0 += 1;
+                }
+                const uint32_t c = c0 + tid;
+                const uint32_t r0 = c < G ? sk_boundary_in_block(p, c, b0) : b1;
+                const uint32_t r1 = c < G ? sk_boundary_in_block(p, c + 1, b0) : b1;
+                uint32_t *list = reinterpret_cast<uint32_t *>(xs);  // x is not needed any more
+                list[tid] = (r1 > r0) ? (c * 2 + (r0 > b0 ? 0u : 1u)) : 0xFFFFFFFFu;
+                const uint32_t n = (uint32_t)__syncthreads_count(c < G && r0 < b1);
+                // thread (g, t): contributors g, g+4, ... of output t, four loads in flight
+                const uint32_t g = tid >> 6, t = tid & 63;
+                float ps = 0.0f;
+                for (uint32_t k = g; k < n; k += 16) {
+                    float v[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const uint32_t slot = (k + 4 * e < n) ? list[k + 4 * e] : 0xFFFFFFFFu;
+                        v[e] = (slot != 0xFFFFFFFFu) ? __ldcg(part + (size_t)slot * 64 + t) : 0.0f;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; e++) ps += v[e];
+                }
+                red[g * 64 + t] = ps;
+                __syncthreads();
+                if (tid < 64) {
+                    sum = red[tid];
+#pragma unroll
+                    for (int gg = 1; gg < SK_THREADS / 64; gg++) sum += red[gg * 64 + tid];
+                }
+            }
+        }
+
+        // ---- epilogue ---------------------------------------------------------------------------
+        if (MODE == GEMV_SWIGLU) {
+            // rows "1" are gate rows, rows "2" the up rows of the same output index
+            __syncthreads();
+            if (tid < 64) red[tid] = sum;
+            __syncthreads();
+            if (tid < 32) {
+                const uint32_t row = blk * 32 + tid;
+                if (row < a.m) {
+                    const float g = __half2float(__float2half_rn(red[tid]));
+                    const float uu = __half2float(__float2half_rn(red[32 + tid]));
+                    const float s = __half2float(__float2half_rn(g / (1.0f + expf(-g))));
+                    a.y[(size_t)bat * a.y_stride + row] = __half_as_ushort(__float2half_rn(s * uu));
+                }
+            }
+        } else if (tid < 64) {
+            const uint32_t row = ((tid >> 5) ? hb2 : hb1) * 32 + (tid & 31);
+            if (MODE == GEMV_F32) {
+                if (row < a.m) reinterpret_cast<float *>(a.y)[(size_t)bat * a.y_stride + row] = sum;
+            } else if (row < a.m) {
+                __half hv = __float2half_rn(sum);
+                if (MODE == GEMV_RESID) {
+                    const float r = __half2float(__ushort_as_half(a.resid[(size_t)bat * a.y_stride + row]));
+                    hv = __float2half_rn(__half2float(hv) + r);
+                }
+                a.y[(size_t)bat * a.y_stride + row] = __half_as_ushort(hv);
+            }
+        }
+    }
+}
+
+template <int MODE, int SBASE>
+static int launch_sk_v(prism_cuda_ctx *ctx, const SkArgs &a, dim3 grid) {
+    static bool configured[8] = {false};
+    if (!configured[ctx->device & 7]) {
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_sk_kernel<MODE, SBASE>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_BYTES));
+        configured[ctx->device & 7] = true;
+    }
+    launch_pdl(ctx, "lut_gemv_sk_kernel", lut_gemv_sk_kernel<MODE, SBASE>, grid, SK_THREADS, SK_SMEM_BYTES, a);
+    return after_launch(ctx, "lut_gemv_sk_kernel");
+}
+
+template <int MODE>
+static int launch_sk(prism_cuda_ctx *ctx, const SkArgs &a, dim3 grid) {
+    if (ctx->smem_base == SK_KNOWN_SBASE) return launch_sk_v<MODE, SK_KNOWN_SBASE>(ctx, a, grid);
+    return launch_sk_v<MODE, -1>(ctx, a, grid);
+}
+
+bool sk_eligible(const LutTensor &t) { return t.bits == 4 && t.k % 32 == 0 && t.k >= 32; }
+
+// Chooses the partition (see SkPart) for one activation vector of a batch.
+SkPart sk_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch) {
+    SkPart p{};
+    p.n_chunks = n_chunks;
+    p.total = n_blocks * n_chunks;
+    uint32_t slots = (uint32_t)ctx->sm_count * SK_CTAS_PER_SM / (batch ? batch : 1);
+    if (slots == 0) slots = 1;
+    uint32_t min_chunks = ctx->sk_min_chunks > SK_QUANT ? (uint32_t)ctx->sk_min_chunks : (uint32_t)SK_QUANT;
+    if (p.total / slots >= (uint32_t)ctx->sk_stream_chunks && p.total / slots >= (n_chunks + 127) / 128) {
+        p.G = slots;
+        p.q = p.total / p.G;
+        p.r = p.total % p.G;
+        // short rows, several blocks per CTA: whole blocks only (no partial sums, no extra table)
+        p.whole_blocks = (n_chunks <= 64 && p.q >= 3 * n_chunks) ? 1 : 0;
+    } else {
+        uint32_t s = n_chunks / min_chunks;
+        if (s > slots / n_blocks) s = slots / n_blocks;
+        if (s > 8) s = 8;
+        if (s < 1) s = 1;
+        p.s = s;
+        p.G = n_blocks * s;
+    }
+    return p;
+}
+
+int launch_gemv_sk(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
+                   uint32_t x_stride, void *y, uint32_t y_stride, const uint16_t *resid, uint32_t batch,
+                   float norm_eps) {
+    SkArgs a{};
+    a.n_chunks = t.n_chunks;
+    a.m = t.m;
+    a.x = x; a.x_stride = x_stride; a.y = static_cast<uint16_t *>(y); a.y_stride = y_stride; a.resid = resid;
+    a.err = ctx->dev_err;
+    a.norm_n = norm_eps >= 0.0f ? t.k : 0;
+    a.norm_eps = norm_eps >= 0.0f ? norm_eps : 0.0f;
+    if (mode == GEMV_SWIGLU) {
+        a.idx1 = t.idx; a.pal1 = t.pal; a.idx2 = t2->idx; a.pal2 = t2->pal;
+        a.hb_mul = 1; a.hb_add2 = 0;
+        a.n_blocks = t.n_hb;
+    } else {
+        a.idx1 = a.idx2 = t.idx; a.pal1 = a.pal2 = t.pal;
+        a.hb_mul = 2; a.hb_add2 = 1;
+        a.n_blocks = t.n_hb / 2;
+    }
+    a.part = sk_partition(ctx, a.n_blocks, a.n_chunks, batch);
+    const uint32_t G = a.part.G;
+    PRISM_TRY(ensure_splitk(ctx, (size_t)batch * G * 128, (size_t)batch * a.n_blocks));
+    a.partials = ctx->splitk_partials;
+    a.counters = ctx->splitk_counters;
+    const dim3 grid(G, batch);
+    switch (mode) {
+    case GEMV_PLAIN: return launch_sk<GEMV_PLAIN>(ctx, a, grid);
+    case GEMV_RESID: return launch_sk<GEMV_RESID>(ctx, a, grid);
+    case GEMV_F32: return launch_sk<GEMV_F32>(ctx, a, grid);
+    default: return launch_sk<GEMV_SWIGLU>(ctx, a, grid);
+    }
+}
+
+}  // namespace prism

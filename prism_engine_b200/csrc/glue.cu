@@ -48,6 +48,8 @@ __device__ float block_max(float v, float *sh) {
 constexpr int RMS_THREADS = 1024;
 __global__ void __launch_bounds__(RMS_THREADS) rms_norm_kernel(const uint16_t *__restrict__ in,
                                                                uint16_t *__restrict__ out, uint32_t n, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sh[32];
     const uint16_t *x = in + (size_t)blockIdx.x * n;
     uint16_t *y = out + (size_t)blockIdx.x * n;
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(RMS_THREADS) rms_norm_kernel(const uint16_t *_
 
 int launch_rms_norm(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint32_t n, float eps,
                     uint32_t batch) {
-    rms_norm_kernel<<<batch, RMS_THREADS, 0, ctx->stream>>>(in, out, n, eps);
+    launch_pdl(ctx, "rms_norm_kernel", rms_norm_kernel, batch, RMS_THREADS, 0, in, out, n, eps);
     return after_launch(ctx, "rms_norm_kernel");
 }
 
@@ -102,6 +104,8 @@ int launch_rms_norm(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint
 // The position comes from device memory when pos_dev is set (graph replay).
 __global__ void rope_kernel(uint16_t *__restrict__ x, uint32_t n, const int32_t *__restrict__ pos_dev,
                             int64_t pos_host, uint32_t hd, float base, uint32_t x_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t half = hd / 2;
     const uint32_t pairs = (n / hd) * half;
     uint16_t *xb = x + (size_t)blockIdx.y * x_stride;
@@ -122,17 +126,19 @@ int launch_rope(prism_cuda_ctx *ctx, uint16_t *x, uint32_t n, const int32_t *pos
                 uint32_t head_dim, float base, uint32_t batch, uint32_t x_stride) {
     const uint32_t pairs = (n / head_dim) * (head_dim / 2);
     dim3 grid((pairs + 127) / 128, batch);
-    rope_kernel<<<grid, 128, 0, ctx->stream>>>(x, n, pos_dev, pos_host, head_dim, base, x_stride);
+    launch_pdl(ctx, "rope_kernel", rope_kernel, grid, 128, 0, x, n, pos_dev, pos_host, head_dim, base, x_stride);
     return after_launch(ctx, "rope_kernel");
 }
 
 // vec_add_inplace (cpu_fallback.rs:56-62)
 __global__ void vec_add_kernel(uint16_t *__restrict__ a, const uint16_t *__restrict__ b, uint32_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) a[i] = f2h(h2f(a[i]) + h2f(b[i]));
 }
 int launch_vec_add(prism_cuda_ctx *ctx, uint16_t *a, const uint16_t *b, uint32_t n) {
-    vec_add_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(a, b, n);
+    launch_pdl(ctx, "vec_add_kernel", vec_add_kernel, (n + 255) / 256, 256, 0, a, b, n);
     return after_launch(ctx, "vec_add_kernel");
 }
 
@@ -152,6 +158,8 @@ int launch_silu(prism_cuda_ctx *ctx, uint16_t *x, uint32_t n) {
 // Activation arm of step() (engine_impl.rs:1355-1366): g = f16(silu(g)); g = f16(g*u).
 __global__ void silu_mul_kernel(uint16_t *__restrict__ out, const uint16_t *__restrict__ g,
                                 const uint16_t *__restrict__ u, uint32_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         float f = h2f(g[i]);
@@ -160,7 +168,7 @@ __global__ void silu_mul_kernel(uint16_t *__restrict__ out, const uint16_t *__re
     }
 }
 int launch_silu_mul(prism_cuda_ctx *ctx, uint16_t *out, const uint16_t *g, const uint16_t *u, uint32_t n) {
-    silu_mul_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(out, g, u, n);
+    launch_pdl(ctx, "silu_mul_kernel", silu_mul_kernel, (n + 255) / 256, 256, 0, out, g, u, n);
     return after_launch(ctx, "silu_mul_kernel");
 }
 
@@ -186,6 +194,8 @@ int launch_softmax(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint3
 // sequence; rows of `logits` are `stride` apart.
 __global__ void argmax_kernel(const uint16_t *__restrict__ logits, uint32_t n, uint32_t stride,
                               uint32_t *__restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ uint32_t si[32];
     const uint16_t *lg = logits + (size_t)blockIdx.x * stride;
@@ -226,7 +236,7 @@ __global__ void argmax_kernel(const uint16_t *__restrict__ logits, uint32_t n, u
 }
 int launch_argmax(prism_cuda_ctx *ctx, const uint16_t *logits, uint32_t n, uint32_t stride, uint32_t batch,
                   uint32_t *out_dev) {
-    argmax_kernel<<<batch, 1024, 0, ctx->stream>>>(logits, n, stride, out_dev);
+    launch_pdl(ctx, "argmax_kernel", argmax_kernel, batch, 1024, 0, logits, n, stride, out_dev);
     return after_launch(ctx, "argmax_kernel");
 }
 
@@ -235,6 +245,8 @@ int launch_argmax(prism_cuda_ctx *ctx, const uint16_t *logits, uint32_t n, uint3
 // [f32 scale][kvd x i8], scale = 127/max|x| (1 when max <= 1e-10),
 // round-half-away, clamp to [-128,127].
 __global__ void kv_append_kernel(KvAppendArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sh[32];
     const uint32_t b = blockIdx.x, which = blockIdx.y;
     const uint16_t *src = (which ? a.v : a.k) + (size_t)b * a.src_stride;
@@ -265,7 +277,7 @@ __global__ void kv_append_kernel(KvAppendArgs a) {
 }
 int launch_kv_append(prism_cuda_ctx *ctx, const KvAppendArgs &a) {
     dim3 grid(a.batch, 2);
-    kv_append_kernel<<<grid, 128, 0, ctx->stream>>>(a);
+    launch_pdl(ctx, "kv_append_kernel", kv_append_kernel, grid, 128, 0, a);
     return after_launch(ctx, "kv_append_kernel");
 }
 
@@ -287,6 +299,8 @@ __device__ __forceinline__ float kv_load(const void *base, uint32_t int8, uint32
 }
 
 __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(AttnArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float sc[];  // [sl] scores, then exp
     __shared__ float sh[32];
     __shared__ float qs[256];
@@ -344,6 +358,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(AttnArgs a) {
 // all warps of the block.  Partial outputs of the warps are combined in warp order.
 template <int VEC>
 __global__ void __launch_bounds__(ATTN_THREADS) attention_f16_kernel(AttnArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float sc[];  // [sl] scores, then exp
     __shared__ float sh[32];
     __shared__ float part[(ATTN_THREADS / 32) * 32 * VEC];
@@ -447,14 +463,14 @@ int launch_attention(prism_cuda_ctx *ctx, const AttnArgs &a) {
                         (a.seq_stride * 2) % 16 == 0;
     if (vec_ok) {
         switch (a.hd) {
-        case 32: attention_f16_kernel<1><<<grid, ATTN_THREADS, smem, ctx->stream>>>(a); break;
-        case 64: attention_f16_kernel<2><<<grid, ATTN_THREADS, smem, ctx->stream>>>(a); break;
-        case 128: attention_f16_kernel<4><<<grid, ATTN_THREADS, smem, ctx->stream>>>(a); break;
-        default: attention_f16_kernel<8><<<grid, ATTN_THREADS, smem, ctx->stream>>>(a); break;
+        case 32: launch_pdl(ctx, "attention_f16_kernel", attention_f16_kernel<1>, grid, ATTN_THREADS, smem, a); break;
+        case 64: launch_pdl(ctx, "attention_f16_kernel", attention_f16_kernel<2>, grid, ATTN_THREADS, smem, a); break;
+        case 128: launch_pdl(ctx, "attention_f16_kernel", attention_f16_kernel<4>, grid, ATTN_THREADS, smem, a); break;
+        default: launch_pdl(ctx, "attention_f16_kernel", attention_f16_kernel<8>, grid, ATTN_THREADS, smem, a); break;
         }
         return after_launch(ctx, "attention_f16_kernel");
     }
-    attention_kernel<<<grid, ATTN_THREADS, smem, ctx->stream>>>(a);
+    launch_pdl(ctx, "attention_kernel", attention_kernel, grid, ATTN_THREADS, smem, a);
     return after_launch(ctx, "attention_kernel");
 }
 

@@ -155,6 +155,8 @@ __global__ void embed_kernel(const uint8_t *__restrict__ idx, const uint16_t *__
                              uint32_t m, uint32_t k, uint32_t n_chunks,
                              const uint32_t *__restrict__ tokens, uint16_t *__restrict__ out,
                              uint16_t *__restrict__ out2) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr uint32_t NE = 1u << BITS, PER_CHUNK = 128 / BITS, MASK = NE - 1;
     uint32_t b = blockIdx.y;
     uint32_t tok = tokens[b];
@@ -189,9 +191,9 @@ int launch_embed(prism_cuda_ctx *ctx, const LutTensor &t, const uint32_t *tokens
                  uint16_t *out_dev, uint16_t *out2_dev) {
     dim3 grid((t.n_chunks + 63) / 64, batch);
     if (t.bits == 4)
-        embed_kernel<4><<<grid, 64, 0, ctx->stream>>>(t.idx, t.pal, t.m, t.k, t.n_chunks, tokens_dev, out_dev, out2_dev);
+        launch_pdl(ctx, "embed_kernel", embed_kernel<4>, grid, 64, 0, t.idx, t.pal, t.m, t.k, t.n_chunks, tokens_dev, out_dev, out2_dev);
     else
-        embed_kernel<2><<<grid, 64, 0, ctx->stream>>>(t.idx, t.pal, t.m, t.k, t.n_chunks, tokens_dev, out_dev, out2_dev);
+        launch_pdl(ctx, "embed_kernel", embed_kernel<2>, grid, 64, 0, t.idx, t.pal, t.m, t.k, t.n_chunks, tokens_dev, out_dev, out2_dev);
     return after_launch(ctx, "embed_kernel");
 }
 
