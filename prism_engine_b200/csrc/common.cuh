@@ -127,21 +127,39 @@ int after_launch(prism_cuda_ctx *ctx, const char *kernel);
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
+// Launch with a thread-block cluster of `cluster_x` CTAs along x (1: none) and, when the context
+// allows it, the programmatic-dependent-launch attribute.
 template <typename... KArgs, typename... Args>
-inline void launch_pdl(prism_cuda_ctx *ctx, const char *name, void (*kernel)(KArgs...), dim3 grid, dim3 block,
-                      size_t smem, Args &&...args) {
+inline void launch_cluster_pdl(prism_cuda_ctx *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                               unsigned cluster_x, Args &&...args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        n++;
+    }
+    if (ctx->pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = ctx->pdl ? 1 : 0;
-    (void)name;
+    cfg.numAttrs = n;
     (void)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);  // a failure stays in the last-error slot: after_launch() reports it
+}
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(prism_cuda_ctx *ctx, const char *name, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                       size_t smem, Args &&...args) {
+    (void)name;
+    launch_cluster_pdl(ctx, kernel, grid, block, smem, 1u, static_cast<Args &&>(args)...);
 }
 #endif
 
@@ -225,6 +243,13 @@ struct KvAppendArgs {
     uint32_t kvd, batch; uint64_t seq_stride; uint32_t int8; uint32_t max_seq;
 };
 int launch_kv_append(prism_cuda_ctx *ctx, const KvAppendArgs &a);
+
+// attn.cu: RoPE(q), RoPE(k) when rope_k, cache append and attention in one kernel (fp16 cache,
+// head_dim 32/64/128/256).  a.q is this step's (un-rotated) query rows, a.k / a.v the cache of the
+// layer slot, k_src / v_src this step's key/value rows (a.q_stride apart, like a.q).
+bool attn_fused_eligible(const AttnArgs &a);
+int launch_attn_fused(prism_cuda_ctx *ctx, const AttnArgs &a, const uint16_t *k_src, const uint16_t *v_src,
+                      uint32_t rope_k, float rope_base);
 
 }  // namespace prism
 

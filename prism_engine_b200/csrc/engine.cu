@@ -200,7 +200,6 @@ static int enqueue_step(prism_cuda_engine *e) {
             PRISM_TRY(linear(e, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, qs, nullptr, B));
             PRISM_TRY(linear(e, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, qs, nullptr, B));
         }
-        if (c.rope_k) PRISM_TRY(launch_rope(ctx, e->k, e->kvd_l, pos_dev, 0, e->hd, base, B, qs));
         const uint32_t slot_mul = e->guard_skip ? c.num_layers : 1, slot_add = e->guard_skip ? l : 0;
         KvAppendArgs ka{};
         ka.k = e->k; ka.v = e->v; ka.src_stride = qs;
@@ -208,14 +207,20 @@ static int enqueue_step(prism_cuda_engine *e) {
         ka.vc = (char *)e->vc + (size_t)li * e->kv_layer_bytes;
         ka.pos_dev = pos_dev; ka.slot_mul = slot_mul; ka.slot_add = slot_add;
         ka.kvd = e->kvd_l; ka.batch = B; ka.seq_stride = e->kv_seq_stride; ka.int8 = c.kv_int8; ka.max_seq = e->kv_slots;
-        PRISM_TRY(launch_kv_append(ctx, ka));
-        PRISM_TRY(launch_rope(ctx, e->q, e->qd_l, pos_dev, 0, e->hd, base, B, qs));
         AttnArgs aa{};
         aa.q = e->q; aa.q_stride = qs; aa.k = ka.kc; aa.v = ka.vc; aa.out = e->att;
         aa.pos_dev = pos_dev; aa.slot_mul = slot_mul; aa.slot_add = slot_add;
         aa.nh = e->nh_l; aa.nkv = e->nkv_l; aa.hd = e->hd; aa.batch = B;
         aa.seq_stride = e->kv_seq_stride; aa.int8 = c.kv_int8; aa.max_seq = e->kv_slots;
-        PRISM_TRY(launch_attention(ctx, aa));
+        if (fused && attn_fused_eligible(aa)) {
+            // Rope(q), Rope(k), cache append and Attention as one kernel
+            PRISM_TRY(launch_attn_fused(ctx, aa, e->k, e->v, c.rope_k, base));
+        } else {
+            if (c.rope_k) PRISM_TRY(launch_rope(ctx, e->k, e->kvd_l, pos_dev, 0, e->hd, base, B, qs));
+            PRISM_TRY(launch_kv_append(ctx, ka));
+            PRISM_TRY(launch_rope(ctx, e->q, e->qd_l, pos_dev, 0, e->hd, base, B, qs));
+            PRISM_TRY(launch_attention(ctx, aa));
+        }
         if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, to, nullptr, e->att, e->qd_l, (uint16_t *)e->part, H, nullptr, B));
             PRISM_TRY(tp_all_reduce_f32(ctx, e->part, (size_t)B * H));

@@ -35,7 +35,7 @@ constexpr int SK_PIECE_CHUNKS = SK_WARPS * 16;  // chunks of x staged at a time 
 #ifndef SK_PF_N
 #define SK_PF_N 2
 #endif
-constexpr int SK_PF = SK_PF_N;           // index chunks in flight per warp (divides 16; at most 6 unrolled)
+constexpr int SK_PF = SK_PF_N;           // index chunks in flight per warp (1, 2 or 4)
 constexpr int SK_QUANT = 8;               // segment boundaries fall on multiples of this many chunks
 constexpr int SK_KNOWN_SBASE = 1024;      // dynamic shared memory starts after the 1 KB the driver reserves
 constexpr size_t SK_SMEM_BYTES = SK_TBL_BYTES + SK_PIECE_CHUNKS * 64 + SK_WARPS * 64 * 4 + 32;
@@ -114,7 +114,15 @@ __device__ __forceinline__ uint4 sk_ldg(const uint8_t *p) {
                  : "l"(p), "n"(IMM));
     return v;
 }
-
+// Where a warp's index chunks come from: 16 bytes per lane and chunk, lane-contiguous (512 B per
+// half-block and chunk).  `OFF` is in bytes from the warp's current chunk.
+struct SkSrcPtr {
+    const uint8_t *p;   // rows "1", this lane
+    uint64_t d2;        // byte distance to the rows "2" array position
+    template <int OFF> __device__ __forceinline__ uint4 load1() const { return sk_ldg<OFF>(p); }
+    template <int OFF> __device__ __forceinline__ uint4 load2() const { return sk_ldg<OFF>(p + d2); }
+    __device__ __forceinline__ void advance(uint32_t bytes) { p += bytes; }
+};
 // Shared-memory loads whose address is `register + immediate`.  SBASE is the offset of dynamic
 // shared memory inside the shared window when it is known at compile time (probed once per
 // context): the table base then rides in the immediate field and a lookup costs one byte-permute
@@ -167,10 +175,9 @@ __device__ __forceinline__ void sk_lookup(uint32_t (&A)[8], uint32_t w1, uint32_
 // the dot product of lane (g, n).  x_off is the byte offset of the chunk's 64 bytes of x inside
 // the staged piece.  Lookups of word h+1 are issued before the tensor-core steps of word h; once
 // the last word's lookups are out, w1/w2 are dead and the chunk PF steps ahead is loaded into them.
-template <int SBASE, int NEXT_IMM>
+template <int SBASE, int NEXT_IMM, typename SRC>
 __device__ __forceinline__ void sk_chunk(float (&acc)[SK_NACC][4], uint4 &w1, uint4 &w2, uint4 (&xb)[2], uint32_t lane_off,
-                                         uint32_t x_off, uint32_t diag, uint32_t base, const uint8_t *n1,
-                                         uint64_t delta2, bool more) {
+                                         uint32_t x_off, uint32_t diag, uint32_t base, const SRC &next, bool more) {
     sk_ldx<SBASE, SK_TBL_BYTES + 0>(xb[0], x_off, base, diag);
     sk_ldx<SBASE, SK_TBL_BYTES + 16>(xb[1], x_off, base, diag);
     uint32_t A0[8], A1[8];
@@ -186,8 +193,8 @@ __device__ __forceinline__ void sk_chunk(float (&acc)[SK_NACC][4], uint4 &w1, ui
     sk_ldx<SBASE, SK_TBL_BYTES + 48>(xb[1], x_off, base, diag);
     sk_lookup<SBASE>(A1, w1.w, w2.w, lane_off, base);
     if (more) {
-        w1 = sk_ldg<NEXT_IMM>(n1);
-        w2 = sk_ldg<NEXT_IMM>(n1 + delta2);
+        w1 = next.template load1<NEXT_IMM>();
+        w2 = next.template load2<NEXT_IMM>();
     }
     sk_mma(acc[0], A0[0], A0[1], A0[2], A0[3], xb[0].x, xb[0].y);
     sk_mma(acc[1], A0[4], A0[5], A0[6], A0[7], xb[0].z, xb[0].w);
@@ -235,17 +242,16 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
         // warp w handles chunks cb + w + 8j, j < nj
         const uint32_t span = ce - cb;
         const uint32_t nj = span > warp ? (span - warp + SK_WARPS - 1) / SK_WARPS : 0;
-        const uint8_t *p1 = a.idx1 + ((size_t)hb1 * nc + cb + warp) * 512 + lane * 16;
-        const uint8_t *p2 = a.idx2 + ((size_t)hb2 * nc + cb + warp) * 512 + lane * 16;
-        const uint64_t delta2 = (uint64_t)(reinterpret_cast<uintptr_t>(p2) - reinterpret_cast<uintptr_t>(p1));
+        SkSrcPtr src;
+        src.p = a.idx1 + ((size_t)hb1 * nc + cb + warp) * 512 + lane * 16;
+        src.d2 = (uint64_t)(reinterpret_cast<uintptr_t>(a.idx2 + ((size_t)hb2 * nc + cb + warp) * 512 + lane * 16) -
+                            reinterpret_cast<uintptr_t>(src.p));
         uint4 q1[SK_PF], q2[SK_PF];
-#pragma unroll
-        for (int i = 0; i < SK_PF; i++) {
-            if ((uint32_t)i < nj) {
-                q1[i] = sk_ldg<0>(p1 + (size_t)i * SK_WARPS * 512);
-                q2[i] = sk_ldg<0>(p2 + (size_t)i * SK_WARPS * 512);
-            }
-        }
+        if (0 < nj) { q1[0] = src.template load1<0>(); q2[0] = src.template load2<0>(); }
+        if (SK_PF > 1 && 1 < nj) { q1[1 % SK_PF] = src.template load1<1 * SK_WARPS * 512>(); q2[1 % SK_PF] = src.template load2<1 * SK_WARPS * 512>(); }
+        if (SK_PF > 2 && 2 < nj) { q1[2 % SK_PF] = src.template load1<2 * SK_WARPS * 512>(); q2[2 % SK_PF] = src.template load2<2 * SK_WARPS * 512>(); }
+        if (SK_PF > 3 && 3 < nj) { q1[3 % SK_PF] = src.template load1<3 * SK_WARPS * 512>(); q2[3 % SK_PF] = src.template load2<3 * SK_WARPS * 512>(); }
+        src.advance(SK_PF * SK_WARPS * 512);  // from here on: the chunk SK_PF steps ahead
 
         __syncthreads();  // the previous segment is done with the tables, x and the reduction buffer
         // ---- pair tables: entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]} ------------------------
@@ -331,16 +337,15 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
             // ---- stream this warp's chunks of the piece: 16 per full piece ------------------------
             const uint32_t j_end = min(nj, j + SK_PIECE_CHUNKS / SK_WARPS);
             uint32_t x_off = warp * 64;
-            const uint8_t *n1 = p1 + (size_t)(j + SK_PF) * SK_WARPS * 512;
 #define SK_STEP(I)                                                                                              \
     if ((I) < SK_PF && ((I) == 0 || j + (I) < j_end))                                                           \
         sk_chunk<SBASE, (I) * SK_WARPS * 512>(acc, q1[(I) % SK_PF], q2[(I) % SK_PF], xb, lane_off,                  \
-                                              x_off + (I) * SK_WARPS * 64, diag, smem_base, n1, delta2,          \
+                                              x_off + (I) * SK_WARPS * 64, diag, smem_base, src,                 \
                                               j + (I) + SK_PF < nj);
             for (; j < j_end; j += SK_PF) {
-                SK_STEP(0) SK_STEP(1) SK_STEP(2) SK_STEP(3) SK_STEP(4) SK_STEP(5)
+                SK_STEP(0) SK_STEP(1) SK_STEP(2) SK_STEP(3)
                 x_off += SK_PF * SK_WARPS * 64;
-                n1 += (size_t)SK_PF * SK_WARPS * 512;
+                src.advance(SK_PF * SK_WARPS * 512);
             }
 #undef SK_STEP
             j = j_end;
@@ -407,25 +412,28 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
                 uint32_t *list = reinterpret_cast<uint32_t *>(xs);  // x is not needed any more
                 list[tid] = (r1 > r0) ? (c * 2 + (r0 > b0 ? 0u : 1u)) : 0xFFFFFFFFu;
                 const uint32_t n = (uint32_t)__syncthreads_count(c < G && r0 < b1);
-                // thread (g, t): contributors g, g+4, ... of output t, four loads in flight
+                // thread (g, t): contributors g, g+NG, ... of output t, four loads in flight
+                constexpr uint32_t NG = SK_THREADS / 64;
                 const uint32_t g = tid >> 6, t = tid & 63;
-                float ps = 0.0f;
-                for (uint32_t k = g; k < n; k += 16) {
-                    float v[4];
+                if (g < NG) {
+                    float ps = 0.0f;
+                    for (uint32_t k = g; k < n; k += 4 * NG) {
+                        float v[4];
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const uint32_t slot = (k + 4 * e < n) ? list[k + 4 * e] : 0xFFFFFFFFu;
-                        v[e] = (slot != 0xFFFFFFFFu) ? __ldcg(part + (size_t)slot * 64 + t) : 0.0f;
+                        for (int e = 0; e < 4; e++) {
+                            const uint32_t slot = (k + NG * e < n) ? list[k + NG * e] : 0xFFFFFFFFu;
+                            v[e] = (slot != 0xFFFFFFFFu) ? __ldcg(part + (size_t)slot * 64 + t) : 0.0f;
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; e++) ps += v[e];
                     }
-#pragma unroll
-                    for (int e = 0; e < 4; e++) ps += v[e];
+                    red[g * 64 + t] = ps;
                 }
-                red[g * 64 + t] = ps;
                 __syncthreads();
                 if (tid < 64) {
                     sum = red[tid];
 #pragma unroll
-                    for (int gg = 1; gg < SK_THREADS / 64; gg++) sum += red[gg * 64 + tid];
+                    for (uint32_t gg = 1; gg < NG; gg++) sum += red[gg * 64 + tid];
                 }
             }
         }

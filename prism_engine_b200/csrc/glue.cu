@@ -2,7 +2,11 @@
 // src/lut/cpu_fallback.rs:39-143 and of the helpers inside step()
 // (src/lut/engine_impl.rs:1076-1459).  All intermediate math is fp32 and every
 // store rounds to fp16 (RNE) at the same points as the reference.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace prism {
 
@@ -190,53 +194,90 @@ int launch_softmax(prism_cuda_ctx *ctx, const uint16_t *in, uint16_t *out, uint3
 }
 
 // argmax (engine_impl.rs:1448-1459): first index holding the strictly greatest
-// value; NaN never wins; an all-NaN/-inf vector gives 0.  One block per
-// sequence; rows of `logits` are `stride` apart.
-__global__ void argmax_kernel(const uint16_t *__restrict__ logits, uint32_t n, uint32_t stride,
-                              uint32_t *__restrict__ out) {
+// value; NaN never wins; an all-NaN/-inf vector gives 0.  A cluster of ARGMAX_CTAS
+// blocks per sequence: each scans a slice with 16-byte loads, rank 0 merges the
+// slices' winners through distributed shared memory.  Rows of `logits` are
+// `stride` apart and 16-byte aligned.
+constexpr int ARGMAX_CTAS = 8;
+constexpr int ARGMAX_THREADS = 512;
+__device__ __forceinline__ void argmax_take(float &bv, uint32_t &bi, float ov, uint32_t oi) {
+    if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+    }
+}
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const uint16_t *__restrict__ logits, uint32_t n,
+                                                                uint32_t stride, uint32_t *__restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t R = cluster.dim_blocks().x, rank = cluster.block_rank();
     __shared__ float sv[32];
     __shared__ uint32_t si[32];
-    const uint16_t *lg = logits + (size_t)blockIdx.x * stride;
+    __shared__ float win_v;
+    __shared__ uint32_t win_i;
+    const uint32_t seq = blockIdx.x / R;
+    const uint16_t *lg = logits + (size_t)seq * stride;
+    // slice of this block, in groups of 8 values
+    const uint32_t groups = (n + 7) / 8, per = (groups + R - 1) / R;
+    const uint32_t g0 = min(groups, rank * per), g1 = min(groups, g0 + per);
     float bv = -INFINITY;
     uint32_t bi = 0xFFFFFFFFu;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        float f = h2f(lg[i]);
-        if (f > bv) {  // ascending i per thread: keeps the first maximum
-            bv = f;
-            bi = i;
+    for (uint32_t g = g0 + threadIdx.x; g < g1; g += ARGMAX_THREADS) {
+        const uint32_t i0 = g * 8;
+        if (i0 + 8 <= n) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(lg + i0);
+            const uint16_t *e = reinterpret_cast<const uint16_t *>(&v);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const float f = h2f(e[k]);
+                if (f > bv) {  // ascending index per thread: keeps the first maximum
+                    bv = f;
+                    bi = i0 + k;
+                }
+            }
+        } else {
+            for (uint32_t i = i0; i < n; i++) {
+                const float f = h2f(lg[i]);
+                if (f > bv) {
+                    bv = f;
+                    bi = i;
+                }
+            }
         }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
-        uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) {
-            bv = ov;
-            bi = oi;
-        }
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+        const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+        argmax_take(bv, bi, ov, oi);
     }
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = ARGMAX_THREADS >> 5;
     if (lane == 0) {
         sv[warp] = bv;
         si[warp] = bi;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < nw; w++) {
-            if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) {
-                bv = sv[w];
-                bi = si[w];
-            }
-        }
-        if (bi == 0xFFFFFFFFu) bi = 0;
-        out[blockIdx.x] = bi;
+        for (int w = 1; w < nw; w++) argmax_take(bv, bi, sv[w], si[w]);
+        win_v = bv;
+        win_i = bi;
     }
+    cluster.sync();
+    if (rank == 0 && threadIdx.x == 0) {
+        for (uint32_t r = 1; r < R; r++)
+            argmax_take(bv, bi, *cluster.map_shared_rank(&win_v, r), *cluster.map_shared_rank(&win_i, r));
+        if (bi == 0xFFFFFFFFu) bi = 0;
+        out[seq] = bi;
+    }
+    cluster.sync();  // peers keep their shared memory alive until rank 0 has read it
 }
 int launch_argmax(prism_cuda_ctx *ctx, const uint16_t *logits, uint32_t n, uint32_t stride, uint32_t batch,
                   uint32_t *out_dev) {
-    launch_pdl(ctx, "argmax_kernel", argmax_kernel, batch, 1024, 0, logits, n, stride, out_dev);
+    if ((reinterpret_cast<uintptr_t>(logits) & 15) || (batch > 1 && stride % 8))
+        return fail(ctx, PRISM_E_ARG, "argmax: rows must be 16-byte aligned");
+    launch_cluster_pdl(ctx, argmax_kernel, dim3(ARGMAX_CTAS * batch), dim3(ARGMAX_THREADS), 0, ARGMAX_CTAS, logits, n,
+                       stride, out_dev);
     return after_launch(ctx, "argmax_kernel");
 }
 
