@@ -57,9 +57,11 @@ const char *prism_cuda_last_error(prism_cuda_ctx *ctx);
 /* The CUDA stream (cudaStream_t) the context launches on. */
 void *prism_cuda_stream(prism_cuda_ctx *ctx);
 int prism_cuda_synchronize(prism_cuda_ctx *ctx);
-/* Tunables: "gemv_variant" (0 = plain CUDA-core kernel, 1 = persistent stream-K pair-table
- * mma.sync kernel, default, 2 = pair-table tcgen05/TMEM kernel, 3 = the pair-table mma.sync
- * kernel on a (block, K split) grid), "gemm_variant" (1 = tcgen05/TMEM
+/* Tunables: "gemv_variant" (0 = plain CUDA-core kernel; 1 = default: pair-table mma.sync kernels,
+ * the warp-specialised persistent one for large matrices and the stream-K one for small;
+ * 2 = pair-table tcgen05/TMEM kernel where eligible; 3 = the pair-table mma.sync kernel on a
+ * (block, K split) grid; 4 / 5 = the warp-specialised / the stream-K kernel for every shape),
+ * "gemm_variant" (1 = tcgen05/TMEM
  * prefill GEMM, default; 0 = activation rows through the GEMV kernel), "fuse" (0/1,
  * default 1: fused epilogues), "pdl" (0/1, default 1: programmatic dependent launch between
  * the kernels of a decode step, so a kernel's weight-only prologue overlaps its predecessor),

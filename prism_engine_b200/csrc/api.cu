@@ -214,7 +214,7 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx) {
 int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
     if (!ctx || !key) return PRISM_E_NULL;
     if (!strcmp(key, "gemv_variant")) {
-        if (value < 0 || value > 3) return fail(ctx, PRISM_E_ARG, "gemv_variant must be 0, 1, 2 or 3");
+        if (value < 0 || value > 5) return fail(ctx, PRISM_E_ARG, "gemv_variant must be 0..5");
         ctx->gemv_variant = (int)value;
     } else if (!strcmp(key, "gemm_variant")) {
         if (value != 0 && value != 1) return fail(ctx, PRISM_E_ARG, "gemm_variant must be 0 or 1");

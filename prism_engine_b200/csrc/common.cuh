@@ -201,6 +201,14 @@ int launch_gemv_sk(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const
                    uint32_t x_stride, void *y, uint32_t y_stride, const uint16_t *resid, uint32_t batch,
                    float norm_eps);
 
+// gemv_ws.cu: warp-specialised persistent form (one CTA per SM; builder warps prepare tables and x
+// while compute warps stream), same arguments as launch_gemv_sk
+bool ws_eligible(const LutTensor &t);
+bool ws_preferred(prism_cuda_ctx *ctx, const LutTensor &t, bool swiglu, uint32_t batch);
+int launch_gemv_ws(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
+                   uint32_t x_stride, void *y, uint32_t y_stride, const uint16_t *resid, uint32_t batch,
+                   float norm_eps);
+
 // gemv_tc5.cu: tcgen05/TMEM GEMV (4-bit, K % 32 == 0, one activation vector)
 bool tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t batch);
 int launch_gemv_tc5(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,

@@ -436,12 +436,17 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
     // a caller may ask for RMSNorm of x to be folded in (engine: the Norm node in front of a matmul)
     const float norm_eps = ctx->pending_norm_eps;
     ctx->pending_norm_eps = -1.0f;
-    // variant 1: persistent stream-K kernel; 2: tcgen05 kernel where eligible, else as 1;
-    // 3: the same tensor-core inner loop on a (block, K split) grid; 0: plain kernel
-    const bool use_tc5 = ctx->gemv_variant == 2 && tc5_eligible(ctx, t, batch);
-    const bool use_sk = !use_tc5 && (ctx->gemv_variant == 1 || ctx->gemv_variant == 2) && sk_eligible(t);
+    // variant 1 (default): the warp-specialised persistent kernel for large matrices, the stream-K
+    // kernel for small ones; 2: tcgen05 kernel where eligible, else as 1; 3: the same tensor-core
+    // inner loop on a (block, K split) grid; 4: warp-specialised kernel for every shape;
+    // 5: stream-K kernel for every shape; 0: plain kernel
+    const int v = ctx->gemv_variant;
+    const bool use_tc5 = v == 2 && tc5_eligible(ctx, t, batch);
+    const bool use_ws = !use_tc5 && ((v == 4 && ws_eligible(t)) ||
+                                     ((v == 1 || v == 2) && ws_preferred(ctx, t, mode == GEMV_SWIGLU, batch)));
+    const bool use_sk = !use_tc5 && !use_ws && (v == 1 || v == 2 || v == 5) && sk_eligible(t);
     const bool use_mma = !use_tc5 && ctx->gemv_variant == 3 && mma_eligible(t);
-    if (norm_eps >= 0.0f && !((use_mma || use_sk) && t.k % 8 == 0 && x_stride >= t.k)) {
+    if (norm_eps >= 0.0f && !((use_mma || use_sk || use_ws) && t.k % 8 == 0 && x_stride >= t.k)) {
         // this kernel choice cannot fold the norm: run it as its own kernel into scratch
         PRISM_TRY(ensure_act(ctx, (size_t)batch * x_stride + 64));
         uint16_t *xn = ctx->act_scratch;
@@ -450,6 +455,7 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
         return launch_gemv(ctx, mode, t, t2, xn, x_stride, y, y_stride, resid, batch);
     }
     if (use_tc5) return launch_gemv_tc5(ctx, mode, t, t2, x, y, resid);
+    if (use_ws) return launch_gemv_ws(ctx, mode, t, t2, x, x_stride, y, y_stride, resid, batch, norm_eps);
     if (use_sk) return launch_gemv_sk(ctx, mode, t, t2, x, x_stride, y, y_stride, resid, batch, norm_eps);
     if (!use_mma) {
         // plain kernel + separate elementwise kernels keep the same rounding points

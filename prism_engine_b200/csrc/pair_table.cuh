@@ -1,0 +1,140 @@
+// Pieces shared by the pair-table tensor-core GEMV kernels: the partition of the work over CTAs,
+// and the device helpers of the inner loop (table lookups, x fragments, mma.sync).
+#pragma once
+
+#include "common.cuh"
+
+namespace prism {
+
+constexpr int SK_QUANT = 8;  // segment boundaries fall on multiples of this many chunks
+
+// The partition of the U = n_blocks * n_chunks units over G CTAs, in one of two forms.
+//  * stream (s == 0): CTA i starts at i*q + min(i, r) (q = U / G, r = U % G), ranges as equal as
+//    integers allow, G = every resident CTA slot.  For work of many chunks per CTA.
+//  * uniform (s > 0): every block is cut into s equal parts, CTA b*s + k takes part k of block b,
+//    so a CTA never builds more than one table.  For small matrices, where the time is latency.
+// A start that falls inside a block is moved down to a multiple of SK_QUANT chunks, or up to the
+// next block when fewer than SK_QUANT chunks of the block would be left (no segment is shorter
+// than SK_QUANT chunks); with whole_blocks set it is moved down to the start of the block.
+struct SkPart {
+    uint32_t q, r, G, n_chunks, total, s, whole_blocks;
+};
+__host__ __device__ inline uint32_t sk_raw_start(const SkPart &p, uint32_t i) {
+    if (i >= p.G) return p.total;
+    if (p.s) {
+        const uint32_t b = i / p.s, k = i - b * p.s;
+        return b * p.n_chunks + k * p.n_chunks / p.s;
+    }
+    return i * p.q + (i < p.r ? i : p.r);
+}
+// snaps a position given relative to the start of its block (0 <= c < n_chunks)
+__host__ __device__ inline uint32_t sk_snap_rel(const SkPart &p, uint32_t c) {
+    if (p.whole_blocks) return 0;
+    const uint32_t s = c / SK_QUANT * SK_QUANT;
+    return (s > 0 && p.n_chunks - s < (uint32_t)SK_QUANT) ? p.n_chunks : s;
+}
+__host__ __device__ inline uint32_t sk_boundary(const SkPart &p, uint32_t i) {
+    const uint32_t u = sk_raw_start(p, i);
+    if (u >= p.total) return p.total;
+    const uint32_t b = u / p.n_chunks;
+    return b * p.n_chunks + sk_snap_rel(p, u - b * p.n_chunks);
+}
+// Start of CTA i's range clipped to the block [b0, b0 + n_chunks).
+__device__ __forceinline__ uint32_t sk_boundary_in_block(const SkPart &p, uint32_t i, uint32_t b0) {
+    const uint32_t u = sk_raw_start(p, i);
+    if (u <= b0) return b0;                       // starts in an earlier block: snapping never crosses b0
+    if (u >= b0 + p.n_chunks) return b0 + p.n_chunks;
+    return b0 + sk_snap_rel(p, u - b0);
+}
+
+struct SkArgs {
+    const uint8_t *idx1, *idx2;   // index arrays the two half-blocks of a block come from
+    const uint16_t *pal1, *pal2;
+    uint32_t n_chunks;            // chunks per row
+    uint32_t hb_mul, hb_add2;     // block b = half-blocks hb_mul*b (rows "1") and hb_mul*b+hb_add2 (rows "2")
+    uint32_t m;                   // valid output rows (per tensor)
+    uint32_t n_blocks;
+    SkPart part;                  // how the (block, chunk) units are dealt to the CTAs
+    const uint16_t *x; uint32_t x_stride;
+    uint16_t *y; uint32_t y_stride;
+    const uint16_t *resid;
+    float *partials;              // [batch][G][2][64]
+    unsigned int *counters;       // [batch][n_blocks], chunks of the block that have arrived
+    unsigned int *err;
+    uint32_t norm_n;              // > 0: stage rms_norm(x) (row of norm_n values) instead of x
+    float norm_eps;
+};
+
+__device__ __forceinline__ void sk_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int IMM>
+__device__ __forceinline__ uint4 sk_ldg(const uint8_t *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4+%5];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "n"(IMM));
+    return v;
+}
+// Where a warp's index chunks come from: 16 bytes per lane and chunk, lane-contiguous (512 B per
+// half-block and chunk).  `OFF` is in bytes from the warp's current chunk.
+struct SkSrcPtr {
+    const uint8_t *p;   // rows "1", this lane
+    uint64_t d2;        // byte distance to the rows "2" array position
+    template <int OFF> __device__ __forceinline__ uint4 load1() const { return sk_ldg<OFF>(p); }
+    template <int OFF> __device__ __forceinline__ uint4 load2() const { return sk_ldg<OFF>(p + d2); }
+    __device__ __forceinline__ void advance(uint32_t bytes) { p += bytes; }
+};
+// Shared-memory loads whose address is `register + immediate`.  SBASE is the offset of dynamic
+// shared memory inside the shared window when it is known at compile time (probed once per
+// context): the table base then rides in the immediate field and a lookup costs one byte-permute
+// (offset) and one load.  SBASE < 0 is the portable variant (base added at run time).
+template <int SBASE, int IMM>
+__device__ __forceinline__ uint32_t sk_lds(uint32_t off, uint32_t base) {
+    uint32_t v;
+    if (SBASE >= 0) asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(off), "n"(SBASE >= 0 ? SBASE + IMM : 0));
+    else asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(off + base), "n"(IMM));
+    return v;
+}
+
+// 16 bytes of x for the lanes that hold a non-zero part of the B operand; the other lanes keep
+// what their registers hold (zero, set once before the first chunk).  Predicated-off lanes issue
+// no shared-memory request.
+template <int SBASE, int IMM>
+__device__ __forceinline__ void sk_ldx(uint4 &v, uint32_t off, uint32_t base, uint32_t diag) {
+    if (SBASE >= 0)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t"
+            "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%6];\n\t}\n"
+            : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+            : "r"(off), "r"(diag), "n"(SBASE >= 0 ? SBASE + IMM : 0));
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t"
+            "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%6];\n\t}\n"
+            : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+            : "r"(off + base), "r"(diag), "n"(IMM));
+}
+
+// The eight table lookups of one 32-bit index word per half-block (= two tensor-core steps).
+// byte j of the word -> (byte << 8) | lane_off: offset of table entry `byte` in this lane's bank;
+// lane_off = lane*4, plus a multiple of 65536 to select one of several tables (its byte 2 is kept).
+template <int SBASE>
+__device__ __forceinline__ void sk_lookup(uint32_t (&A)[8], uint32_t w1, uint32_t w2, uint32_t lane_off, uint32_t base) {
+    const uint32_t o10 = __byte_perm(w1, lane_off, 0x7604), o11 = __byte_perm(w1, lane_off, 0x7614);
+    const uint32_t o12 = __byte_perm(w1, lane_off, 0x7624), o13 = __byte_perm(w1, lane_off, 0x7634);
+    const uint32_t o20 = __byte_perm(w2, lane_off, 0x7604), o21 = __byte_perm(w2, lane_off, 0x7614);
+    const uint32_t o22 = __byte_perm(w2, lane_off, 0x7624), o23 = __byte_perm(w2, lane_off, 0x7634);
+    A[0] = sk_lds<SBASE, 0>(o10, base);   A[1] = sk_lds<SBASE, 128>(o20, base);
+    A[2] = sk_lds<SBASE, 0>(o11, base);   A[3] = sk_lds<SBASE, 128>(o21, base);
+    A[4] = sk_lds<SBASE, 0>(o12, base);   A[5] = sk_lds<SBASE, 128>(o22, base);
+    A[6] = sk_lds<SBASE, 0>(o13, base);   A[7] = sk_lds<SBASE, 128>(o23, base);
+}
+
+}  // namespace prism

@@ -64,7 +64,7 @@ def run_parity(oracle, cfg_dict, profile, n_prompt, max_new, seed, max_seq=256, 
 
 
 @pytest.mark.parametrize("profile", ["baseline", "reference_cpu"])
-@pytest.mark.parametrize("variant,fuse", [(2, 1), (1, 1), (0, 0), (0, 1)])
+@pytest.mark.parametrize("variant,fuse", [(2, 1), (1, 1), (0, 0), (0, 1), (4, 1)])
 def test_tiny_model_token_parity(oracle, profile, variant, fuse):
     got, want, margins = run_parity(oracle, TINY, profile, n_prompt=9, max_new=40, seed=3, variant=variant, fuse=fuse)
     assert np.array_equal(got, want)

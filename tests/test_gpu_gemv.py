@@ -18,7 +18,7 @@ GEMV_SHAPES = [(64, 32), (33, 64), (100, 96), (4864, 896), (896, 4864), (128, 89
                (640, 29568), (20000, 512), (9000, 1312)]
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4, 5])
 @pytest.mark.parametrize("m,k", GEMV_SHAPES)
 def test_gemv_matches_oracle(backend, oracle, variant, m, k):
     backend.set_option("gemv_variant", variant)
@@ -46,7 +46,7 @@ def test_gemv_2bit(backend, oracle, m, k):
     backend.free(h)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4, 5])
 def test_gemv_one_hot_is_exact(backend, oracle, variant):
     """x = e_j picks column j of the dequantised matrix: a single-term sum, so bit-exact at full size."""
     backend.set_option("gemv_variant", variant)
@@ -80,7 +80,7 @@ def test_gemv_linearity_full_size(backend, oracle):
     backend.free(h)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4, 5])
 @pytest.mark.parametrize("hidden,inter", [(64, 96), (896, 4864), (256, 1000 // 8 * 8)])
 def test_fused_gate_up_and_mlp(backend, oracle, variant, hidden, inter):
     backend.set_option("gemv_variant", variant)
