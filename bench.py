@@ -285,7 +285,7 @@ def run_ours(args):
         "config": workload_config(args, arch),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_8tbs_nominal": achieved / 8000.0,
-                     "kernel": "lut_gemv_mma_kernel", "launches_timed": gemv_launches,
+                     "kernel": "lut_gemv_ws_kernel (lut_gemv_sk_kernel for small matrices)", "launches_timed": gemv_launches,
                      "avg_launch_us": gemv_ms * 1e3 / max(gemv_launches, 1),
                      "algorithmic_bytes_per_launch": gemv_bytes / max(gemv_launches, 1),
                      "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE and TRAFFIC_PER_ALGORITHMIC_BYTE * gemv_bytes / max(gemv_launches, 1)},
@@ -318,10 +318,10 @@ def run_ours(args):
     return 0
 
 
-# DRAM bytes per algorithmic byte of lut_gemv_mma_kernel, from the ncu capture summarised in
-# profiles/lut_gemv_mma_kernel_qwen72b_shapes.md (LM-head launch: 3.30 TB/s x 191.9 us = 633 MB of
-# DRAM traffic for 628 MB of algorithmic bytes).
-TRAFFIC_PER_ALGORITHMIC_BYTE = 1.008
+# DRAM bytes per algorithmic byte of the GEMV launches of a 72B decode step, from the ncu capture
+# summarised in profiles/lut_gemv_ws_kernel_qwen72b_shapes.md (the five launch shapes together:
+# 1083.3 MB of DRAM traffic for 1069.8 MB of algorithmic bytes).
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0126
 
 
 def small_shape_bandwidth(be, peak):

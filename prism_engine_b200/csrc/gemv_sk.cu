@@ -254,17 +254,15 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
             // range order.
             float *part = a.partials + (size_t)bat * G * 128;
             if (tid < 64) part[((size_t)cta * 2 + (cb > 0 ? 0 : 1)) * 64 + tid] = sum;
-            __threadfence();
             __syncthreads();
             if (tid == 0) {
                 unsigned int *ctr = a.counters + (size_t)bat * a.n_blocks + blk;
-                const unsigned int prev = atomicAdd(ctr, span);
+                const unsigned int prev = sk_arrive(ctr, span);
                 s_last = (prev + span == nc) ? 1u : 0u;
                 if (s_last) *ctr = 0;  // ready for the next launch on this stream
             }
             __syncthreads();
             if (!s_last) continue;
-            __threadfence();
             // The contributors of the block are consecutive CTAs.  Thread k works out what CTA
             // c0 + k left (slot 0: its range starts inside the block, slot 1: it starts with the
             // block); then 64 threads add the slots in that order, four loads in flight.

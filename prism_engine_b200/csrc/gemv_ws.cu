@@ -36,7 +36,7 @@ constexpr int WS_NB = WS_NB_N;                  // builder warps
 static_assert(WS_NB == 4, "the finish step (scratch sizes, two groups of 64 threads) is written for 128 builder threads");
 constexpr int WS_THREADS = (WS_NC + WS_NB) * 32;
 constexpr int WS_BTHREADS = WS_NB * 32;
-constexpr int WS_PF = WS_PF_N;                  // index chunks in flight per compute warp (1 or 2)
+constexpr int WS_PF = WS_PF_N;                  // index chunks in flight per compute warp (1, 2 or 4)
 constexpr int WS_STAGE_CHUNKS = 256;            // chunks of x per stage (8192 halves, 16 KB)
 constexpr int WS_TBL_BYTES = 65536;             // one pair-table buffer
 constexpr int WS_X_OFF = 2 * WS_TBL_BYTES;      // two x buffers
@@ -47,6 +47,15 @@ constexpr int WS_BAR_OFF = WS_FIN_OFF + 256 * 4;            // full[2], empty[2]
 constexpr size_t WS_SMEM_BYTES = WS_BAR_OFF + 64;
 constexpr int WS_KNOWN_SBASE = 1024;
 constexpr uint32_t WS_WAIT_LIMIT = 1u << 24;    // polls (with back-off) before a wait gives up
+
+#ifdef WS_TIMING
+// Debug builds: per-phase clock stamps of CTA 0 (SM clock cycles since kernel entry).
+__device__ unsigned long long g_ws_timing[16];
+#define WS_STAMP(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_ws_timing[i] = clock64() - g_ws_t0; } while (0)
+__device__ unsigned long long g_ws_t0;
+#else
+#define WS_STAMP(i) do { } while (0)
+#endif
 
 // One stage of a CTA's range.
 struct WsStage {
@@ -159,24 +168,34 @@ __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint3
                             reinterpret_cast<uintptr_t>(src.p));
         // first chunks in flight before the stage's table and x are waited for
         uint4 q1[WS_PF], q2[WS_PF];
-        if (0 < nj) { q1[0] = src.load1<0>(); q2[0] = src.load2<0>(); }
-        if (WS_PF > 1 && 1 < nj) { q1[1 % WS_PF] = src.load1<WS_NC * 512>(); q2[1 % WS_PF] = src.load2<WS_NC * 512>(); }
+#define WS_LOAD(I)                                                              \
+    if ((I) < WS_PF && (I) < nj) {                                              \
+        q1[(I) % WS_PF] = src.load1<((I) % WS_PF) * WS_NC * 512>();             \
+        q2[(I) % WS_PF] = src.load2<((I) % WS_PF) * WS_NC * 512>();             \
+    }
+        WS_LOAD(0) WS_LOAD(1) WS_LOAD(2) WS_LOAD(3)
+#undef WS_LOAD
         src.advance(WS_PF * WS_NC * 512);  // from here on: the chunk WS_PF steps ahead
         if (st.first) {
 #pragma unroll
             for (int i = 0; i < 2; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
         }
+        if (t == 0 && cw == 0) WS_STAMP(4);
         ws_wait(bar_full + 8 * xbuf, par, err_flag);
+        if (t == 0 && cw == 0) WS_STAMP(5);
         const uint32_t lane_off = lane * 4 | (tb << 16);
         uint32_t x_off = xbuf * WS_X_BYTES + cw * 64;
+#define WS_STEP(I)                                                                                            \
+    if ((I) < WS_PF && ((I) == 0 || j + (I) < nj))                                                            \
+        ws_chunk<SBASE, ((I) % WS_PF) * WS_NC * 512>(acc, q1[(I) % WS_PF], q2[(I) % WS_PF], xb, lane_off,         \
+                                                     x_off + ((I) % WS_PF) * WS_NC * 64, diag, smem_base, src, \
+                                                     j + (I) + WS_PF < nj);
         for (uint32_t j = 0; j < nj; j += WS_PF) {
-            ws_chunk<SBASE, 0>(acc, q1[0], q2[0], xb, lane_off, x_off, diag, smem_base, src, j + WS_PF < nj);
-            if (WS_PF > 1 && j + 1 < nj)
-                ws_chunk<SBASE, WS_NC * 512>(acc, q1[1 % WS_PF], q2[1 % WS_PF], xb, lane_off, x_off + WS_NC * 64, diag,
-                                             smem_base, src, j + 1 + WS_PF < nj);
+            WS_STEP(0) WS_STEP(1) WS_STEP(2) WS_STEP(3)
             x_off += WS_PF * WS_NC * 64;
             src.advance(WS_PF * WS_NC * 512);
         }
+#undef WS_STEP
         if (st.last) {
             // accumulator column n = 2q, 2q+1 (q = lane%4) of MMA row g = lane/4 (and g+8): column n is
             // the dot product of the lane (g, n); only n < 4 is populated.
@@ -190,6 +209,7 @@ __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint3
             }
         }
         t5::mbar_arrive(bar_empty + 8 * xbuf);  // every lane: its reads of the buffers and its sums are done
+        if (cw == 0) WS_STAMP(6);  // overwritten every stage: the last one stays
     }
 }
 
@@ -214,17 +234,15 @@ __device__ __forceinline__ void ws_finish(const SkArgs &a, uint8_t *smem, const 
     if (span != nc) {
         float *part = a.partials + (size_t)bat * G * 128;
         if (bt < 64) part[((size_t)cta * 2 + (st.cb > 0 ? 0 : 1)) * 64 + bt] = sum;
-        __threadfence();
         ws_bar_builders();
         if (bt == 0) {
             unsigned int *ctr = a.counters + (size_t)bat * a.n_blocks + blk;
-            const unsigned int prev = atomicAdd(ctr, span);
+            const unsigned int prev = sk_arrive(ctr, span);
             s_last = (prev + span == nc) ? 1u : 0u;
             if (s_last) *ctr = 0;  // ready for the next launch on this stream
         }
         ws_bar_builders();
         if (!s_last) return;
-        __threadfence();
         const uint32_t b0 = blk * nc, b1 = b0 + nc;
         const SkPart &p = a.part;
         // first contributor: the CTA whose unsnapped range holds b0, unless its snapped range ends there
@@ -312,6 +330,7 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
             if (hist[xbuf].last) ws_finish<MODE>(a, smem, hist[xbuf], bt, cta, G, bat);
         }
         hist[xbuf] = st;
+        bool staged = false;
         if (st.first) {
             // pair tables: entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]}; builder warp w writes the
             // entries with hi = w, w + WS_NB, ...; lane L writes its own bank.
@@ -336,22 +355,46 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
             }
         }
         if (!waited) {
+            if (bw == 0) WS_STAMP(1);
             // Everything above reads only weights.  x, the partial sums, the counters and y belong to
             // the stream order: wait for the kernels before this one.
             pdl_wait();
+            if (bw == 0) WS_STAMP(2);
             waited = true;
             // RMSNorm folded into the staging (rms_norm_inplace, src/lut/cpu_fallback.rs:39-54): every CTA
             // sums the squares of the whole row once (a few KB from L2) and scales the slices it stages.
             if (a.norm_n) {
+                // rows of up to 8192 values are read once: kept in registers between the sum of
+                // squares and the scaling of this first stage's slice
                 const uint4 *xr = reinterpret_cast<const uint4 *>(xrow);
+                const uint32_t n16row = a.norm_n / 8;
+                const bool one_pass = n16row <= 8 * WS_BTHREADS;
+                uint4 keep[8];
                 float ss = 0.0f;
-                for (uint32_t i = bt; i < a.norm_n / 8; i += WS_BTHREADS) {
-                    const uint4 v = xr[i];
-                    const __half2 *hp = reinterpret_cast<const __half2 *>(&v);
+                if (one_pass) {
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const float2 f = __half22float2(hp[e]);
-                        ss += f.x * f.x + f.y * f.y;
+                    for (int e = 0; e < 8; e++) {
+                        const uint32_t i = bt + e * WS_BTHREADS;
+                        keep[e] = i < n16row ? xr[i] : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const __half2 *hp = reinterpret_cast<const __half2 *>(&keep[e]);
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const float2 f = __half22float2(hp[q]);
+                            ss += f.x * f.x + f.y * f.y;
+                        }
+                    }
+                } else {
+                    for (uint32_t i = bt; i < n16row; i += WS_BTHREADS) {
+                        const uint4 v = xr[i];
+                        const __half2 *hp = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const float2 f = __half22float2(hp[q]);
+                            ss += f.x * f.x + f.y * f.y;
+                        }
                     }
                 }
 #pragma unroll
@@ -365,10 +408,29 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
                 }
                 ws_bar_builders();
                 inv = s_inv;
+                if (one_pass) {
+                    const uint32_t lo = st.pb * 4, hi = st.pe * 4;  // this stage's slice in 16-byte units of the row
+                    uint4 *xd = reinterpret_cast<uint4 *>(smem + WS_X_OFF + xbuf * WS_X_BYTES);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const uint32_t i = bt + e * WS_BTHREADS;
+                        if (i >= lo && i < hi) {
+                            uint4 v = keep[e];
+                            __half2 *hp = reinterpret_cast<__half2 *>(&v);
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                const float2 f = __half22float2(hp[q]);
+                                hp[q] = __floats2half2_rn(f.x * inv, f.y * inv);
+                            }
+                            xd[i - lo] = v;
+                        }
+                    }
+                    staged = true;
+                }
             }
         }
         // this stage's slice of x (fp16, normalised on the way if asked)
-        {
+        if (!staged) {
             const uint32_t n16 = (st.pe - st.pb) * 4;  // 16-byte units
             const uint4 *xg = reinterpret_cast<const uint4 *>(xrow + (size_t)st.pb * 32);
             uint4 *xd = reinterpret_cast<uint4 *>(smem + WS_X_OFF + xbuf * WS_X_BYTES);
@@ -388,7 +450,9 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
             }
         }
         t5::mbar_arrive(bar_full + 8 * xbuf);  // every builder thread: its table entries and x words are stored
+        if (t == 0 && bw == 0) WS_STAMP(3);
     }
+    if (bw == 0) WS_STAMP(7);
     // retire the last two stages in order
     const uint32_t n_stages = t;
     for (uint32_t r = (n_stages >= 2 ? n_stages - 2 : 0); r < n_stages; r++) {
@@ -396,6 +460,7 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
         ws_wait(bar_empty + 8 * xbuf, (r >> 1) & 1, err_flag);
         if (hist[xbuf].last) ws_finish<MODE>(a, smem, hist[xbuf], bt, cta, G, bat);
     }
+    if (bw == 0) WS_STAMP(8);
 }
 
 template <int MODE, int SBASE>
@@ -407,6 +472,9 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lut_gemv_ws_kernel(const SkArgs
         return;
     }
     pdl_launch_dependents();
+#ifdef WS_TIMING
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_ws_t0 = clock64();
+#endif
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t cta = blockIdx.x, G = gridDim.x, bat = blockIdx.y;
     const uint32_t u_begin = sk_boundary(a.part, cta);
@@ -519,3 +587,9 @@ int launch_gemv_ws(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const
 }
 
 }  // namespace prism
+
+#ifdef WS_TIMING
+extern "C" int prism_debug_ws_timing(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, prism::g_ws_timing, sizeof(unsigned long long) * 16);
+}
+#endif

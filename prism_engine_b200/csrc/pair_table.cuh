@@ -65,6 +65,16 @@ struct SkArgs {
     float norm_eps;
 };
 
+// Arrival on a block's counter: an acq_rel add at gpu scope.  Called by one thread after a CTA-level
+// barrier that follows the CTA's stores of partial sums (the release then covers those stores) and
+// before a CTA-level barrier that precedes the loads of other CTAs' partial sums (the acquire covers
+// them), so no separate fences are needed.
+__device__ __forceinline__ unsigned int sk_arrive(unsigned int *ctr, unsigned int v) {
+    unsigned int prev;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;\n" : "=r"(prev) : "l"(ctr), "r"(v) : "memory");
+    return prev;
+}
+
 __device__ __forceinline__ void sk_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                        uint32_t b0, uint32_t b1) {
     asm volatile(
