@@ -65,6 +65,8 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
  * prefill GEMM, default; 0 = activation rows through the GEMV kernel), "fuse" (0/1,
  * default 1: fused epilogues), "pdl" (0/1, default 1: programmatic dependent launch between
  * the kernels of a decode step, so a kernel's weight-only prologue overlaps its predecessor),
+ * "tp_peer_ar" (0/1, default 1: tensor-parallel partial sums are reduced by one kernel through
+ * peer memory instead of ncclAllReduce + add; set it identically on every rank),
  * "sk_min_chunks" (default 8: fewest 1 KB index chunks the GEMV gives one CTA of a small matrix),
  * "sk_stream_chunks" (default 64: chunks per CTA from which the GEMV deals contiguous, balanced
  * ranges to a persistent grid instead of cutting every 64-row block into equal parts). */
@@ -277,9 +279,14 @@ int prism_cuda_bench_gemm(prism_cuda_ctx *ctx, int32_t handle, uint32_t m_tok, u
 #define PRISM_NCCL_ID_BYTES 128
 /* Rank 0 fills `id` and hands the bytes to the other ranks (any transport). */
 int prism_cuda_tp_unique_id(uint8_t id[PRISM_NCCL_ID_BYTES]);
-/* Joins this context to a `world`-rank NCCL communicator. */
+/* Joins this context to a `world`-rank NCCL communicator and, when every rank can map every
+ * other rank's memory (one process per GPU, peer access over NVLink), sets up the receive areas of
+ * the peer-memory all-reduce the decode step then uses after its row-parallel matmuls. */
 int prism_cuda_tp_init(prism_cuda_ctx *ctx, int world, int rank, const uint8_t id[PRISM_NCCL_ID_BYTES]);
 int prism_cuda_tp_world(prism_cuda_ctx *ctx, int *world, int *rank);
+/* 1 when the peer-memory all-reduce is set up on this context (same answer on every rank), 0 when
+ * the step falls back to ncclAllReduce. */
+int prism_cuda_tp_peer_ready(prism_cuda_ctx *ctx);
 /* In-place fp16 sum over ranks of a device vector, on the context stream. */
 int prism_cuda_tp_all_reduce_dev(prism_cuda_ctx *ctx, void *buf_dev, size_t n_halfs);
 

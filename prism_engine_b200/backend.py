@@ -282,6 +282,10 @@ class CudaBackend:
         buf = (C.c_uint8 * _lib.NCCL_ID_BYTES).from_buffer_copy(uid)
         self._ck(self.L.prism_cuda_tp_init(self.ctx, world, rank, buf))
 
+    def tp_peer_ready(self) -> bool:
+        """True when the row-parallel partial sums are reduced through peer memory (else NCCL)."""
+        return bool(self.L.prism_cuda_tp_peer_ready(self.ctx))
+
 
 def model_config(num_layers, hidden_size, num_heads, num_kv_heads, head_dim, intermediate_size, vocab_size,
                  norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True, bits=4, max_seq=4096, max_batch=1,

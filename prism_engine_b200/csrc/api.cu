@@ -227,6 +227,8 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
     } else if (!strcmp(key, "sk_stream_chunks")) {
         if (value < 8 || value > (1 << 20)) return fail(ctx, PRISM_E_ARG, "sk_stream_chunks must be in 8..2^20");
         ctx->sk_stream_chunks = (int)value;
+    } else if (!strcmp(key, "tp_peer_ar")) {
+        ctx->tp_peer_ar = value ? 1 : 0;
     } else if (!strcmp(key, "pdl")) {
         ctx->pdl = value ? 1 : 0;
     } else {

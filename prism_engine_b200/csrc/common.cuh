@@ -92,6 +92,14 @@ struct prism_cuda_ctx {
     int tp_world = 1, tp_rank = 0;
     void *nccl_comm = nullptr;
     prism_nccl_api *nccl = nullptr;
+    // peer-memory all-reduce (tp.cu): receive area and flags of this rank, mapped by every peer
+    float *tp_recv = nullptr;          // [2 epochs][world][tp_cap] floats
+    unsigned int *tp_flags = nullptr;  // [world][TP_AR_MAX_CTAS] last epoch each peer CTA has delivered
+    unsigned int *tp_state = nullptr;  // {epoch, CTAs done} of the all-reduce sequence
+    void **tp_peer_tab = nullptr;      // device array: world receive-area pointers, then world flag pointers
+    void *tp_peer_map[32] = {nullptr};   // what cudaIpcOpenMemHandle returned: [q] receive area, [16+q] flags of peer q
+    size_t tp_cap = 0;                 // floats per rank slot; 0: peer path unavailable, NCCL is used
+    int tp_peer_ar = 1;                // option "tp_peer_ar": use the peer-memory all-reduce when available
 };
 
 namespace prism {
@@ -169,6 +177,13 @@ int ensure_act(prism_cuda_ctx *ctx, size_t halfs);
 int ensure_tmp(prism_cuda_ctx *ctx, size_t halfs);
 LutTensor *get_tensor(prism_cuda_ctx *ctx, int32_t handle);
 int probe_smem_base(prism_cuda_ctx *ctx);
+// tp.cu
+int tp_all_reduce_f32(prism_cuda_ctx *ctx, float *buf, size_t n);
+int tp_all_gather_bytes(prism_cuda_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank);
+// h[i] = f16( f32(f16(sum over ranks of part[i])) + f32(h[i]) ): the all-reduce of a row-parallel
+// matmul's fp32 partial sums fused with the residual add, through peer memory (one kernel, no NCCL).
+bool tp_peer_ar_ok(prism_cuda_ctx *ctx, size_t n);
+int tp_all_reduce_resid_peer(prism_cuda_ctx *ctx, const float *part, uint16_t *h, size_t n);
 // Reads the device error word; a non-zero value becomes PRISM_E_STATE.
 int check_device_error(prism_cuda_ctx *ctx);
 

@@ -14,8 +14,6 @@
 #include "common.cuh"
 
 namespace prism {
-int tp_all_reduce_f32(prism_cuda_ctx *ctx, float *buf, size_t n);
-int tp_all_gather_bytes(prism_cuda_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank);
 int synth_shard(prism_cuda_ctx *ctx, const char *name, uint32_t rows, uint32_t cols, uint32_t bits,
                 uint64_t seed, float sigma, uint32_t row0, uint32_t col0, int32_t *handle);
 }  // namespace prism
@@ -147,6 +145,16 @@ __global__ void final_pair_kernel(const uint64_t *__restrict__ pairs, uint32_t b
     next[b] = best ? ~(uint32_t)(best & 0xFFFFFFFFu) : 0u;
 }
 
+// Row-parallel matmul epilogue of a tensor-parallel rank: h = f16(f16(sum over ranks of part) + h).
+// One kernel through peer memory when the ranks could map each other, else ncclAllReduce + add.
+static int tp_reduce_add_resid(prism_cuda_engine *e, uint32_t n) {
+    prism_cuda_ctx *ctx = e->ctx;
+    if (tp_peer_ar_ok(ctx, n)) return tp_all_reduce_resid_peer(ctx, e->part, e->h, n);
+    PRISM_TRY(tp_all_reduce_f32(ctx, e->part, n));
+    launch_pdl(ctx, "round_add_resid_kernel", round_add_resid_kernel, (n + 255) / 256, 256, 0, e->part, e->h, n);
+    return after_launch(ctx, "round_add_resid_kernel");
+}
+
 // One palettized linear of the step.  A batch of 8 or more sequences goes through the tensor-core
 // GEMM (weights streamed once for the whole batch) followed by the same elementwise kernels the
 // unfused path uses, so the fp16 rounding points stay those of the reference; smaller batches use
@@ -223,9 +231,7 @@ static int enqueue_step(prism_cuda_engine *e) {
         }
         if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, to, nullptr, e->att, e->qd_l, (uint16_t *)e->part, H, nullptr, B));
-            PRISM_TRY(tp_all_reduce_f32(ctx, e->part, (size_t)B * H));
-            launch_pdl(ctx, "round_add_resid_kernel", round_add_resid_kernel, (B * H + 255) / 256, 256, 0, e->part, e->h, B * H);
-            PRISM_TRY(after_launch(ctx, "round_add_resid_kernel"));
+            PRISM_TRY(tp_reduce_add_resid(e, B * H));
         } else if (fused) {
             PRISM_TRY(linear(e, GEMV_RESID, to, nullptr, e->att, e->qd_l, e->h, H, e->h, B));
         } else {
@@ -244,9 +250,7 @@ static int enqueue_step(prism_cuda_engine *e) {
         const LutTensor &td = ctx->tensors[e->wd[l]];
         if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, td, nullptr, e->act, e->act_stride, (uint16_t *)e->part, H, nullptr, B));
-            PRISM_TRY(tp_all_reduce_f32(ctx, e->part, (size_t)B * H));
-            launch_pdl(ctx, "round_add_resid_kernel", round_add_resid_kernel, (B * H + 255) / 256, 256, 0, e->part, e->h, B * H);
-            PRISM_TRY(after_launch(ctx, "round_add_resid_kernel"));
+            PRISM_TRY(tp_reduce_add_resid(e, B * H));
         } else if (fused) {
             PRISM_TRY(linear(e, GEMV_RESID, td, nullptr, e->act, e->act_stride, e->h, H, e->h, B));
         } else {

@@ -7,6 +7,7 @@
 #include <nccl.h>
 
 #include <cstring>
+#include <vector>
 
 #include "common.cuh"
 
@@ -72,11 +73,194 @@ int tp_all_gather_bytes(prism_cuda_ctx *ctx, const void *send, void *recv, size_
     return PRISM_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// All-reduce through peer memory, fused with the residual add that follows a row-parallel matmul.
+//
+// Every rank owns a receive area [2][world][cap] floats and a flag array [world][TP_AR_MAX_CTAS],
+// both mapped by every peer (cudaIpc*).  All-reduce number e (counted on the device, the same on
+// every rank because every rank runs the same kernel sequence) works in independent slices, one
+// per CTA: CTA c of rank r stores its slice of the partial sums into slot [e & 1][r] of EVERY rank's
+// receive area (plain stores over NVLink), makes them visible (fence at system scope) and writes e
+// into flag [r][c] of every rank; it then waits until its own flags [0..world)[c] all hold e and adds
+// the `world` slices of its own receive area in rank order, so every rank computes bit-identical
+// sums.  Two slots are enough: a rank can only start e+2 after every peer has delivered e+1, which a
+// peer does only after it finished reading e.  The wait is bounded; when it gives up it sets the
+// context's error word and the step goes on with whatever arrived.
+// ---------------------------------------------------------------------------------------------
+constexpr int TP_AR_MAX_CTAS = 64;
+constexpr int TP_AR_THREADS = 256;
+constexpr size_t TP_AR_CAP_FLOATS = 64 * 1024;     // largest vector the peer path takes (256 KB per slot)
+constexpr unsigned int TP_AR_SPIN_LIMIT = 1u << 22;  // polls with back-off: about two seconds
+
+__global__ void __launch_bounds__(TP_AR_THREADS) tp_ar_resid_kernel(const float *__restrict__ part, uint16_t *h,
+                                                                    uint32_t n, void *const *peer_tab,
+                                                                    float *recv, unsigned int *flags,
+                                                                    unsigned int *state, uint32_t world,
+                                                                    uint32_t rank, uint32_t cap,
+                                                                    unsigned int *err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t cta = blockIdx.x, tid = threadIdx.x;
+    const unsigned int e = state[0] + 1;  // stable: the previous all-reduce kernel has completed
+    const uint32_t slot = e & 1;
+    const uint32_t i = (cta * TP_AR_THREADS + tid) * 4;
+    // ---- deliver this CTA's slice to every rank ----
+    if (i < n) {
+        const float4 v = *reinterpret_cast<const float4 *>(part + i);
+        for (uint32_t q = 0; q < world; q++) {
+            float *dst = static_cast<float *>(peer_tab[q]) + ((size_t)slot * world + rank) * cap + i;
+            *reinterpret_cast<float4 *>(dst) = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < world) {
+        unsigned int *f = static_cast<unsigned int *>(peer_tab[world + tid]) + rank * TP_AR_MAX_CTAS + cta;
+        asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(f), "r"(e) : "memory");
+    }
+    // ---- wait for the same slice of every rank ----
+    if (tid < world) {
+        const unsigned int *f = flags + tid * TP_AR_MAX_CTAS + cta;
+        unsigned int seen = 0, polls = 0;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(f) : "memory");
+            if (seen == e) break;
+            if (++polls > TP_AR_SPIN_LIMIT) {
+                atomicExch(err, 3u);  // a peer did not deliver: reported by the next host call
+                break;
+            }
+            if (polls > 64) __nanosleep(polls > 4096 ? 500 : 50);
+        }
+    }
+    __syncthreads();
+    // ---- add in rank order, round, add the residual ----
+    if (i < n) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t r = 0; r < world; r++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(recv + ((size_t)slot * world + r) * cap + i));
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        uint2 hv = *reinterpret_cast<const uint2 *>(h + i);
+        const __half2 h01 = *reinterpret_cast<const __half2 *>(&hv.x), h23 = *reinterpret_cast<const __half2 *>(&hv.y);
+        const float o0 = __half2float(__float2half_rn(s.x)) + __low2float(h01);
+        const float o1 = __half2float(__float2half_rn(s.y)) + __high2float(h01);
+        const float o2 = __half2float(__float2half_rn(s.z)) + __low2float(h23);
+        const float o3 = __half2float(__float2half_rn(s.w)) + __high2float(h23);
+        const __half2 r01 = __floats2half2_rn(o0, o1), r23 = __floats2half2_rn(o2, o3);
+        hv.x = *reinterpret_cast<const unsigned int *>(&r01);
+        hv.y = *reinterpret_cast<const unsigned int *>(&r23);
+        *reinterpret_cast<uint2 *>(h + i) = hv;
+    }
+    // ---- the last CTA to finish advances the epoch ----
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&state[1], 1u) == gridDim.x - 1) {
+            state[1] = 0;
+            state[0] = e;
+        }
+    }
+}
+
+bool tp_peer_ar_ok(prism_cuda_ctx *ctx, size_t n) {
+    return ctx->tp_world > 1 && ctx->tp_peer_ar && ctx->tp_cap != 0 && n <= ctx->tp_cap && n % 4 == 0 &&
+           (n + TP_AR_THREADS * 4 - 1) / (TP_AR_THREADS * 4) <= (size_t)TP_AR_MAX_CTAS;
+}
+
+int tp_all_reduce_resid_peer(prism_cuda_ctx *ctx, const float *part, uint16_t *h, size_t n) {
+    if (!tp_peer_ar_ok(ctx, n)) return fail(ctx, PRISM_E_STATE, "peer-memory all-reduce not available for this size");
+    const unsigned ctas = (unsigned)((n + TP_AR_THREADS * 4 - 1) / (TP_AR_THREADS * 4));
+    launch_pdl(ctx, "tp_ar_resid_kernel", tp_ar_resid_kernel, dim3(ctas), dim3(TP_AR_THREADS), 0, part, h, (uint32_t)n,
+               (void *const *)ctx->tp_peer_tab, ctx->tp_recv, ctx->tp_flags, ctx->tp_state, (uint32_t)ctx->tp_world,
+               (uint32_t)ctx->tp_rank, (uint32_t)ctx->tp_cap, ctx->dev_err);
+    return after_launch(ctx, "tp_ar_resid_kernel");
+}
+
+// Allocates this rank's receive area and flags, exchanges the IPC handles through NCCL and maps the
+// peers'.  Any failure leaves tp_cap = 0: the engine then reduces with ncclAllReduce.
+static int tp_peer_setup(prism_cuda_ctx *ctx) {
+    const int T = ctx->tp_world;
+    if (T > 16) return PRISM_OK;
+    const size_t recv_bytes = 2ull * T * TP_AR_CAP_FLOATS * sizeof(float);
+    const size_t flag_bytes = (size_t)T * TP_AR_MAX_CTAS * sizeof(unsigned int);
+    struct Handles { cudaIpcMemHandle_t recv, flags; };
+    Handles mine{}, *all_dev = nullptr;
+    std::vector<Handles> all(T);
+    auto give_up = [&](const char *why) {
+        (void)why;
+        (void)cudaGetLastError();
+        ctx->tp_cap = 0;
+        return PRISM_OK;
+    };
+    if (cudaMalloc((void **)&ctx->tp_recv, recv_bytes) != cudaSuccess) return give_up("cudaMalloc");
+    if (cudaMalloc((void **)&ctx->tp_flags, flag_bytes) != cudaSuccess) return give_up("cudaMalloc");
+    if (cudaMalloc((void **)&ctx->tp_state, 2 * sizeof(unsigned int)) != cudaSuccess) return give_up("cudaMalloc");
+    if (cudaMalloc((void **)&ctx->tp_peer_tab, 2 * T * sizeof(void *)) != cudaSuccess) return give_up("cudaMalloc");
+    cudaMemsetAsync(ctx->tp_flags, 0, flag_bytes, ctx->stream);
+    cudaMemsetAsync(ctx->tp_state, 0, 2 * sizeof(unsigned int), ctx->stream);
+    if (cudaIpcGetMemHandle(&mine.recv, ctx->tp_recv) != cudaSuccess) return give_up("cudaIpcGetMemHandle");
+    if (cudaIpcGetMemHandle(&mine.flags, ctx->tp_flags) != cudaSuccess) return give_up("cudaIpcGetMemHandle");
+    if (cudaMalloc((void **)&all_dev, sizeof(Handles) * (T + 1)) != cudaSuccess) return give_up("cudaMalloc");
+    cudaMemcpyAsync(all_dev + T, &mine, sizeof(Handles), cudaMemcpyHostToDevice, ctx->stream);
+    int rc = tp_all_gather_bytes(ctx, all_dev + T, all_dev, sizeof(Handles));
+    if (rc == PRISM_OK) {
+        cudaMemcpyAsync(all.data(), all_dev, sizeof(Handles) * T, cudaMemcpyDeviceToHost, ctx->stream);
+        if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = PRISM_E_CUDA;
+    }
+    cudaFree(all_dev);
+    if (rc != PRISM_OK) return give_up("all-gather of handles");
+    std::vector<void *> tab(2 * T, nullptr);
+    bool ok = true;
+    for (int q = 0; q < T && ok; q++) {
+        if (q == ctx->tp_rank) {
+            tab[q] = ctx->tp_recv;
+            tab[T + q] = ctx->tp_flags;
+            continue;
+        }
+        void *pr = nullptr, *pf = nullptr;
+        if (cudaIpcOpenMemHandle(&pr, all[q].recv, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
+            cudaIpcOpenMemHandle(&pf, all[q].flags, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            ctx->tp_peer_map[q] = pr;  // closed at shutdown if it was opened
+            ok = false;
+            break;
+        }
+        tab[q] = pr;
+        tab[T + q] = pf;
+        ctx->tp_peer_map[q] = pr;
+        ctx->tp_peer_map[16 + q] = pf;
+    }
+    // every rank must take the same path: agree on the outcome (min over ranks)
+    float flag_host = ok ? 1.0f : 0.0f, *flag_dev = nullptr;
+    if (cudaMalloc((void **)&flag_dev, sizeof(float)) != cudaSuccess) return give_up("cudaMalloc");
+    cudaMemcpyAsync(flag_dev, &flag_host, sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+    ncclResult_t r = ctx->nccl->AllReduce(flag_dev, flag_dev, 1, ncclFloat32, ncclMin, (ncclComm_t)ctx->nccl_comm, ctx->stream);
+    cudaMemcpyAsync(&flag_host, flag_dev, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(flag_dev);
+    if (r != ncclSuccess || flag_host < 0.5f) return give_up("a rank could not map its peers");
+    if (cudaMemcpy(ctx->tp_peer_tab, tab.data(), 2 * T * sizeof(void *), cudaMemcpyHostToDevice) != cudaSuccess)
+        return give_up("cudaMemcpy");
+    ctx->tp_cap = TP_AR_CAP_FLOATS;
+    return PRISM_OK;
+}
+
 }  // namespace prism
 
 using namespace prism;
 
 extern "C" void prism_tp_shutdown(prism_cuda_ctx *ctx) {
+    for (int q = 0; q < 32; q++) {
+        if (ctx->tp_peer_map[q]) {
+            cudaIpcCloseMemHandle(ctx->tp_peer_map[q]);
+            ctx->tp_peer_map[q] = nullptr;
+        }
+    }
+    cudaFree(ctx->tp_recv);
+    cudaFree(ctx->tp_flags);
+    cudaFree(ctx->tp_state);
+    cudaFree(ctx->tp_peer_tab);
+    ctx->tp_recv = nullptr; ctx->tp_flags = nullptr; ctx->tp_state = nullptr; ctx->tp_peer_tab = nullptr;
+    ctx->tp_cap = 0;
     if (ctx->nccl_comm && ctx->nccl) {
         ctx->nccl->CommDestroy((ncclComm_t)ctx->nccl_comm);
         ctx->nccl_comm = nullptr;
@@ -120,7 +304,7 @@ int prism_cuda_tp_init(prism_cuda_ctx *ctx, int world, int rank, const uint8_t i
     }
     ctx->nccl = api;
     ctx->nccl_comm = comm;
-    return PRISM_OK;
+    return tp_peer_setup(ctx);
 }
 
 int prism_cuda_tp_world(prism_cuda_ctx *ctx, int *world, int *rank) {
@@ -129,6 +313,8 @@ int prism_cuda_tp_world(prism_cuda_ctx *ctx, int *world, int *rank) {
     if (rank) *rank = ctx->tp_rank;
     return PRISM_OK;
 }
+
+int prism_cuda_tp_peer_ready(prism_cuda_ctx *ctx) { return (ctx && ctx->tp_world > 1 && ctx->tp_cap != 0) ? 1 : 0; }
 
 int prism_cuda_tp_all_reduce_dev(prism_cuda_ctx *ctx, void *buf_dev, size_t n_halfs) {
     if (!ctx || !buf_dev) return fail(ctx, PRISM_E_NULL, "null argument");
