@@ -227,6 +227,13 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
     } else if (!strcmp(key, "sk_stream_chunks")) {
         if (value < 8 || value > (1 << 20)) return fail(ctx, PRISM_E_ARG, "sk_stream_chunks must be in 8..2^20");
         ctx->sk_stream_chunks = (int)value;
+    } else if (!strcmp(key, "batch_gemv_max")) {
+        if (value < 1 || value > 4096) return fail(ctx, PRISM_E_ARG, "batch_gemv_max must be in 1..4096");
+        ctx->batch_gemv_max = (int)value;
+    } else if (!strcmp(key, "attn_cluster")) {
+        if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8)
+            return fail(ctx, PRISM_E_ARG, "attn_cluster must be 0, 1, 2, 4 or 8");
+        ctx->attn_cluster = (int)value;
     } else if (!strcmp(key, "tp_peer_ar")) {
         ctx->tp_peer_ar = value ? 1 : 0;
     } else if (!strcmp(key, "pdl")) {

@@ -277,6 +277,8 @@ int launch_attn_fused(prism_cuda_ctx *ctx, const AttnArgs &a, const uint16_t *k_
     fa.rope_k = rope_k; fa.rope_base = rope_base;
     // cluster size: enough CTAs per head to keep every SM loading cache rows at long contexts
     uint32_t S = a.max_seq >= 512 ? 8 : a.max_seq >= 256 ? 4 : a.max_seq >= 128 ? 2 : 1;
+    if (ctx->attn_cluster == 1 || ctx->attn_cluster == 2 || ctx->attn_cluster == 4 || ctx->attn_cluster == 8)
+        S = (uint32_t)ctx->attn_cluster;
     fa.chunk_cap = (a.max_seq + S - 1) / S;
     const size_t smem = (size_t)fa.chunk_cap * sizeof(float);
     if (smem > 160 * 1024) return fail(ctx, PRISM_E_ARG, "fused attention: max_seq too large for the score buffer");

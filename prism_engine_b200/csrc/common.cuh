@@ -71,6 +71,8 @@ struct prism_cuda_ctx {
     int fuse = 1;
     int sk_min_chunks = 8;      // stream-K GEMV, small matrices: fewest 1 KB index chunks a CTA is given
     int sk_stream_chunks = 64;  // chunks per CTA from which the balanced contiguous partition is used
+    int batch_gemv_max = 8;  // decode batches up to this size use the batched GEMV (groups of 8), larger ones the GEMM
+    int attn_cluster = 0;    // CTAs per (head, sequence) of the fused attention kernel; 0: chosen from max_seq
     int pdl = 1;  // programmatic dependent launch between the kernels of the decode chain
     uint64_t launches = 0;
     // staging for host-pointer entry points (grown on demand)
@@ -223,6 +225,12 @@ bool ws_preferred(prism_cuda_ctx *ctx, const LutTensor &t, bool swiglu, uint32_t
 int launch_gemv_ws(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
                    uint32_t x_stride, void *y, uint32_t y_stride, const uint16_t *resid, uint32_t batch,
                    float norm_eps);
+
+// gemv_wsb.cu: the warp-specialised kernel for 2..8 activation rows at once (weights streamed once);
+// the rows must already be normalised
+bool wsb_eligible(const LutTensor &t, uint32_t batch);
+int launch_gemv_wsb(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
+                    uint32_t x_stride, void *y, uint32_t y_stride, const uint16_t *resid, uint32_t batch);
 
 // gemv_tc5.cu: tcgen05/TMEM GEMV (4-bit, K % 32 == 0, one activation vector)
 bool tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t batch);

@@ -162,7 +162,7 @@ static int tp_reduce_add_resid(prism_cuda_engine *e, uint32_t n) {
 static int linear(prism_cuda_engine *e, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
                   uint32_t xs, uint16_t *y, uint32_t ys, const uint16_t *resid, uint32_t B) {
     prism_cuda_ctx *ctx = e->ctx;
-    const bool gemm_ok = B >= 8 && ctx->gemm_variant == 1 && e->gu && gemm_tc5_eligible(ctx, t, B) && xs == t.k &&
+    const bool gemm_ok = B > (uint32_t)ctx->batch_gemv_max && ctx->gemm_variant == 1 && e->gu && gemm_tc5_eligible(ctx, t, B) && xs == t.k &&
                          (mode == GEMV_SWIGLU ? ys == t.m : ys == t.m);
     if (!gemm_ok) return launch_gemv(ctx, mode, t, t2, x, xs, y, ys, resid, B);
     if (mode == GEMV_PLAIN) return launch_gemm(ctx, t, x, B, y);
@@ -195,7 +195,7 @@ static int enqueue_step(prism_cuda_engine *e) {
                         &to = ctx->tensors[e->wo[l]], &tg = ctx->tensors[e->wg[l]], &tu = ctx->tensors[e->wu[l]];
         const uint32_t qs = e->qkv_stride;
         // the Norm node is folded into the x staging of the matmul that consumes it (small batches)
-        const bool fold = fused && B < 8;
+        const bool fold = fused && B == 1;  // batches go through the one-pass batched GEMV, which takes normalised rows
         if (fold && e->wqkv[l] >= 0) {
             ctx->pending_norm_eps = c.norm_eps;
             PRISM_TRY(launch_gemv(ctx, GEMV_PLAIN, ctx->tensors[e->wqkv[l]], nullptr, e->h, H, e->qkv, qs, nullptr, B));
@@ -260,7 +260,7 @@ static int enqueue_step(prism_cuda_engine *e) {
         }
         li += 1;
     }
-    const bool fold_head = fused && B < 8;
+    const bool fold_head = fused && B == 1;
     if (!fold_head) PRISM_TRY(launch_rms_norm(ctx, e->h, e->xn, H, c.norm_eps, B));
     const LutTensor &head = ctx->tensors[(c.tie_word_embeddings || e->lm_head < 0) ? e->embed : e->lm_head];
     const uint32_t lstride = round_up_u32(e->V_l, 8);

@@ -441,10 +441,12 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
     // inner loop on a (block, K split) grid; 4: warp-specialised kernel for every shape;
     // 5: stream-K kernel for every shape; 0: plain kernel
     const int v = ctx->gemv_variant;
-    const bool use_tc5 = v == 2 && tc5_eligible(ctx, t, batch);
-    const bool use_ws = !use_tc5 && ((v == 4 && ws_eligible(t)) ||
-                                     ((v == 1 || v == 2) && ws_preferred(ctx, t, mode == GEMV_SWIGLU, batch)));
-    const bool use_sk = !use_tc5 && !use_ws && (v == 1 || v == 2 || v == 5) && sk_eligible(t);
+    // 2..8 activation rows: one pass over the weights for all of them (larger batches in groups of 8)
+    const bool use_wsb = (v == 1 || v == 2) && batch >= 2 && wsb_eligible(t, batch < 8 ? batch : 8);
+    const bool use_tc5 = !use_wsb && v == 2 && tc5_eligible(ctx, t, batch);
+    const bool use_ws = !use_wsb && !use_tc5 && ((v == 4 && ws_eligible(t)) ||
+                                                 ((v == 1 || v == 2) && ws_preferred(ctx, t, mode == GEMV_SWIGLU, batch)));
+    const bool use_sk = !use_wsb && !use_tc5 && !use_ws && (v == 1 || v == 2 || v == 5) && sk_eligible(t);
     const bool use_mma = !use_tc5 && ctx->gemv_variant == 3 && mma_eligible(t);
     if (norm_eps >= 0.0f && !((use_mma || use_sk || use_ws) && t.k % 8 == 0 && x_stride >= t.k)) {
         // this kernel choice cannot fold the norm: run it as its own kernel into scratch
@@ -453,6 +455,18 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
         for (uint32_t b = 0; b < batch; b++)
             PRISM_TRY(launch_rms_norm(ctx, x + (size_t)b * x_stride, xn + (size_t)b * x_stride, t.k, norm_eps, 1));
         return launch_gemv(ctx, mode, t, t2, xn, x_stride, y, y_stride, resid, batch);
+    }
+    if (use_wsb) {
+        for (uint32_t g0 = 0; g0 < batch; g0 += 8) {
+            const uint32_t nb = batch - g0 < 8 ? batch - g0 : 8;
+            const uint16_t *xg = x + (size_t)g0 * x_stride;
+            void *yg = mode == GEMV_F32 ? (void *)(reinterpret_cast<float *>(y) + (size_t)g0 * y_stride)
+                                        : (void *)(y + (size_t)g0 * y_stride);
+            const uint16_t *rg = resid ? resid + (size_t)g0 * y_stride : nullptr;
+            if (nb == 1) PRISM_TRY(launch_gemv(ctx, mode, t, t2, xg, x_stride, static_cast<uint16_t *>(yg), y_stride, rg, 1));
+            else PRISM_TRY(launch_gemv_wsb(ctx, mode, t, t2, xg, x_stride, yg, y_stride, rg, nb));
+        }
+        return PRISM_OK;
     }
     if (use_tc5) return launch_gemv_tc5(ctx, mode, t, t2, x, y, resid);
     if (use_ws) return launch_gemv_ws(ctx, mode, t, t2, x, x_stride, y, y_stride, resid, batch, norm_eps);

@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "pair_table.cuh"
 #include "tc5_ptx.cuh"
+#include "ws_common.cuh"
 
 namespace prism {
 
@@ -33,7 +34,7 @@ namespace prism {
 #endif
 constexpr int WS_NC = WS_NC_N;                  // compute warps
 constexpr int WS_NB = WS_NB_N;                  // builder warps
-static_assert(WS_NB == 4, "the finish step (scratch sizes, two groups of 64 threads) is written for 128 builder threads");
+static_assert(WS_NB * 32 == WS_COMMON_BTHREADS, "the finish step (scratch sizes, two groups of 64 threads) is written for 128 builder threads");
 constexpr int WS_THREADS = (WS_NC + WS_NB) * 32;
 constexpr int WS_BTHREADS = WS_NB * 32;
 constexpr int WS_PF = WS_PF_N;                  // index chunks in flight per compute warp (1, 2 or 4)
@@ -46,7 +47,6 @@ constexpr int WS_FIN_OFF = WS_RED_OFF + 2 * WS_NC * 64 * 4; // builder scratch: 
 constexpr int WS_BAR_OFF = WS_FIN_OFF + 256 * 4;            // full[2], empty[2], flags
 constexpr size_t WS_SMEM_BYTES = WS_BAR_OFF + 64;
 constexpr int WS_KNOWN_SBASE = 1024;
-constexpr uint32_t WS_WAIT_LIMIT = 1u << 24;    // polls (with back-off) before a wait gives up
 
 #ifdef WS_TIMING
 // Debug builds: per-phase clock stamps of CTA 0 (SM clock cycles since kernel entry).
@@ -56,66 +56,6 @@ __device__ unsigned long long g_ws_t0;
 #else
 #define WS_STAMP(i) do { } while (0)
 #endif
-
-// One stage of a CTA's range.
-struct WsStage {
-    uint32_t blk, pb, pe;   // block, chunk run [pb, pe) inside it
-    uint32_t cb, ce;        // the whole run of this CTA inside the block (segment)
-    uint32_t seg;           // index of the segment within the CTA (table buffer = seg & 1)
-    bool first, last;       // first / last stage of the segment
-};
-// Walks the stages of the range [u, u_end).
-struct WsWalk {
-    uint32_t u, u_end, nc, seg, pb_next;
-    WsStage cur;
-    bool in_seg;
-    __device__ __forceinline__ void init(uint32_t u0, uint32_t u1, uint32_t n_chunks) {
-        u = u0; u_end = u1; nc = n_chunks; seg = 0; in_seg = false; pb_next = 0;
-        cur = WsStage{};
-    }
-    // false when the range is exhausted
-    __device__ __forceinline__ bool next() {
-        if (!in_seg) {
-            if (u >= u_end) return false;
-            cur.blk = u / nc;
-            cur.cb = u - cur.blk * nc;
-            cur.ce = min(nc, cur.cb + (u_end - u));
-            u += cur.ce - cur.cb;
-            cur.seg = seg++;
-            pb_next = cur.cb;
-            in_seg = true;
-        }
-        cur.pb = pb_next;
-        cur.pe = min(cur.ce, cur.pb + (uint32_t)WS_STAGE_CHUNKS);
-        cur.first = cur.pb == cur.cb;
-        cur.last = cur.pe == cur.ce;
-        pb_next = cur.pe;
-        if (cur.last) in_seg = false;
-        return true;
-    }
-};
-
-__device__ __forceinline__ void ws_wait(uint32_t bar, uint32_t parity, volatile uint32_t *err_flag) {
-    for (uint32_t i = 0; i < WS_WAIT_LIMIT; i++) {
-        if (t5::mbar_test(bar, parity)) return;
-        if ((i & 15) == 15) {
-            if (*err_flag) return;
-            __nanosleep(20);
-        }
-    }
-    *err_flag = 1;
-}
-__device__ __forceinline__ void ws_bar_builders() { asm volatile("bar.sync 1, %0;\n" ::"n"(WS_BTHREADS) : "memory"); }
-__device__ __forceinline__ uint32_t ws_bar_builders_count(bool pred) {
-    uint32_t n;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %1, 0;\n\t"
-        "bar.red.popc.u32 %0, 1, %2, p;\n\t}\n"
-        : "=r"(n)
-        : "r"((uint32_t)pred), "n"(WS_BTHREADS)
-        : "memory");
-    return n;
-}
 
 // One 32-weight chunk of the two half-blocks (see sk_chunk in gemv_sk.cu for the operand layout);
 // compute warps are WS_NC chunks apart.
@@ -155,7 +95,7 @@ __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint3
     uint4 xb[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     WsWalk walk;
-    walk.init(u_begin, u_end, nc);
+    walk.init(u_begin, u_end, nc, WS_STAGE_CHUNKS);
     for (uint32_t t = 0; walk.next(); t++) {
         const WsStage &st = walk.cur;
         const uint32_t xbuf = t & 1, par = (t >> 1) & 1, tb = st.seg & 1;
@@ -318,7 +258,7 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
     bool waited = false;
     WsStage hist[2];  // the two stages in flight, by buffer
     WsWalk walk;
-    walk.init(u_begin, u_end, nc);
+    walk.init(u_begin, u_end, nc, WS_STAGE_CHUNKS);
     uint32_t t = 0;
     for (; walk.next(); t++) {
         const WsStage st = walk.cur;
@@ -434,18 +374,27 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
             const uint32_t n16 = (st.pe - st.pb) * 4;  // 16-byte units
             const uint4 *xg = reinterpret_cast<const uint4 *>(xrow + (size_t)st.pb * 32);
             uint4 *xd = reinterpret_cast<uint4 *>(smem + WS_X_OFF + xbuf * WS_X_BYTES);
-            if (a.norm_n == 0) {
-                for (uint32_t i = bt; i < n16; i += WS_BTHREADS) xd[i] = xg[i];
-            } else {
-                for (uint32_t i = bt; i < n16; i += WS_BTHREADS) {
-                    uint4 v = xg[i];
-                    __half2 *hp = reinterpret_cast<__half2 *>(&v);
+            // four 16-byte loads per thread in flight before the first store
+            for (uint32_t i0 = bt; i0 < n16; i0 += 4 * WS_BTHREADS) {
+                uint4 v[4];
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const float2 f = __half22float2(hp[e]);
-                        hp[e] = __floats2half2_rn(f.x * inv, f.y * inv);
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t i = i0 + e * WS_BTHREADS;
+                    v[e] = i < n16 ? xg[i] : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t i = i0 + e * WS_BTHREADS;
+                    if (i >= n16) continue;
+                    if (a.norm_n != 0) {
+                        __half2 *hp = reinterpret_cast<__half2 *>(&v[e]);
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const float2 f = __half22float2(hp[q]);
+                            hp[q] = __floats2half2_rn(f.x * inv, f.y * inv);
+                        }
                     }
-                    xd[i] = v;
+                    xd[i] = v[e];
                 }
             }
         }
@@ -529,7 +478,7 @@ bool ws_preferred(prism_cuda_ctx *ctx, const LutTensor &t, bool swiglu, uint32_t
 }
 
 // Chooses the partition (see SkPart) for one activation vector of a batch: one CTA per SM.
-static SkPart ws_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch) {
+SkPart ws_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch) {
     SkPart p{};
     p.n_chunks = n_chunks;
     p.total = n_blocks * n_chunks;

@@ -101,7 +101,8 @@ def test_fused_gate_up_and_mlp(backend, oracle, variant, hidden, inter):
 
 
 @pytest.mark.parametrize("gemm_variant", [0, 1])
-@pytest.mark.parametrize("m,k,m_tok", [(192, 256, 37), (256, 512, 300), (130, 64, 32), (512, 3584, 96)])
+@pytest.mark.parametrize("m,k,m_tok", [(192, 256, 37), (256, 512, 300), (130, 64, 32), (512, 3584, 96),
+                                        (4864, 896, 2), (896, 4864, 3), (2368, 8192, 7), (192, 256, 9), (640, 29568, 5)])
 def test_gemm_rows_are_gemvs(backend, oracle, gemm_variant, m, k, m_tok):
     backend.set_option("gemm_variant", gemm_variant)
     pay = synth.make_payload(m, k, seed=6)
