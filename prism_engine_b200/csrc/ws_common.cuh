@@ -18,19 +18,39 @@ struct WsStage {
     uint32_t seg;           // index of the segment within the CTA (table buffer = seg & 1)
     bool first, last;       // first / last stage of the segment
 };
-// Walks the stages of the range [u, u_end).
+// Walks the stages of a CTA's range [u0, u1).  The two segments that cover only part of a block
+// (the head of the range, when it starts inside a block, and its tail, when it ends inside one)
+// come first, whole blocks after them: the partial sums of shared blocks are delivered, and fixed up
+// by whichever CTA completes the block, while the whole blocks are still being streamed, and the
+// kernel ends on a segment that only has to write its outputs.
 struct WsWalk {
-    uint32_t u, u_end, nc, seg, pb_next, sc;
+    uint32_t lo1, hi1, lo2, hi2;  // tail, whole blocks (the head is the first [u, u_end))
+    uint32_t phase, u, u_end, nc, seg, pb_next, sc;
     WsStage cur;
     bool in_seg;
     __device__ __forceinline__ void init(uint32_t u0, uint32_t u1, uint32_t n_chunks, uint32_t stage_chunks) {
-        u = u0; u_end = u1; nc = n_chunks; sc = stage_chunks; seg = 0; in_seg = false; pb_next = 0;
+        nc = n_chunks; sc = stage_chunks; seg = 0; in_seg = false; pb_next = 0;
         cur = WsStage{};
+        const uint32_t b0 = u0 / nc;
+        uint32_t m0 = u0;                                   // start of what follows the head
+        u = u_end = u0;
+        if (u0 != b0 * nc) {                                // the range starts inside block b0: head
+            u_end = min(u1, (b0 + 1) * nc);
+            m0 = u_end;
+        }
+        const uint32_t t0 = max(m0, (u1 / nc) * nc);        // start of the block the range ends in
+        lo1 = t0; hi1 = (t0 < u1 && u1 != (u1 / nc) * nc) ? u1 : t0;  // tail: only if it ends inside a block
+        lo2 = m0; hi2 = hi1 > lo1 ? t0 : u1;                // whole blocks between them
+        phase = 0;
     }
     // false when the range is exhausted
     __device__ __forceinline__ bool next() {
         if (!in_seg) {
-            if (u >= u_end) return false;
+            while (u >= u_end) {
+                if (++phase > 2) return false;
+                u = phase == 1 ? lo1 : lo2;
+                u_end = phase == 1 ? hi1 : hi2;
+            }
             cur.blk = u / nc;
             cur.cb = u - cur.blk * nc;
             cur.ce = min(nc, cur.cb + (u_end - u));
