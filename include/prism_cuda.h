@@ -77,6 +77,13 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
 int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value);
 /* Number of kernels this library has launched on the context so far. */
 uint64_t prism_cuda_launch_count(prism_cuda_ctx *ctx);
+/* Host arithmetic only (no context, no GPU): how the persistent GEMV kernels deal a matrix of
+ * n_blocks 64-row blocks x n_chunks 1 KB index chunks to `slots` resident CTAs.  Writes the number of
+ * CTAs and, when `bounds` is given (cap >= CTAs + 1 entries), the first (block, chunk) unit of every
+ * CTA's range followed by the total.  No counterpart in the reference; exists so the partition can be
+ * checked without a device. */
+int prism_cuda_gemv_partition(uint32_t n_blocks, uint32_t n_chunks, uint32_t slots, uint32_t stream_chunks,
+                              uint32_t min_chunks, uint32_t *n_ctas, uint32_t *bounds, uint32_t cap);
 
 /* ---- weights: the upload loop of MetalBackend::new (engine_impl.rs:123-133)
  *      and PrismEngine::load (engine_impl.rs:597-676) ---------------------- */

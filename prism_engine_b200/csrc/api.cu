@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "pair_table.cuh"
 
 namespace prism {
 
@@ -245,6 +246,19 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
 }
 
 uint64_t prism_cuda_launch_count(prism_cuda_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+int prism_cuda_gemv_partition(uint32_t n_blocks, uint32_t n_chunks, uint32_t slots, uint32_t stream_chunks,
+                              uint32_t min_chunks, uint32_t *n_ctas, uint32_t *bounds, uint32_t cap) {
+    if (!n_ctas) return PRISM_E_NULL;
+    if (n_blocks == 0 || n_chunks == 0 || slots == 0 || (uint64_t)n_blocks * n_chunks >= (1ull << 32)) return PRISM_E_ARG;
+    const SkPart p = sk_choose_partition(n_blocks, n_chunks, slots, stream_chunks, min_chunks, 128);
+    *n_ctas = p.G;
+    if (bounds) {
+        if (cap < p.G + 1) return PRISM_E_ARG;
+        for (uint32_t i = 0; i <= p.G; i++) bounds[i] = sk_boundary(p, i);
+    }
+    return PRISM_OK;
+}
 
 int prism_cuda_upload_palettized_shard(prism_cuda_ctx *ctx, const char *name, const uint8_t *payload,
                                        size_t len, uint32_t dim_m, uint32_t dim_n, uint32_t bits,

@@ -362,27 +362,8 @@ bool sk_eligible(const LutTensor &t) { return t.bits == 4 && t.k % 32 == 0 && t.
 
 // Chooses the partition (see SkPart) for one activation vector of a batch.
 SkPart sk_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch) {
-    SkPart p{};
-    p.n_chunks = n_chunks;
-    p.total = n_blocks * n_chunks;
-    uint32_t slots = (uint32_t)ctx->sm_count * SK_CTAS_PER_SM / (batch ? batch : 1);
-    if (slots == 0) slots = 1;
-    uint32_t min_chunks = ctx->sk_min_chunks > SK_QUANT ? (uint32_t)ctx->sk_min_chunks : (uint32_t)SK_QUANT;
-    if (p.total / slots >= (uint32_t)ctx->sk_stream_chunks && p.total / slots >= (n_chunks + 127) / 128) {
-        p.G = slots;
-        p.q = p.total / p.G;
-        p.r = p.total % p.G;
-        // short rows, several blocks per CTA: whole blocks only (no partial sums, no extra table)
-        p.whole_blocks = (n_chunks <= 64 && p.q >= 3 * n_chunks) ? 1 : 0;
-    } else {
-        uint32_t s = n_chunks / min_chunks;
-        if (s > slots / n_blocks) s = slots / n_blocks;
-        if (s > 8) s = 8;
-        if (s < 1) s = 1;
-        p.s = s;
-        p.G = n_blocks * s;
-    }
-    return p;
+    const uint32_t slots = (uint32_t)ctx->sm_count * SK_CTAS_PER_SM / (batch ? batch : 1);
+    return sk_choose_partition(n_blocks, n_chunks, slots, (uint32_t)ctx->sk_stream_chunks, (uint32_t)ctx->sk_min_chunks, 128);
 }
 
 int launch_gemv_sk(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,

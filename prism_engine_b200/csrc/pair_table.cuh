@@ -65,6 +65,35 @@ struct SkArgs {
     float norm_eps;
 };
 
+// Chooses between the two forms for a matrix of n_blocks x n_chunks units and `slots` resident CTA
+// slots: contiguous balanced ranges when a CTA gets at least `stream_chunks` chunks (and no block
+// more than `max_contrib` contributors), else every block in s <= 8 equal parts of at least
+// `min_chunks` chunks.  Pure host arithmetic.
+inline SkPart sk_choose_partition(uint32_t n_blocks, uint32_t n_chunks, uint32_t slots, uint32_t stream_chunks,
+                                  uint32_t min_chunks, uint32_t max_contrib) {
+    SkPart p{};
+    p.n_chunks = n_chunks;
+    p.total = n_blocks * n_chunks;
+    if (slots == 0) slots = 1;
+    if (min_chunks < (uint32_t)SK_QUANT) min_chunks = SK_QUANT;
+    if (p.total / slots >= stream_chunks && p.total / slots >= (n_chunks + max_contrib - 1) / max_contrib &&
+        p.total / slots >= 1) {
+        p.G = slots;
+        p.q = p.total / p.G;
+        p.r = p.total % p.G;
+        // short rows, several blocks per CTA: whole blocks only (no partial sums, no extra table)
+        p.whole_blocks = (n_chunks <= 64 && p.q >= 3 * n_chunks) ? 1 : 0;
+    } else {
+        uint32_t s = n_chunks / min_chunks;
+        if (n_blocks && s > slots / n_blocks) s = slots / n_blocks;
+        if (s > 8) s = 8;
+        if (s < 1) s = 1;
+        p.s = s;
+        p.G = n_blocks * s;
+    }
+    return p;
+}
+
 // gemv_ws.cu: the partition of the warp-specialised kernels (one CTA per SM)
 SkPart ws_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch);
 
