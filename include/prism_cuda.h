@@ -119,6 +119,19 @@ int prism_cuda_tensor_dims(prism_cuda_ctx *ctx, int32_t handle, uint32_t *dim_m,
 /* Inverse of the re-lay: writes the tensor back as a reference-format payload
  * (len must equal dim_m*2^bits*2 + dim_m*dim_n*bits/8). */
 int prism_cuda_download_payload(prism_cuda_ctx *ctx, int32_t handle, uint8_t *payload, size_t len);
+
+/* ---- offline quantiser: palettize_matrix (src/quantization/palette.rs:230-275) + payload assembly
+ *      (src/lut/compiler.rs:50-61) -------------------------------------------------------------
+ * Fits a k-entry (k <= 16) palette per row of the fp32 matrix weights[dim_m][dim_n] with the
+ * reference's deterministic k-means (fit_palette, palette.rs:75-174; max_iter = 50 there), encodes
+ * the row (encode_channel, :189-217) and writes the reference payload (dim_m x 16 fp16 palettes,
+ * then dim_m rows of dim_n/2 index bytes), bit-identical to the CPU quantiser.  dim_n must be even;
+ * len must be dim_m*32 + dim_m*dim_n/2.  Host pointers; _dev takes device pointers and runs on the
+ * context stream. */
+int prism_cuda_palettize(prism_cuda_ctx *ctx, const float *weights, uint32_t dim_m, uint32_t dim_n, uint32_t k,
+                         uint32_t max_iter, uint8_t *payload, size_t len);
+int prism_cuda_palettize_dev(prism_cuda_ctx *ctx, const float *weights_dev, uint32_t dim_m, uint32_t dim_n,
+                             uint32_t k, uint32_t max_iter, uint8_t *payload_dev);
 /* Dequantised weights, row-major [dim_m][dim_n] fp16 bit patterns: the gather
  * of PrismEngine::embed (engine_impl.rs:1407-1446) / dequantize_matrix
  * (src/quantization/palette.rs:280-292) for every row.  Bit-exact. */

@@ -99,6 +99,9 @@ SIGNATURES = {
     "prism_cuda_tp_init": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
     "prism_cuda_tp_world": (C.c_int, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "prism_cuda_tp_peer_ready": (C.c_int, [_vp]),
+    "prism_cuda_palettize": (C.c_int, [_vp, C.POINTER(C.c_float), C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                       C.POINTER(C.c_uint8), C.c_size_t]),
+    "prism_cuda_palettize_dev": (C.c_int, [_vp, _vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _vp]),
     "prism_cuda_gemv_partition": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                             C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.c_uint32]),
     "prism_cuda_tp_all_reduce_dev": (C.c_int, [_vp, _vp, _sz]),

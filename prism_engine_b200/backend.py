@@ -282,6 +282,17 @@ class CudaBackend:
         buf = (C.c_uint8 * _lib.NCCL_ID_BYTES).from_buffer_copy(uid)
         self._ck(self.L.prism_cuda_tp_init(self.ctx, world, rank, buf))
 
+    def palettize(self, weights: np.ndarray, k: int = 16, max_iter: int = 50) -> np.ndarray:
+        """``palettize_matrix`` (src/quantization/palette.rs:230-275) + payload assembly
+        (src/lut/compiler.rs:50-61) on the GPU: fp32 ``weights[dim_m][dim_n]`` -> the reference payload
+        bytes, bit-identical to the CPU quantiser."""
+        w = np.ascontiguousarray(weights, dtype=np.float32)
+        dm, dn = w.shape
+        out = np.empty(dm * 32 + dm * (dn // 2), dtype=np.uint8)
+        self._ck(self.L.prism_cuda_palettize(self.ctx, w.ctypes.data_as(C.POINTER(C.c_float)), dm, dn, k, max_iter,
+                                             out.ctypes.data_as(C.POINTER(C.c_uint8)), out.size))
+        return out
+
     def tp_peer_ready(self) -> bool:
         """True when the row-parallel partial sums are reduced through peer memory (else NCCL)."""
         return bool(self.L.prism_cuda_tp_peer_ready(self.ctx))

@@ -73,10 +73,12 @@ __device__ __forceinline__ void wb_mma_all(float (&acc)[NBP][2][4], const uint32
         sk_mma(acc[p][1], A[4], A[5], A[6], A[7], xb[p].z, xb[p].w);
     }
 }
-template <int SBASE, int NBP>
+// NEXT_IMM >= 0: the chunk two steps ahead inside the same stage is requested from `next` (when
+// `more`); NEXT_IMM < 0: the request goes through the cross-stage cursor `pf`.
+template <int SBASE, int NBP, int NEXT_IMM>
 __device__ __forceinline__ void wb_chunk(float (&acc)[NBP][2][4], uint4 &w1, uint4 &w2, uint4 (&xb)[NBP],
                                          uint32_t lane_off, uint32_t x_off, uint32_t diag, uint32_t base,
-                                         WsPrefetch &pf) {
+                                         WsPrefetch &pf, const SkSrcPtr &next, bool more) {
     uint32_t A0[8], A1[8];
     sk_lookup<SBASE>(A0, w1.x, w2.x, lane_off, base);
     wb_ldx_all<SBASE, NBP, 0>(xb, x_off, base, diag);
@@ -87,15 +89,20 @@ __device__ __forceinline__ void wb_chunk(float (&acc)[NBP][2][4], uint4 &w1, uin
     wb_mma_all<NBP>(acc, A1, xb);
     wb_ldx_all<SBASE, NBP, 2>(xb, x_off, base, diag);
     sk_lookup<SBASE>(A1, w1.w, w2.w, lane_off, base);
-    // w1/w2 are dead from here: they take the chunk two steps ahead (possibly of a later stage)
-    if (pf.valid) {
+    // w1/w2 are dead from here: they take the chunk two steps ahead
+    if (NEXT_IMM >= 0) {
+        if (more) {
+            w1 = next.template load1<(NEXT_IMM >= 0 ? NEXT_IMM : 0)>();
+            w2 = next.template load2<(NEXT_IMM >= 0 ? NEXT_IMM : 0)>();
+        }
+    } else if (pf.valid) {
         w1 = pf.src.load1<0>();
         w2 = pf.src.load2<0>();
     }
     wb_mma_all<NBP>(acc, A0, xb);
     wb_ldx_all<SBASE, NBP, 3>(xb, x_off, base, diag);
     wb_mma_all<NBP>(acc, A1, xb);
-    if (pf.valid) pf.advance();
+    if (NEXT_IMM < 0 && pf.valid) pf.advance();
 }
 
 // ---- compute warps --------------------------------------------------------------------------------
@@ -112,18 +119,24 @@ __device__ __forceinline__ void wb_compute(const SkArgs &a, uint8_t *smem, uint3
     for (int p = 0; p < NBP; p++) xb[p] = make_uint4(0, 0, 0, 0);
     float acc[NBP][2][4];
     static_assert(WB_PF == 2, "the ring below has two slots");
+    // Three or four sequence pairs: stages are short (48..64 chunks), so the two chunks in flight are
+    // requested continuously over the stages (slot 0 holds the chunk consumed next).  One or two
+    // pairs: stages are long and the cheaper per-stage ring is used.
+    constexpr bool CONT = NBP > 2;
     WsWalk walk;
     walk.init(u_begin, u_end, nc, Geo::SC);
-    // two chunks in flight, continuously over the stages: slot 0 holds the chunk consumed next
     WsPrefetch pf;
-    pf.init(&a, u_begin, u_end, Geo::SC, cw, Geo::NC, lane);
+    pf.valid = false;
     uint4 q1[2], q2[2];
+    if (CONT) {
+        pf.init(&a, u_begin, u_end, Geo::SC, cw, Geo::NC, lane);
 #pragma unroll
-    for (int i = 0; i < 2; i++) {
-        if (pf.valid) {
-            q1[i] = pf.src.load1<0>();
-            q2[i] = pf.src.load2<0>();
-            pf.advance();
+        for (int i = 0; i < 2; i++) {
+            if (pf.valid) {
+                q1[i] = pf.src.load1<0>();
+                q2[i] = pf.src.load2<0>();
+                pf.advance();
+            }
         }
     }
     uint32_t segs_done = 0;
@@ -132,6 +145,17 @@ __device__ __forceinline__ void wb_compute(const SkArgs &a, uint8_t *smem, uint3
         const uint32_t xbuf = t & 1, par = (t >> 1) & 1, tb = st.seg & 1;
         const uint32_t span = st.pe - st.pb;
         const uint32_t nj = span > cw ? (span - cw + Geo::NC - 1) / Geo::NC : 0;  // this warp: chunks pb + cw + NC*j
+        SkSrcPtr src;
+        src.p = nullptr; src.d2 = 0;
+        if (!CONT) {
+            const uint32_t hb1 = a.hb_mul * st.blk, hb2 = hb1 + a.hb_add2;
+            src.p = a.idx1 + ((size_t)hb1 * nc + st.pb + cw) * 512 + lane * 16;
+            src.d2 = (uint64_t)(reinterpret_cast<uintptr_t>(a.idx2 + ((size_t)hb2 * nc + st.pb + cw) * 512 + lane * 16) -
+                                reinterpret_cast<uintptr_t>(src.p));
+            if (0 < nj) { q1[0] = src.load1<0>(); q2[0] = src.load2<0>(); }
+            if (1 < nj) { q1[1] = src.load1<Geo::NC * 512>(); q2[1] = src.load2<Geo::NC * 512>(); }
+            src.advance(2 * Geo::NC * 512);  // from here on: the chunk two steps ahead
+        }
         if (st.first) {
 #pragma unroll
             for (int p = 0; p < NBP; p++)
@@ -147,15 +171,27 @@ __device__ __forceinline__ void wb_compute(const SkArgs &a, uint8_t *smem, uint3
 #endif
         const uint32_t lane_off = lane * 4 | (tb << 16);
         uint32_t x_off = xbuf * WB_X_BYTES + (lane >> 4) * Geo::ROW_BYTES + cw * 64;
-        for (uint32_t j = 0; j < nj; j += 2) {
-            wb_chunk<SBASE, NBP>(acc, q1[0], q2[0], xb, lane_off, x_off, diag, smem_base, pf);
-            if (j + 1 < nj) wb_chunk<SBASE, NBP>(acc, q1[1], q2[1], xb, lane_off, x_off + Geo::NC * 64, diag, smem_base, pf);
-            x_off += 2 * Geo::NC * 64;
-        }
-        if (nj & 1) {  // an odd count leaves the next chunk in slot 1: rotate the ring
-            const uint4 t1 = q1[0], t2 = q2[0];
-            q1[0] = q1[1]; q2[0] = q2[1];
-            q1[1] = t1; q2[1] = t2;
+        if (CONT) {
+            for (uint32_t j = 0; j < nj; j += 2) {
+                wb_chunk<SBASE, NBP, -1>(acc, q1[0], q2[0], xb, lane_off, x_off, diag, smem_base, pf, src, false);
+                if (j + 1 < nj)
+                    wb_chunk<SBASE, NBP, -1>(acc, q1[1], q2[1], xb, lane_off, x_off + Geo::NC * 64, diag, smem_base, pf, src, false);
+                x_off += 2 * Geo::NC * 64;
+            }
+            if (nj & 1) {  // an odd count leaves the next chunk in slot 1: rotate the ring
+                const uint4 t1 = q1[0], t2 = q2[0];
+                q1[0] = q1[1]; q2[0] = q2[1];
+                q1[1] = t1; q2[1] = t2;
+            }
+        } else {
+            for (uint32_t j = 0; j < nj; j += 2) {
+                wb_chunk<SBASE, NBP, 0>(acc, q1[0], q2[0], xb, lane_off, x_off, diag, smem_base, pf, src, j + 2 < nj);
+                if (j + 1 < nj)
+                    wb_chunk<SBASE, NBP, Geo::NC * 512>(acc, q1[1], q2[1], xb, lane_off, x_off + Geo::NC * 64, diag, smem_base,
+                                                        pf, src, j + 3 < nj);
+                x_off += 2 * Geo::NC * 64;
+                src.advance(2 * Geo::NC * 512);
+            }
         }
         if (st.last) {
             // the builders have read the sums of the segment before this one

@@ -154,20 +154,23 @@ def test_batched_sequences_match_single(oracle):
     eng.close(); be.close()
 
 
-def test_batch8_goes_through_the_gemm_and_matches_the_oracle(oracle):
-    """Eight sequences per step: every linear is one tensor-core GEMM over the batch; tokens of each sequence
-    must still be the oracle's."""
+@pytest.mark.parametrize("batch_gemv_max,batch", [(8, 8), (1, 8), (8, 5), (8, 11)])
+def test_batched_decode_matches_the_oracle(oracle, batch_gemv_max, batch):
+    """Several sequences per step.  Up to `batch_gemv_max` sequences every linear is one pass of the batched
+    GEMV (groups of 8 beyond that), above it one tensor-core GEMM over the batch; tokens of each sequence must
+    still be the oracle's."""
     cfg = dict(TINY, hidden_size=128, intermediate_size=256, head_dim=32, vocab_size=1024)
     be = p.CudaBackend(device=0)
-    mc = p.model_config(**cfg, max_seq=64, max_batch=8, profile="baseline")
+    be.set_option("batch_gemv_max", batch_gemv_max)
+    mc = p.model_config(**cfg, max_seq=64, max_batch=batch, profile="baseline")
     eng = p.PrismEngine(be, mc)
     eng.synth_weights(seed=13)
-    prompts = np.stack([synth.make_prompt(5, cfg["vocab_size"], seed=s) for s in range(8)])
+    prompts = np.stack([synth.make_prompt(5, cfg["vocab_size"], seed=s) for s in range(batch)])
     l0 = be.launch_count()
     got = eng.generate(prompts, 33)
     assert be.launch_count() > l0
     twin = oracle_twin(oracle, be, cfg, mc)
-    for b in (0, 3, 7):
+    for b in (0, 3, batch - 1):
         want, margins = twin.generate(prompts[b], 33)
         assert np.array_equal(got[b][:32], want[:32]), (b, float(margins.min()))
     eng.close(); twin.close(); be.close()
