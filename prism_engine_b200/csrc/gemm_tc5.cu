@@ -26,16 +26,23 @@ constexpr int GM_THREADS = 18 * 32;
 constexpr int GM_NT_MAX = 256;                // largest token tile = N of the MMA (template parameter NT <= 256)
 constexpr int GM_TBL_BYTES = 2 * 65536;
 constexpr int GM_SA = 8;                      // A stages (16 TMEM columns each)
-constexpr int GM_SX = 4;                      // X stages (256 tokens x 32 k fp16 = 16 KB each)
-constexpr int GM_XSTAGE_BYTES = GM_NT_MAX * 32 * 2;  // stage slot size (a tile of NT tokens uses NT*64 bytes of it)
+constexpr int GM_X_BYTES = 4 * GM_NT_MAX * 32 * 2;   // activation staging area: 64 KB
+constexpr int GM_SX_MAX = 32;                 // most X stages (small token tiles): a stage is NT tokens x 32 k fp16 = NT*64 bytes
+// X stages for a token tile of NT: as many as fit the staging area, at most GM_SX_MAX.  Small tiles
+// need the depth: a stage is refilled by a bulk copy whose latency is the same whatever its size.
+template <int NT>
+struct GmX {
+    static constexpr int SX = (GM_X_BYTES / (NT * 64)) < GM_SX_MAX ? (GM_X_BYTES / (NT * 64)) : GM_SX_MAX;
+    static constexpr int STAGE_BYTES = NT * 64;
+};
 constexpr int GM_D_COL = GM_SA * 16;          // accumulator: 256 columns after the A stages
 constexpr int GM_TMEM_COLS = 512;
 constexpr int GM_PF = 4;
 constexpr int GM_SBASE = 1024;
 constexpr int GM_X_OFF = GM_TBL_BYTES;
-constexpr int GM_BAR_OFF = GM_X_OFF + GM_SX * GM_XSTAGE_BYTES;
+constexpr int GM_BAR_OFF = GM_X_OFF + GM_X_BYTES;
 // barriers (8 B each): afull[SA], aempty[SA], xfull[SX], xempty[SX], dfull, dempty
-constexpr int GM_STATE_OFF = GM_BAR_OFF + 8 * (2 * GM_SA + 2 * GM_SX + 2);
+constexpr int GM_STATE_OFF = GM_BAR_OFF + 8 * (2 * GM_SA + 2 * GM_SX_MAX + 2);
 constexpr size_t GM_SMEM_BYTES = GM_STATE_OFF + 64;
 
 struct GemmArgs {
@@ -79,7 +86,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t bar = smem_base + GM_BAR_OFF;
     const uint32_t b_afull = bar, b_aempty = bar + 8 * GM_SA, b_xfull = bar + 16 * GM_SA,
-                   b_xempty = b_xfull + 8 * GM_SX, b_dfull = b_xempty + 8 * GM_SX, b_dempty = b_dfull + 8;
+                   b_xempty = b_xfull + 8 * GM_SX_MAX, b_dfull = b_xempty + 8 * GM_SX_MAX, b_dempty = b_dfull + 8;
+    constexpr int SX = GmX<NT>::SX, XSTAGE = GmX<NT>::STAGE_BYTES;
     volatile uint32_t *err_flag = reinterpret_cast<volatile uint32_t *>(smem + GM_STATE_OFF);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + GM_STATE_OFF + 8);
     const uint32_t nch = a.n_chunks;
@@ -87,7 +95,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
 
     if (tid == 0) {
         for (int s = 0; s < GM_SA; s++) { t5::mbar_init(b_afull + 8 * s, 4); t5::mbar_init(b_aempty + 8 * s, 1); }
-        for (int s = 0; s < GM_SX; s++) { t5::mbar_init(b_xfull + 8 * s, 1); t5::mbar_init(b_xempty + 8 * s, 1); }
+        for (int s = 0; s < SX; s++) { t5::mbar_init(b_xfull + 8 * s, 1); t5::mbar_init(b_xempty + 8 * s, 1); }
         t5::mbar_init(b_dfull, 1);
         t5::mbar_init(b_dempty, GM_DEQ_WARPS);
         *err_flag = 0;
@@ -212,11 +220,11 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
             t5::fence_after();
             const uint32_t dcol = tmem_base + GM_D_COL;
             for (uint32_t c = 0; c < nch; c++, n++) {
-                const uint32_t sa = n % GM_SA, pa = (n / GM_SA) & 1, sx = n % GM_SX, px = (n / GM_SX) & 1;
+                const uint32_t sa = n % GM_SA, pa = (n / GM_SA) & 1, sx = n % SX, px = (n / SX) & 1;
                 t5::mbar_wait_bounded(b_xfull + 8 * sx, px, err_flag);
                 t5::mbar_wait_bounded(b_afull + 8 * sa, pa, err_flag);
                 t5::fence_after();
-                const uint32_t acol = tmem_base + sa * 16, xs = x_addr + sx * GM_XSTAGE_BYTES;
+                const uint32_t acol = tmem_base + sa * 16, xs = x_addr + sx * XSTAGE;
                 // B: NT tokens x 16 k; core matrices of 8 tokens are 128 B apart, k-blocks of 8 are NT*16 B apart
                 t5::mma_ts(dcol, acol, t5::smem_desc(xs, NT * 16, 128), idesc, c > 0);
                 t5::mma_ts(dcol, acol + 8, t5::smem_desc(xs + 2 * NT * 16, NT * 16, 128), idesc, 1);
@@ -233,12 +241,12 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
             const uint32_t tt = w / a.n_rt;
             const uint8_t *src0 = a.xc + (size_t)tt * NT * 16;
             for (uint32_t c = 0; c < nch; c++, n++) {
-                const uint32_t sx = n % GM_SX, px = (n / GM_SX) & 1;
+                const uint32_t sx = n % SX, px = (n / SX) & 1;
                 t5::mbar_wait_bounded(b_xempty + 8 * sx, px ^ 1, err_flag);
                 t5::mbar_arrive_expect_tx(b_xfull + 8 * sx, NT * 64);
 #pragma unroll
                 for (int kb = 0; kb < 4; kb++)
-                    t5::bulk_g2s(x_addr + sx * GM_XSTAGE_BYTES + kb * NT * 16,
+                    t5::bulk_g2s(x_addr + sx * XSTAGE + kb * NT * 16,
                                  src0 + (size_t)(4 * c + kb) * a.m_tok_pad * 16, NT * 16, b_xfull + 8 * sx);
             }
         }
