@@ -51,18 +51,24 @@ struct GemmArgs {
     uint32_t n_chunks, n_hb, m;       // chunks per row (K/32), half-blocks, valid weight rows
     uint32_t n_rt, n_tt;              // row tiles (128 rows), token tiles (256 tokens)
     uint32_t m_tok, m_tok_pad;
-    const uint8_t *xc;                // [K/8][m_tok_pad][16 B]
+    const uint8_t *xc;                // [token tile][K/8][NT][16 B]
     uint16_t *y;                      // [m_tok][m]
     unsigned int *err;
 };
 
-// X [m_tok][k] fp16 -> Xc [k/8][m_tok_pad][8]; padded token rows are zero.
+// X [m_tok][k] fp16 -> Xc [token tile][k/8][nt][8]: the 32 k of one chunk for the nt tokens of one
+// tile are one contiguous run of nt*64 bytes, already in the order the shared-memory B operand
+// wants (k-blocks of 8, then tokens), so a stage is filled by ONE bulk copy.  Padded token rows are
+// zero.
 __global__ void gemm_relay_x_kernel(const uint16_t *__restrict__ x, uint32_t m_tok, uint32_t m_tok_pad, uint32_t k,
-                                    uint4 *__restrict__ xc) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t total = (size_t)(k / 8) * m_tok_pad;
-    if (i >= total) return;
-    const uint32_t t = (uint32_t)(i % m_tok_pad), k8 = (uint32_t)(i / m_tok_pad);
+                                    uint32_t nt, uint4 *__restrict__ xc) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // index into the output
+    const size_t k8n = k / 8;
+    if (i >= k8n * m_tok_pad) return;
+    const uint32_t tin = (uint32_t)(i % nt);
+    const size_t rest = i / nt;
+    const uint32_t k8 = (uint32_t)(rest % k8n), tt = (uint32_t)(rest / k8n);
+    const uint32_t t = tt * nt + tin;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (t < m_tok) v = *reinterpret_cast<const uint4 *>(x + (size_t)t * k + (size_t)k8 * 8);
     xc[i] = v;
@@ -239,15 +245,12 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
         uint32_t n = 0;
         for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x) {
             const uint32_t tt = w / a.n_rt;
-            const uint8_t *src0 = a.xc + (size_t)tt * NT * 16;
+            const uint8_t *src0 = a.xc + (size_t)tt * nch * NT * 64;
             for (uint32_t c = 0; c < nch; c++, n++) {
                 const uint32_t sx = n % SX, px = (n / SX) & 1;
                 t5::mbar_wait_bounded(b_xempty + 8 * sx, px ^ 1, err_flag);
                 t5::mbar_arrive_expect_tx(b_xfull + 8 * sx, NT * 64);
-#pragma unroll
-                for (int kb = 0; kb < 4; kb++)
-                    t5::bulk_g2s(x_addr + sx * XSTAGE + kb * NT * 16,
-                                 src0 + (size_t)(4 * c + kb) * a.m_tok_pad * 16, NT * 16, b_xfull + 8 * sx);
+                t5::bulk_g2s(x_addr + sx * XSTAGE, src0 + (size_t)c * NT * 64, NT * 64, b_xfull + 8 * sx);
             }
         }
     }
@@ -273,11 +276,11 @@ static int launch_gemm_nt(prism_cuda_ctx *ctx, GemmArgs &a, const LutTensor &t, 
     }
     a.m_tok_pad = round_up_u32(a.m_tok, NT);
     a.n_tt = a.m_tok_pad / NT;
-    // X -> [k/8][token][8] (context scratch)
+    // X -> [token tile][k/8][NT][8] (context scratch)
     const size_t xc_halfs = (size_t)t.k * a.m_tok_pad;
     PRISM_TRY(ensure_tmp(ctx, xc_halfs));
     const size_t units = xc_halfs / 8;
-    gemm_relay_x_kernel<<<(unsigned)((units + 255) / 256), 256, 0, ctx->stream>>>(X, a.m_tok, a.m_tok_pad, t.k,
+    gemm_relay_x_kernel<<<(unsigned)((units + 255) / 256), 256, 0, ctx->stream>>>(X, a.m_tok, a.m_tok_pad, t.k, (uint32_t)NT,
                                                                                 reinterpret_cast<uint4 *>(ctx->tmp_scratch));
     PRISM_TRY(after_launch(ctx, "gemm_relay_x_kernel"));
     a.xc = reinterpret_cast<const uint8_t *>(ctx->tmp_scratch);
