@@ -25,17 +25,23 @@ constexpr int GM_MMA_WARP = 16, GM_X_WARP = 17;
 constexpr int GM_THREADS = 18 * 32;
 constexpr int GM_NT_MAX = 256;                // largest token tile = N of the MMA (template parameter NT <= 256)
 constexpr int GM_TBL_BYTES = 2 * 65536;
-constexpr int GM_SA = 8;                      // A stages (16 TMEM columns each)
+// A pipeline stage is CPS index chunks (32 k each): the hand-over between the dequantising warps,
+// the MMA thread and the activation loader costs a few hundred cycles of single-thread control
+// whatever the stage holds, so small token tiles (cheap MMAs) take four chunks per stage, large
+// ones two.  The A operand occupies 256 TMEM columns either way (16 per chunk).
+constexpr int GM_SA = 8;                      // most A stages (two chunks each)
+constexpr int GM_D_COL = 256;                 // accumulator: up to 256 columns after the A stages
 constexpr int GM_X_BYTES = 4 * GM_NT_MAX * 32 * 2;   // activation staging area: 64 KB
 constexpr int GM_SX_MAX = 32;                 // most X stages (small token tiles): a stage is NT tokens x 32 k fp16 = NT*64 bytes
 // X stages for a token tile of NT: as many as fit the staging area, at most GM_SX_MAX.  Small tiles
 // need the depth: a stage is refilled by a bulk copy whose latency is the same whatever its size.
 template <int NT>
 struct GmX {
-    static constexpr int SX = (GM_X_BYTES / (NT * 64)) < GM_SX_MAX ? (GM_X_BYTES / (NT * 64)) : GM_SX_MAX;
-    static constexpr int STAGE_BYTES = NT * 64;
+    static constexpr int CPS = NT <= 64 ? 4 : 2;              // chunks per stage
+    static constexpr int SA = GM_D_COL / (16 * CPS);          // A stages: 4 or 8
+    static constexpr int STAGE_BYTES = NT * 64 * CPS;
+    static constexpr int SX = (GM_X_BYTES / STAGE_BYTES) < GM_SX_MAX ? (GM_X_BYTES / STAGE_BYTES) : GM_SX_MAX;
 };
-constexpr int GM_D_COL = GM_SA * 16;          // accumulator: 256 columns after the A stages
 constexpr int GM_TMEM_COLS = 512;
 constexpr int GM_PF = 4;
 constexpr int GM_SBASE = 1024;
@@ -93,14 +99,14 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
     const uint32_t bar = smem_base + GM_BAR_OFF;
     const uint32_t b_afull = bar, b_aempty = bar + 8 * GM_SA, b_xfull = bar + 16 * GM_SA,
                    b_xempty = b_xfull + 8 * GM_SX_MAX, b_dfull = b_xempty + 8 * GM_SX_MAX, b_dempty = b_dfull + 8;
-    constexpr int SX = GmX<NT>::SX, XSTAGE = GmX<NT>::STAGE_BYTES;
+    constexpr int SX = GmX<NT>::SX, XSTAGE = GmX<NT>::STAGE_BYTES, CPS = GmX<NT>::CPS, SA = GmX<NT>::SA;
     volatile uint32_t *err_flag = reinterpret_cast<volatile uint32_t *>(smem + GM_STATE_OFF);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + GM_STATE_OFF + 8);
     const uint32_t nch = a.n_chunks;
     const uint32_t n_items = a.n_rt * a.n_tt;  // item w: row tile w % n_rt, token tile w / n_rt
 
     if (tid == 0) {
-        for (int s = 0; s < GM_SA; s++) { t5::mbar_init(b_afull + 8 * s, 4); t5::mbar_init(b_aempty + 8 * s, 1); }
+        for (int s = 0; s < SA; s++) { t5::mbar_init(b_afull + 8 * s, 4); t5::mbar_init(b_aempty + 8 * s, 1); }
         for (int s = 0; s < SX; s++) { t5::mbar_init(b_xfull + 8 * s, 1); t5::mbar_init(b_xempty + 8 * s, 1); }
         t5::mbar_init(b_dfull, 1);
         t5::mbar_init(b_dempty, GM_DEQ_WARPS);
@@ -128,8 +134,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
             const uint8_t *sp = a.idx + (size_t)h * nch * 512 + lane * 16;
             uint4 r[GM_PF];
 #pragma unroll
-            for (int i = 0; i < GM_PF; i++) {
-                const uint32_t c = j + 4 * i;
+            for (int i = 0; i < GM_PF; i++) {  // r[i]: chunk (i % CPS) of this warp's stage number i / CPS
+                const uint32_t c = (j + 4 * (i / CPS)) * CPS + (i % CPS);
                 if (c < nch) r[i] = t5::ldg128_nc(sp + (size_t)c * 512);
             }
             if (rt != cur_rt) {  // same decision in all warps: they walk the same item list
@@ -154,44 +160,51 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
                 asm volatile("bar.sync %0, 256;\n" ::"r"(1 + pair) : "memory");
             }
             // ---- K loop: lookups -> TMEM stage -> signal the MMA thread ----
-            for (uint32_t c0 = j; c0 < nch; c0 += 4 * GM_PF) {
+            // a stage is CPS consecutive chunks; warp slot j takes the stages j, j+4, ...
+            const uint32_t nst = nch / CPS;
+            for (uint32_t s0 = j; s0 < nst; s0 += 4 * (GM_PF / CPS)) {
 #pragma unroll
-                for (int i = 0; i < GM_PF; i++) {
-                    const uint32_t c = c0 + 4 * i;
-                    if (c < nch) {
-                        const uint4 wv = r[i];
-                        const uint32_t nc = c + 4 * GM_PF;
-                        if (nc < nch) r[i] = t5::ldg128_nc(sp + (size_t)nc * 512);
-                        const uint32_t aw[4] = {wv.x, wv.y, wv.z, wv.w};
-                        uint32_t A[16];
-                        if (slot == 0) {
+                for (int i = 0; i < GM_PF / CPS; i++) {
+                    const uint32_t su = s0 + 4 * i;
+                    if (su < nst) {
+                        uint32_t A[CPS][16];
 #pragma unroll
-                            for (int hh = 0; hh < 4; hh++) {
-                                A[4 * hh + 0] = gm_lds(__byte_perm(aw[hh], laneq, 0x7604), 0);
-                                A[4 * hh + 1] = gm_lds(__byte_perm(aw[hh], laneq, 0x7614), 0);
-                                A[4 * hh + 2] = gm_lds(__byte_perm(aw[hh], laneq, 0x7624), 0);
-                                A[4 * hh + 3] = gm_lds(__byte_perm(aw[hh], laneq, 0x7634), 0);
-                            }
-                        } else {
+                        for (int cc = 0; cc < CPS; cc++) {
+                            const uint32_t c = su * CPS + cc;
+                            const uint4 wv = r[i * CPS + cc];
+                            const uint32_t nc = c + 4 * GM_PF;
+                            if (nc < nch) r[i * CPS + cc] = t5::ldg128_nc(sp + (size_t)nc * 512);
+                            const uint32_t aw[4] = {wv.x, wv.y, wv.z, wv.w};
+                            if (slot == 0) {
 #pragma unroll
-                            for (int hh = 0; hh < 4; hh++) {
-                                A[4 * hh + 0] = gm_lds(__byte_perm(aw[hh], laneq, 0x7604), 1);
-                                A[4 * hh + 1] = gm_lds(__byte_perm(aw[hh], laneq, 0x7614), 1);
-                                A[4 * hh + 2] = gm_lds(__byte_perm(aw[hh], laneq, 0x7624), 1);
-                                A[4 * hh + 3] = gm_lds(__byte_perm(aw[hh], laneq, 0x7634), 1);
+                                for (int hh = 0; hh < 4; hh++) {
+                                    A[cc][4 * hh + 0] = gm_lds(__byte_perm(aw[hh], laneq, 0x7604), 0);
+                                    A[cc][4 * hh + 1] = gm_lds(__byte_perm(aw[hh], laneq, 0x7614), 0);
+                                    A[cc][4 * hh + 2] = gm_lds(__byte_perm(aw[hh], laneq, 0x7624), 0);
+                                    A[cc][4 * hh + 3] = gm_lds(__byte_perm(aw[hh], laneq, 0x7634), 0);
+                                }
+                            } else {
+#pragma unroll
+                                for (int hh = 0; hh < 4; hh++) {
+                                    A[cc][4 * hh + 0] = gm_lds(__byte_perm(aw[hh], laneq, 0x7604), 1);
+                                    A[cc][4 * hh + 1] = gm_lds(__byte_perm(aw[hh], laneq, 0x7614), 1);
+                                    A[cc][4 * hh + 2] = gm_lds(__byte_perm(aw[hh], laneq, 0x7624), 1);
+                                    A[cc][4 * hh + 3] = gm_lds(__byte_perm(aw[hh], laneq, 0x7634), 1);
+                                }
                             }
                         }
-                        const uint32_t n = n_base + c, stage = n % GM_SA, ph = (n / GM_SA) & 1;
+                        const uint32_t n = n_base + su, stage = n % SA, ph = (n / SA) & 1;
                         t5::mbar_wait_warp(b_aempty + 8 * stage, ph ^ 1, err_flag);
                         t5::fence_after();
-                        t5::st16(tmem_lane + stage * 16, A);
+#pragma unroll
+                        for (int cc = 0; cc < CPS; cc++) t5::st16(tmem_lane + stage * 16 * CPS + cc * 16, A[cc]);
                         t5::wait_st();
                         t5::fence_before();
                         if (lane == 0) t5::mbar_arrive(b_afull + 8 * stage);
                     }
                 }
             }
-            n_base += nch;
+            n_base += nst;
             // ---- epilogue: warp (q, j) converts token columns [64j, 64j+64) of its 32 rows ----
             t5::mbar_wait_warp(b_dfull, ti & 1, err_flag);
             t5::fence_after();
@@ -225,15 +238,18 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
             t5::mbar_wait_bounded(b_dempty, (ti & 1) ^ 1, err_flag);  // epilogue of the previous tile has read D
             t5::fence_after();
             const uint32_t dcol = tmem_base + GM_D_COL;
-            for (uint32_t c = 0; c < nch; c++, n++) {
-                const uint32_t sa = n % GM_SA, pa = (n / GM_SA) & 1, sx = n % SX, px = (n / SX) & 1;
+            for (uint32_t su = 0; su < nch / CPS; su++, n++) {
+                const uint32_t sa = n % SA, pa = (n / SA) & 1, sx = n % SX, px = (n / SX) & 1;
                 t5::mbar_wait_bounded(b_xfull + 8 * sx, px, err_flag);
                 t5::mbar_wait_bounded(b_afull + 8 * sa, pa, err_flag);
                 t5::fence_after();
-                const uint32_t acol = tmem_base + sa * 16, xs = x_addr + sx * XSTAGE;
+                const uint32_t acol = tmem_base + sa * 16 * CPS, xs = x_addr + sx * XSTAGE;
                 // B: NT tokens x 16 k; core matrices of 8 tokens are 128 B apart, k-blocks of 8 are NT*16 B apart
-                t5::mma_ts(dcol, acol, t5::smem_desc(xs, NT * 16, 128), idesc, c > 0);
-                t5::mma_ts(dcol, acol + 8, t5::smem_desc(xs + 2 * NT * 16, NT * 16, 128), idesc, 1);
+#pragma unroll
+                for (int cc = 0; cc < CPS; cc++) {
+                    t5::mma_ts(dcol, acol + cc * 16, t5::smem_desc(xs + cc * NT * 64, NT * 16, 128), idesc, (su | cc) != 0);
+                    t5::mma_ts(dcol, acol + cc * 16 + 8, t5::smem_desc(xs + cc * NT * 64 + 2 * NT * 16, NT * 16, 128), idesc, 1);
+                }
                 t5::commit(b_aempty + 8 * sa);
                 t5::commit(b_xempty + 8 * sx);
             }
@@ -246,11 +262,11 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
         for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x) {
             const uint32_t tt = w / a.n_rt;
             const uint8_t *src0 = a.xc + (size_t)tt * nch * NT * 64;
-            for (uint32_t c = 0; c < nch; c++, n++) {
+            for (uint32_t su = 0; su < nch / CPS; su++, n++) {
                 const uint32_t sx = n % SX, px = (n / SX) & 1;
                 t5::mbar_wait_bounded(b_xempty + 8 * sx, px ^ 1, err_flag);
-                t5::mbar_arrive_expect_tx(b_xfull + 8 * sx, NT * 64);
-                t5::bulk_g2s(x_addr + sx * XSTAGE, src0 + (size_t)c * NT * 64, NT * 64, b_xfull + 8 * sx);
+                t5::mbar_arrive_expect_tx(b_xfull + 8 * sx, XSTAGE);
+                t5::bulk_g2s(x_addr + sx * XSTAGE, src0 + (size_t)su * XSTAGE, XSTAGE, b_xfull + 8 * sx);
             }
         }
     }
@@ -263,7 +279,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
 // ---- host side ---------------------------------------------------------------------------------
 
 bool gemm_tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t m_tok) {
-    return ctx->smem_base == GM_SBASE && t.bits == 4 && t.k % 32 == 0 && t.k >= 64 && m_tok >= 8;
+    return ctx->smem_base == GM_SBASE && t.bits == 4 && t.k % 128 == 0 && m_tok >= 8;  // whole stages of two or four chunks
 }
 
 template <int NT>
