@@ -65,7 +65,7 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
  * prefill GEMM, default; 0 = activation rows through the GEMV kernel), "fuse" (0/1,
  * default 1: fused epilogues), "pdl" (0/1, default 1: programmatic dependent launch between
  * the kernels of a decode step, so a kernel's weight-only prologue overlaps its predecessor),
- * "batch_gemv_max" (default 24: decode batches up to this many sequences stream the weights once
+ * "batch_gemv_max" (default 8: decode batches up to this many sequences stream the weights once
  * through the batched GEMV, in groups of 8; larger batches use the tcgen05 GEMM),
  * "attn_cluster" (0 = from max_seq, default; 1/2/4/8 CTAs per head and sequence in the fused
  * attention kernel),

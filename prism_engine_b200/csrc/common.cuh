@@ -71,7 +71,7 @@ struct prism_cuda_ctx {
     int fuse = 1;
     int sk_min_chunks = 8;      // stream-K GEMV, small matrices: fewest 1 KB index chunks a CTA is given
     int sk_stream_chunks = 64;  // chunks per CTA from which the balanced contiguous partition is used
-    int batch_gemv_max = 24;  // decode batches up to this size use the batched GEMV (groups of 8), larger ones the GEMM
+    int batch_gemv_max = 8;   // decode batches up to this size use the batched GEMV (groups of 8), larger ones the GEMM
     int attn_cluster = 0;    // CTAs per (head, sequence) of the fused attention kernel; 0: chosen from max_seq
     int pdl = 1;  // programmatic dependent launch between the kernels of the decode chain
     uint64_t launches = 0;
