@@ -73,6 +73,7 @@ struct prism_cuda_ctx {
     int sk_stream_chunks = 64;  // chunks per CTA from which the balanced contiguous partition is used
     int batch_gemv_max = 8;   // decode batches up to this size use the batched GEMV (groups of 8), larger ones the GEMM
     int attn_cluster = 0;    // CTAs per (head, sequence) of the fused attention kernel; 0: chosen from max_seq
+    int gemm_reuse_x = 0;    // set by a caller for the second of two GEMMs over the same activations: skip the re-lay
     int pdl = 1;  // programmatic dependent launch between the kernels of the decode chain
     uint64_t launches = 0;
     // staging for host-pointer entry points (grown on demand)

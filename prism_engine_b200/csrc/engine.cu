@@ -168,6 +168,7 @@ static int linear(prism_cuda_engine *e, GemvMode mode, const LutTensor &t, const
     if (mode == GEMV_PLAIN) return launch_gemm(ctx, t, x, B, y);
     if (mode == GEMV_RESID) {  // y (== resid, in place) = f16( f16(W x) + resid )
         PRISM_TRY(launch_gemm(ctx, t, x, B, e->gu));
+        if (y == resid) return launch_vec_add(ctx, y, e->gu, B * t.m);  // in place: the add commutes
         PRISM_TRY(launch_vec_add(ctx, e->gu, resid, B * t.m));
         PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(y, e->gu, (size_t)B * t.m * 2, cudaMemcpyDeviceToDevice, ctx->stream));
         return PRISM_OK;
@@ -175,7 +176,10 @@ static int linear(prism_cuda_engine *e, GemvMode mode, const LutTensor &t, const
     // SwiGLU: gate and up GEMMs, then f16(f16(silu(g)) * u)
     uint16_t *g = e->gu, *u = e->gu + (size_t)B * t.m;
     PRISM_TRY(launch_gemm(ctx, t, x, B, g));
-    PRISM_TRY(launch_gemm(ctx, *t2, x, B, u));
+    ctx->gemm_reuse_x = 1;  // same activations, same token tile: the re-laid copy is still in scratch
+    const int rc_up = launch_gemm(ctx, *t2, x, B, u);
+    ctx->gemm_reuse_x = 0;
+    PRISM_TRY(rc_up);
     return launch_silu_mul(ctx, y, g, u, B * t.m);
 }
 

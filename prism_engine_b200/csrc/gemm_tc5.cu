@@ -296,9 +296,11 @@ static int launch_gemm_nt(prism_cuda_ctx *ctx, GemmArgs &a, const LutTensor &t, 
     const size_t xc_halfs = (size_t)t.k * a.m_tok_pad;
     PRISM_TRY(ensure_tmp(ctx, xc_halfs));
     const size_t units = xc_halfs / 8;
-    gemm_relay_x_kernel<<<(unsigned)((units + 255) / 256), 256, 0, ctx->stream>>>(X, a.m_tok, a.m_tok_pad, t.k, (uint32_t)NT,
-                                                                                reinterpret_cast<uint4 *>(ctx->tmp_scratch));
-    PRISM_TRY(after_launch(ctx, "gemm_relay_x_kernel"));
+    if (!ctx->gemm_reuse_x) {
+        gemm_relay_x_kernel<<<(unsigned)((units + 255) / 256), 256, 0, ctx->stream>>>(X, a.m_tok, a.m_tok_pad, t.k, (uint32_t)NT,
+                                                                                    reinterpret_cast<uint4 *>(ctx->tmp_scratch));
+        PRISM_TRY(after_launch(ctx, "gemm_relay_x_kernel"));
+    }
     a.xc = reinterpret_cast<const uint8_t *>(ctx->tmp_scratch);
     // one row tile per CTA when possible, so its tables are built once
     const uint32_t G = (uint32_t)ctx->sm_count;
