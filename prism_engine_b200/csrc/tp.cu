@@ -81,16 +81,17 @@ int tp_all_gather_bytes(prism_cuda_ctx *ctx, const void *send, void *recv, size_
 // every rank because every rank runs the same kernel sequence) works in independent slices, one
 // per CTA: CTA c of rank r stores its slice of the partial sums into slot [e & 1][r] of EVERY rank's
 // receive area (plain stores over NVLink), makes them visible (fence at system scope) and writes e
-// into flag [r][c] of every rank; it then waits until its own flags [0..world)[c] all hold e and adds
+// into flag [r][c] of every rank; it then waits until its own flags [0..world)[c] all hold e (or more: a
+// peer can be one all-reduce ahead) and adds
 // the `world` slices of its own receive area in rank order, so every rank computes bit-identical
 // sums.  Two slots are enough: a rank can only start e+2 after every peer has delivered e+1, which a
 // peer does only after it finished reading e.  The wait is bounded; when it gives up it sets the
 // context's error word and the step goes on with whatever arrived.
 // ---------------------------------------------------------------------------------------------
-constexpr int TP_AR_MAX_CTAS = 64;
+constexpr int TP_AR_MAX_CTAS = 256;
 constexpr int TP_AR_THREADS = 256;
-constexpr size_t TP_AR_CAP_FLOATS = 64 * 1024;     // largest vector the peer path takes (256 KB per slot)
-constexpr unsigned int TP_AR_SPIN_LIMIT = 1u << 22;  // polls with back-off: about two seconds
+constexpr size_t TP_AR_CAP_FLOATS = 256 * 1024;    // largest vector the peer path takes (1 MB per slot: batch 32 x 8192)
+constexpr unsigned int TP_AR_SPIN_LIMIT = 1u << 25;  // polls with back-off: about fifteen seconds (ranks may start seconds apart)
 
 __global__ void __launch_bounds__(TP_AR_THREADS) tp_ar_resid_kernel(const float *__restrict__ part, uint16_t *h,
                                                                     uint32_t n, void *const *peer_tab,
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(TP_AR_THREADS) tp_ar_resid_kernel(const float 
         unsigned int seen = 0, polls = 0;
         for (;;) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(f) : "memory");
-            if (seen == e) break;
+            if ((int)(seen - e) >= 0) break;  // a peer that is already one all-reduce ahead has delivered this one too
             if (++polls > TP_AR_SPIN_LIMIT) {
                 atomicExch(err, 3u);  // a peer did not deliver: reported by the next host call
                 break;
