@@ -27,8 +27,8 @@ constexpr int GM_NT_MAX = 256;                // largest token tile = N of the M
 constexpr int GM_TBL_BYTES = 2 * 65536;
 // A pipeline stage is CPS index chunks (32 k each): the hand-over between the dequantising warps,
 // the MMA thread and the activation loader costs a few hundred cycles of single-thread control
-// whatever the stage holds, so small token tiles (cheap MMAs) take four chunks per stage, large
-// ones two.  The A operand occupies 256 TMEM columns either way (16 per chunk).
+// whatever the stage holds, so a weight stage is four chunks (the A operand occupies 256 TMEM
+// columns, 16 per chunk); an activation stage is four chunks too, two for 256-token tiles.
 constexpr int GM_SA = 8;                      // most A stages (two chunks each)
 constexpr int GM_D_COL = 256;                 // accumulator: up to 256 columns after the A stages
 constexpr int GM_X_BYTES = 4 * GM_NT_MAX * 32 * 2;   // activation staging area: 64 KB
@@ -37,9 +37,10 @@ constexpr int GM_SX_MAX = 32;                 // most X stages (small token tile
 // need the depth: a stage is refilled by a bulk copy whose latency is the same whatever its size.
 template <int NT>
 struct GmX {
-    static constexpr int CPS = NT <= 64 ? 4 : 2;              // chunks per stage
-    static constexpr int SA = GM_D_COL / (16 * CPS);          // A stages: 4 or 8
-    static constexpr int STAGE_BYTES = NT * 64 * CPS;
+    static constexpr int CPS = 4;                             // chunks per A (weight) stage
+    static constexpr int XC = NT <= 128 ? 4 : 2;              // chunks per X (activation) stage: at most 32 KB
+    static constexpr int SA = GM_D_COL / (16 * CPS);          // A stages: 4
+    static constexpr int STAGE_BYTES = NT * 64 * XC;
     static constexpr int SX = (GM_X_BYTES / STAGE_BYTES) < GM_SX_MAX ? (GM_X_BYTES / STAGE_BYTES) : GM_SX_MAX;
 };
 constexpr int GM_TMEM_COLS = 512;
@@ -99,7 +100,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
     const uint32_t bar = smem_base + GM_BAR_OFF;
     const uint32_t b_afull = bar, b_aempty = bar + 8 * GM_SA, b_xfull = bar + 16 * GM_SA,
                    b_xempty = b_xfull + 8 * GM_SX_MAX, b_dfull = b_xempty + 8 * GM_SX_MAX, b_dempty = b_dfull + 8;
-    constexpr int SX = GmX<NT>::SX, XSTAGE = GmX<NT>::STAGE_BYTES, CPS = GmX<NT>::CPS, SA = GmX<NT>::SA;
+    constexpr int SX = GmX<NT>::SX, XSTAGE = GmX<NT>::STAGE_BYTES, CPS = GmX<NT>::CPS, SA = GmX<NT>::SA, XC = GmX<NT>::XC;
     volatile uint32_t *err_flag = reinterpret_cast<volatile uint32_t *>(smem + GM_STATE_OFF);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + GM_STATE_OFF + 8);
     const uint32_t nch = a.n_chunks;
@@ -233,25 +234,31 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
         // =============================== MMA issuing thread ===============================
         const uint32_t idesc = t5::idesc_f16(128, NT);
         const uint32_t x_addr = smem_base + GM_X_OFF;
-        uint32_t n = 0, ti = 0;
+        uint32_t n = 0, nx = 0, ti = 0;
         for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x, ti++) {
             t5::mbar_wait_bounded(b_dempty, (ti & 1) ^ 1, err_flag);  // epilogue of the previous tile has read D
             t5::fence_after();
             const uint32_t dcol = tmem_base + GM_D_COL;
             for (uint32_t su = 0; su < nch / CPS; su++, n++) {
-                const uint32_t sa = n % SA, pa = (n / SA) & 1, sx = n % SX, px = (n / SX) & 1;
-                t5::mbar_wait_bounded(b_xfull + 8 * sx, px, err_flag);
+                const uint32_t sa = n % SA, pa = (n / SA) & 1;
                 t5::mbar_wait_bounded(b_afull + 8 * sa, pa, err_flag);
-                t5::fence_after();
-                const uint32_t acol = tmem_base + sa * 16 * CPS, xs = x_addr + sx * XSTAGE;
-                // B: NT tokens x 16 k; core matrices of 8 tokens are 128 B apart, k-blocks of 8 are NT*16 B apart
+                const uint32_t acol = tmem_base + sa * 16 * CPS;
 #pragma unroll
-                for (int cc = 0; cc < CPS; cc++) {
-                    t5::mma_ts(dcol, acol + cc * 16, t5::smem_desc(xs + cc * NT * 64, NT * 16, 128), idesc, (su | cc) != 0);
-                    t5::mma_ts(dcol, acol + cc * 16 + 8, t5::smem_desc(xs + cc * NT * 64 + 2 * NT * 16, NT * 16, 128), idesc, 1);
+                for (int xi = 0; xi < CPS / XC; xi++, nx++) {
+                    const uint32_t sx = nx % SX, px = (nx / SX) & 1;
+                    t5::mbar_wait_bounded(b_xfull + 8 * sx, px, err_flag);
+                    t5::fence_after();
+                    const uint32_t xs = x_addr + sx * XSTAGE;
+                    // B: NT tokens x 16 k; core matrices of 8 tokens are 128 B apart, k-blocks of 8 are NT*16 B apart
+#pragma unroll
+                    for (int cc = 0; cc < XC; cc++) {
+                        const uint32_t ac = acol + (xi * XC + cc) * 16;
+                        t5::mma_ts(dcol, ac, t5::smem_desc(xs + cc * NT * 64, NT * 16, 128), idesc, (su | xi | cc) != 0);
+                        t5::mma_ts(dcol, ac + 8, t5::smem_desc(xs + cc * NT * 64 + 2 * NT * 16, NT * 16, 128), idesc, 1);
+                    }
+                    t5::commit(b_xempty + 8 * sx);
                 }
                 t5::commit(b_aempty + 8 * sa);
-                t5::commit(b_xempty + 8 * sx);
             }
             t5::commit(b_dfull);
         }
@@ -262,7 +269,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
         for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x) {
             const uint32_t tt = w / a.n_rt;
             const uint8_t *src0 = a.xc + (size_t)tt * nch * NT * 64;
-            for (uint32_t su = 0; su < nch / CPS; su++, n++) {
+            for (uint32_t su = 0; su < nch / XC; su++, n++) {
                 const uint32_t sx = n % SX, px = (n / SX) & 1;
                 t5::mbar_wait_bounded(b_xempty + 8 * sx, px ^ 1, err_flag);
                 t5::mbar_arrive_expect_tx(b_xfull + 8 * sx, XSTAGE);
