@@ -31,7 +31,7 @@ constexpr int GM_TBL_BYTES = 2 * 65536;
 // columns, 16 per chunk); an activation stage is four chunks too, two for 256-token tiles.
 constexpr int GM_SA = 8;                      // most A stages (two chunks each)
 constexpr int GM_D_COL = 256;                 // accumulator: up to 256 columns after the A stages
-constexpr int GM_X_BYTES = 4 * GM_NT_MAX * 32 * 2;   // activation staging area: 64 KB
+constexpr int GM_X_BYTES = 6 * GM_NT_MAX * 32 * 2;   // activation staging area: 96 KB (three 32 KB stages at 128- and 256-token tiles)
 constexpr int GM_SX_MAX = 32;                 // most X stages (small token tiles): a stage is NT tokens x 32 k fp16 = NT*64 bytes
 // X stages for a token tile of NT: as many as fit the staging area, at most GM_SX_MAX.  Small tiles
 // need the depth: a stage is refilled by a bulk copy whose latency is the same whatever its size.
