@@ -368,6 +368,9 @@ def run_gemm(args):
 
     torch.cuda.set_device(0)
     be = p.CudaBackend(device=0)
+    for kv in args.option:
+        key, val = kv.split("=")
+        be.set_option(key, int(val))
     arch = arch_dict(args.workload)
     H, I = arch["hidden_size"], arch["intermediate_size"]
     kvd = arch["num_kv_heads"] * arch["head_dim"]
