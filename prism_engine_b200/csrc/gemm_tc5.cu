@@ -69,6 +69,8 @@ struct GemmArgs {
 // zero.
 __global__ void gemm_relay_x_kernel(const uint16_t *__restrict__ x, uint32_t m_tok, uint32_t m_tok_pad, uint32_t k,
                                     uint32_t nt, uint4 *__restrict__ xc) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // index into the output
     const size_t k8n = k / 8;
     if (i >= k8n * m_tok_pad) return;
@@ -96,6 +98,10 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
         if (threadIdx.x == 0) atomicExch(a.err, 4u);
         return;
     }
+    // Tables, barriers and TMEM are set up from weights alone while the previous kernel drains; the
+    // loader thread waits for it before the first activation copy, and everything that reads or
+    // writes activations (MMAs, epilogue) follows that copy through the mbarriers.
+    pdl_launch_dependents();
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t bar = smem_base + GM_BAR_OFF;
     const uint32_t b_afull = bar, b_aempty = bar + 8 * GM_SA, b_xfull = bar + 16 * GM_SA,
@@ -266,6 +272,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
         // =============================== activation loader ===============================
         const uint32_t x_addr = smem_base + GM_X_OFF;
         uint32_t n = 0;
+        pdl_wait();
         for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x) {
             const uint32_t tt = w / a.n_rt;
             const uint8_t *src0 = a.xc + (size_t)tt * nch * NT * 64;
@@ -304,8 +311,8 @@ static int launch_gemm_nt(prism_cuda_ctx *ctx, GemmArgs &a, const LutTensor &t, 
     PRISM_TRY(ensure_tmp(ctx, xc_halfs));
     const size_t units = xc_halfs / 8;
     if (!ctx->gemm_reuse_x) {
-        gemm_relay_x_kernel<<<(unsigned)((units + 255) / 256), 256, 0, ctx->stream>>>(X, a.m_tok, a.m_tok_pad, t.k, (uint32_t)NT,
-                                                                                    reinterpret_cast<uint4 *>(ctx->tmp_scratch));
+        launch_pdl(ctx, "gemm_relay_x_kernel", gemm_relay_x_kernel, dim3((unsigned)((units + 255) / 256)), dim3(256), 0, X, a.m_tok,
+                   a.m_tok_pad, t.k, (uint32_t)NT, reinterpret_cast<uint4 *>(ctx->tmp_scratch));
         PRISM_TRY(after_launch(ctx, "gemm_relay_x_kernel"));
     }
     a.xc = reinterpret_cast<const uint8_t *>(ctx->tmp_scratch);
@@ -314,7 +321,7 @@ static int launch_gemm_nt(prism_cuda_ctx *ctx, GemmArgs &a, const LutTensor &t, 
     uint32_t grid;
     if (a.n_rt <= G) grid = a.n_rt * std::max(1u, std::min(G / a.n_rt, a.n_tt));
     else grid = G;
-    lut_gemm_tc5_kernel<NT><<<grid, GM_THREADS, GM_SMEM_BYTES, ctx->stream>>>(a);
+    launch_pdl(ctx, "lut_gemm_tc5_kernel", lut_gemm_tc5_kernel<NT>, dim3(grid), dim3(GM_THREADS), GM_SMEM_BYTES, a);
     return after_launch(ctx, "lut_gemm_tc5_kernel");
 }
 
