@@ -73,7 +73,12 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
  * peer memory instead of ncclAllReduce + add; set it identically on every rank),
  * "sk_min_chunks" (default 8: fewest 1 KB index chunks the GEMV gives one CTA of a small matrix),
  * "sk_stream_chunks" (default 64: chunks per CTA from which the GEMV deals contiguous, balanced
- * ranges to a persistent grid instead of cutting every 64-row block into equal parts). */
+ * ranges to a persistent grid instead of cutting every 64-row block into equal parts),
+ * "wait_limit_polls" (default 0 = built-in, about fifteen seconds: polls after which a kernel stops
+ * waiting for a tensor-parallel peer or a grid-wide arrival, records a device error code and goes on;
+ * the next synchronising call then returns PRISM_E_TIMEOUT and the context stays usable),
+ * "cimage_cache" (0/1, default 0: prism_cuda_engine_load_cimage keeps the re-laid image beside the file).
+ * A captured decode graph is rebuilt after any option change. */
 int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value);
 /* Number of kernels this library has launched on the context so far. */
 uint64_t prism_cuda_launch_count(prism_cuda_ctx *ctx);
@@ -141,6 +146,25 @@ int prism_cuda_free_tensor(prism_cuda_ctx *ctx, int32_t handle);
 /* Uploads every Palettized4Bit tensor of a reference-format .cimage file
  * (src/quantization/cimage.rs:242-277) under its own key; *n_out = tensors uploaded. */
 int prism_cuda_load_cimage(prism_cuda_ctx *ctx, const char *path, uint32_t *n_out);
+/* The same with a cache of the RE-LAID image (the device layout of every tensor) kept in `cache_path`
+ * (NULL or "": `path` + ".b200relay"): a later load of the same container reads only its header and the
+ * cache, and copies each tensor's index array and palettes to the device as they are -- no payload read,
+ * no re-lay kernels.  The cache is keyed by a hash of the container's header and size; a stale or
+ * foreign file is ignored and rewritten.  *hit_out = 1 when the cache was used.  Stands where
+ * PrismEngine::load re-reads and re-copies every payload on each start (engine_impl.rs:600-616). */
+int prism_cuda_load_cimage_cached(prism_cuda_ctx *ctx, const char *path, const char *cache_path, uint32_t *n_out,
+                                  int *hit_out);
+/* ExecutionPlan of the last container loaded on this context (CImageHeader::execution_plan,
+ * src/quantization/cimage.rs:54-60; schema src/lut/graph.rs:552-589), as PrismEngine::load parses it
+ * (engine_impl.rs:637-641).  version == 0: the container had no plan or one that does not parse (both
+ * tolerated, as in the reference).  The reference keeps the plan and never dispatches on it; neither does
+ * this backend -- kv_fp16 tells the caller which KV mode the compiler assumed. */
+typedef struct prism_cimage_plan {
+    uint32_t version, num_layers, n_nodes, n_gemm_nodes; /* n_gemm_nodes: MetalGemm + CpuGemm assignments */
+    int32_t kv_fp16;                                     /* 1 "Fp16", 0 "Int8", -1 absent */
+    char architecture[32], attention_strategy[24], lm_head_backend[16];
+} prism_cimage_plan;
+int prism_cuda_cimage_plan(prism_cuda_ctx *ctx, prism_cimage_plan *out);
 
 /* ---- palettized GEMV: MetalBackend::gemv (engine_impl.rs:155-190), i.e.
  *      lut_gemv_cpu (src/lut/cpu_fallback.rs:12-35) on the device ---------- */
@@ -211,6 +235,17 @@ int prism_cuda_vec_add(prism_cuda_ctx *ctx, uint16_t *a, const uint16_t *b, uint
 int prism_cuda_attention(prism_cuda_ctx *ctx, const uint16_t *q, const uint16_t *k,
                          const uint16_t *v, uint32_t seq_len, uint32_t num_heads,
                          uint32_t kv_heads, uint32_t head_dim, uint16_t *out);
+/* The backend-held fp16 KV cache of MetalBackend: `new(.., num_layers, kv_stride)` allocates a K and a V
+ * buffer per layer (engine_impl.rs:109-119), append_kv(layer, k, v, token_idx) copies one token's rows in
+ * (:256-286), and attention_decode reads them.  kv_init sizes the cache ([layer][max_seq][kv_dim] fp16;
+ * the reference fixes max_seq at 4096); kv_append copies kv_dim values each of k and v into position
+ * token_idx; attention_kv is prism_cuda_attention over the first seq_len positions of that layer's
+ * cache.  Where the reference silently ignores a layer or token outside the cache, kv_append returns
+ * PRISM_E_ARG.  (RoPE of q on a host slice is prism_cuda_rope above.) */
+int prism_cuda_kv_init(prism_cuda_ctx *ctx, uint32_t num_layers, uint32_t kv_dim, uint32_t max_seq);
+int prism_cuda_kv_append(prism_cuda_ctx *ctx, uint32_t layer, const uint16_t *k, const uint16_t *v, uint64_t token_idx);
+int prism_cuda_attention_kv(prism_cuda_ctx *ctx, uint32_t layer, const uint16_t *q, uint32_t seq_len, uint32_t num_heads,
+                            uint32_t kv_heads, uint32_t head_dim, uint16_t *out);
 /* argmax (engine_impl.rs:1448-1459): first strictly greatest. */
 int prism_cuda_argmax(prism_cuda_ctx *ctx, const uint16_t *logits, uint32_t n, uint32_t *index);
 
@@ -311,6 +346,19 @@ int prism_cuda_tp_world(prism_cuda_ctx *ctx, int *world, int *rank);
 /* 1 when the peer-memory all-reduce is set up on this context (same answer on every rank), 0 when
  * the step falls back to ncclAllReduce. */
 int prism_cuda_tp_peer_ready(prism_cuda_ctx *ctx);
+/* Why prism_cuda_tp_peer_ready is 0 ("" when the peer path is set up or tensor parallelism is off). */
+const char *prism_cuda_tp_peer_reason(prism_cuda_ctx *ctx);
+/* h[i] = f16( f32(f16(sum over ranks of partial[i])) + f32(h[i]) ) for n values (n % 4 == 0), device pointers,
+ * on the context stream: the peer-memory all-reduce of a row-parallel matmul's fp32 partial sums fused with
+ * the residual add, as the decode step uses it.  Every rank must call it the same number of times.  A rank
+ * whose peers do not deliver within the wait limit ("wait_limit_polls") goes on and the next synchronising
+ * call (prism_cuda_synchronize, engine step/decode/generate) returns PRISM_E_TIMEOUT. */
+int prism_cuda_tp_all_reduce_resid_dev(prism_cuda_ctx *ctx, const void *partial_f32_dev, void *h_f16_dev, size_t n);
+/* Bring-up and diagnostics on ONE GPU, without NCCL: makes this context rank `rank` of a `world`-rank group
+ * whose peers are all this context's own receive area.  Nothing ever delivers the other ranks' slices, so
+ * prism_cuda_tp_all_reduce_resid_dev on such a context exercises exactly the give-up path of the bounded
+ * wait.  No engine can be created on it. */
+int prism_cuda_tp_init_loopback(prism_cuda_ctx *ctx, int world, int rank);
 /* In-place fp16 sum over ranks of a device vector, on the context stream. */
 int prism_cuda_tp_all_reduce_dev(prism_cuda_ctx *ctx, void *buf_dev, size_t n_halfs);
 

@@ -36,6 +36,14 @@ class ModelConfig(C.Structure):
     ]
 
 
+class CImagePlan(C.Structure):
+    """Mirror of ``prism_cimage_plan``."""
+
+    _fields_ = [("version", C.c_uint32), ("num_layers", C.c_uint32), ("n_nodes", C.c_uint32),
+                ("n_gemm_nodes", C.c_uint32), ("kv_fp16", C.c_int32), ("architecture", C.c_char * 32),
+                ("attention_strategy", C.c_char * 24), ("lm_head_backend", C.c_char * 16)]
+
+
 # name -> (restype, argtypes); every symbol include/prism_cuda.h declares
 _vp, _i32, _u32, _u64, _sz = C.c_void_p, C.c_int32, C.c_uint32, C.c_uint64, C.c_size_t
 _cp = C.c_char_p
@@ -105,6 +113,14 @@ SIGNATURES = {
     "prism_cuda_gemv_partition": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                             C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.c_uint32]),
     "prism_cuda_tp_all_reduce_dev": (C.c_int, [_vp, _vp, _sz]),
+    "prism_cuda_tp_peer_reason": (_cp, [_vp]),
+    "prism_cuda_tp_all_reduce_resid_dev": (C.c_int, [_vp, _vp, _vp, _sz]),
+    "prism_cuda_tp_init_loopback": (C.c_int, [_vp, C.c_int, C.c_int]),
+    "prism_cuda_kv_init": (C.c_int, [_vp, _u32, _u32, _u32]),
+    "prism_cuda_kv_append": (C.c_int, [_vp, _u32, _vp, _vp, _u64]),
+    "prism_cuda_attention_kv": (C.c_int, [_vp, _u32, _vp, _u32, _u32, _u32, _u32, _vp]),
+    "prism_cuda_load_cimage_cached": (C.c_int, [_vp, _cp, _cp, _pu32, C.POINTER(C.c_int)]),
+    "prism_cuda_cimage_plan": (C.c_int, [_vp, C.POINTER(CImagePlan)]),
 }
 
 _lib = None

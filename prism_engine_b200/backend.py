@@ -262,10 +262,46 @@ class CudaBackend:
         self._ck(self.L.prism_cuda_bench_gemm(self.ctx, handle, m_tok, reps, C.byref(ms)))
         return ms.value
 
-    def load_cimage(self, path: str) -> int:
+    def load_cimage(self, path: str, cache: Optional[str] = None):
+        """Uploads every palettized tensor of a reference-format ``.cimage``.  ``cache``: path of the cache
+        of the re-laid image ("" = beside the file); returns ``(n, hit)`` then, else ``n``."""
         n = C.c_uint32()
-        self._ck(self.L.prism_cuda_load_cimage(self.ctx, path.encode(), C.byref(n)))
-        return n.value
+        if cache is None:
+            self._ck(self.L.prism_cuda_load_cimage(self.ctx, path.encode(), C.byref(n)))
+            return n.value
+        hit = C.c_int()
+        self._ck(self.L.prism_cuda_load_cimage_cached(self.ctx, path.encode(), cache.encode(), C.byref(n), C.byref(hit)))
+        return n.value, bool(hit.value)
+
+    def cimage_plan(self) -> dict:
+        """``ExecutionPlan`` of the last container loaded (src/lut/graph.rs:552-589); version 0 = none."""
+        pl = _lib.CImagePlan()
+        self._ck(self.L.prism_cuda_cimage_plan(self.ctx, C.byref(pl)))
+        return {"version": pl.version, "num_layers": pl.num_layers, "n_nodes": pl.n_nodes,
+                "n_gemm_nodes": pl.n_gemm_nodes, "kv_cache": {1: "Fp16", 0: "Int8"}.get(pl.kv_fp16),
+                "architecture": pl.architecture.decode(), "attention_strategy": pl.attention_strategy.decode(),
+                "lm_head_backend": pl.lm_head_backend.decode()}
+
+    # -- MetalBackend::{append_kv, attention} over the backend-held cache (engine_impl.rs:109-119, 256-286) ---
+    def kv_init(self, num_layers: int, kv_dim: int, max_seq: int = 4096) -> None:
+        self._ck(self.L.prism_cuda_kv_init(self.ctx, num_layers, kv_dim, max_seq))
+        self._kv_shape = (num_layers, kv_dim, max_seq)
+
+    def append_kv(self, layer: int, k, v, token_idx: int) -> None:
+        """``MetalBackend::append_kv``: a layer or token outside the cache is ignored, as there."""
+        k, v = _u16(k), _u16(v)
+        nl, kvd, ms = getattr(self, "_kv_shape", (0, 0, 0))
+        if layer >= nl or token_idx >= ms or kvd == 0:
+            return
+        if k.size != kvd or v.size != kvd:
+            raise PrismCudaError(_lib.E_ARG, f"append_kv: k and v must have {kvd} elements")
+        self._ck(self.L.prism_cuda_kv_append(self.ctx, layer, _ptr(k), _ptr(v), token_idx))
+
+    def attention_kv(self, layer: int, q, seq_len: int, num_heads: int, kv_heads: int, head_dim: int) -> np.ndarray:
+        q = _u16(q)
+        out = np.zeros(num_heads * head_dim, np.uint16)
+        self._ck(self.L.prism_cuda_attention_kv(self.ctx, layer, _ptr(q), seq_len, num_heads, kv_heads, head_dim, _ptr(out)))
+        return out
 
     # -- tensor parallel ------------------------------------------------------------------------------------------
     @staticmethod
@@ -296,6 +332,17 @@ class CudaBackend:
     def tp_peer_ready(self) -> bool:
         """True when the row-parallel partial sums are reduced through peer memory (else NCCL)."""
         return bool(self.L.prism_cuda_tp_peer_ready(self.ctx))
+
+    def tp_peer_reason(self) -> str:
+        r = self.L.prism_cuda_tp_peer_reason(self.ctx)
+        return r.decode() if r else ""
+
+    def tp_init_loopback(self, world: int, rank: int) -> None:
+        """One-GPU diagnostic group whose peers never deliver (see ``prism_cuda_tp_init_loopback``)."""
+        self._ck(self.L.prism_cuda_tp_init_loopback(self.ctx, world, rank))
+
+    def tp_all_reduce_resid_dev(self, partial_dev: int, h_dev: int, n: int) -> None:
+        self._ck(self.L.prism_cuda_tp_all_reduce_resid_dev(self.ctx, partial_dev, h_dev, n))
 
 
 def model_config(num_layers, hidden_size, num_heads, num_kv_heads, head_dim, intermediate_size, vocab_size,

@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "pair_table.cuh"
+#include "scratch.hpp"
 
 namespace prism {
 
@@ -28,62 +29,78 @@ int after_launch(prism_cuda_ctx *ctx, const char *kernel) {
     return PRISM_OK;
 }
 
-static int grow(prism_cuda_ctx *ctx, void **p, size_t *have, size_t want) {
-    if (want <= *have) return PRISM_OK;
-    // growing frees the old buffer: wait for work that may still read it
-    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    if (*p) PRISM_CUDA_TRY(ctx, cudaFree(*p));
-    *p = nullptr;
-    *have = 0;
-    size_t sz = (want + 255) / 256 * 256;
-    PRISM_CUDA_TRY(ctx, cudaMalloc(p, sz));
-    *have = sz;
-    return PRISM_OK;
-}
+// cudaMalloc / cudaFree behind the allocator interface of grow_buf (scratch.hpp).
+struct CudaScratchAlloc {
+    prism_cuda_ctx *ctx;
+    cudaError_t last = cudaSuccess;
+    const char *what = "";
+    int sync() { what = "cudaStreamSynchronize"; last = cudaStreamSynchronize(ctx->stream); return last == cudaSuccess ? 0 : 1; }
+    int release(void *p) { what = "cudaFree"; last = cudaFree(p); return last == cudaSuccess ? 0 : 1; }
+    int acquire(void **p, size_t bytes) { what = "cudaMalloc"; last = cudaMalloc(p, bytes); return last == cudaSuccess ? 0 : 1; }
+};
 
-int ensure_stage(prism_cuda_ctx *ctx, size_t in_bytes, size_t out_bytes) {
-    PRISM_TRY(grow(ctx, (void **)&ctx->stage_in, &ctx->stage_in_bytes, in_bytes));
-    return grow(ctx, (void **)&ctx->stage_out, &ctx->stage_out_bytes, out_bytes);
-}
-
-int ensure_splitk(prism_cuda_ctx *ctx, size_t floats, size_t counters) {
-    size_t fb = ctx->splitk_floats * 4;
-    PRISM_TRY(grow(ctx, (void **)&ctx->splitk_partials, &fb, floats * 4));
-    ctx->splitk_floats = fb / 4;
-    if (counters > ctx->splitk_counter_n) {
-        size_t cb = ctx->splitk_counter_n * 4;
-        PRISM_TRY(grow(ctx, (void **)&ctx->splitk_counters, &cb, counters * 4));
-        ctx->splitk_counter_n = cb / 4;
-        // arrival counters start at zero; each kernel leaves them at zero again
-        PRISM_CUDA_TRY(ctx, cudaMemsetAsync(ctx->splitk_counters, 0, cb, ctx->stream));
+// Grows one of the context's scratch buffers to `want` elements.  Pointer and element count are
+// written back whatever happens: after a failed allocation both are zero, never a stale size
+// beside a null pointer.
+template <typename T>
+static int grow(prism_cuda_ctx *ctx, T **p, size_t *have, size_t want, bool *grew = nullptr) {
+    GrowBuf b{*p, *have};
+    CudaScratchAlloc al{ctx};
+    const int rc = grow_buf(al, b, want, sizeof(T), grew);
+    *p = static_cast<T *>(b.ptr);
+    *have = b.count;
+    if (rc) {
+        (void)cudaGetLastError();
+        return cuda_fail(ctx, al.last, al.what);
     }
     return PRISM_OK;
 }
 
-int ensure_act(prism_cuda_ctx *ctx, size_t halfs) {
-    size_t hb = ctx->act_halfs * 2;
-    PRISM_TRY(grow(ctx, (void **)&ctx->act_scratch, &hb, halfs * 2));
-    ctx->act_halfs = hb / 2;
+int ensure_stage(prism_cuda_ctx *ctx, size_t in_bytes, size_t out_bytes) {
+    PRISM_TRY(grow(ctx, &ctx->stage_in, &ctx->stage_in_bytes, in_bytes));
+    return grow(ctx, &ctx->stage_out, &ctx->stage_out_bytes, out_bytes);
+}
+
+int ensure_splitk(prism_cuda_ctx *ctx, size_t floats, size_t counters) {
+    PRISM_TRY(grow(ctx, &ctx->splitk_partials, &ctx->splitk_floats, floats));
+    bool grew = false;
+    PRISM_TRY(grow(ctx, &ctx->splitk_counters, &ctx->splitk_counter_n, counters, &grew));
+    // arrival counters start at zero; each kernel leaves them at zero again
+    if (grew)
+        PRISM_CUDA_TRY(ctx, cudaMemsetAsync(ctx->splitk_counters, 0, ctx->splitk_counter_n * sizeof(unsigned int), ctx->stream));
     return PRISM_OK;
 }
 
-int ensure_tmp(prism_cuda_ctx *ctx, size_t halfs) {
-    size_t hb = ctx->tmp_halfs * 2;
-    PRISM_TRY(grow(ctx, (void **)&ctx->tmp_scratch, &hb, halfs * 2));
-    ctx->tmp_halfs = hb / 2;
-    return PRISM_OK;
-}
+int ensure_act(prism_cuda_ctx *ctx, size_t halfs) { return grow(ctx, &ctx->act_scratch, &ctx->act_halfs, halfs); }
+
+int ensure_tmp(prism_cuda_ctx *ctx, size_t halfs) { return grow(ctx, &ctx->tmp_scratch, &ctx->tmp_halfs, halfs); }
 
 int check_device_error(prism_cuda_ctx *ctx) {
     unsigned int v = 0;
     PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(&v, ctx->dev_err, 4, cudaMemcpyDeviceToHost, ctx->stream));
     PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    if (v != 0) {
-        cudaMemsetAsync(ctx->dev_err, 0, 4, ctx->stream);
-        return fail(ctx, PRISM_E_STATE, "a kernel refused to run: shared-memory layout assumption does not hold (code " +
-                                            std::to_string(v) + ")");
+    return device_error_result(ctx, v);
+}
+
+int device_error_result(prism_cuda_ctx *ctx, unsigned int v) {
+    if (v == 0) return PRISM_OK;
+    cudaMemsetAsync(ctx->dev_err, 0, 4, ctx->stream);  // reported once; the context stays usable
+    const std::string code = " (device code " + std::to_string(v) + ")";
+    switch (v) {
+    case 1:
+        return fail(ctx, PRISM_E_STATE, "a kernel refused to run: dynamic shared memory does not start where the table lookups assume" + code);
+    case 2:
+        return fail(ctx, PRISM_E_TIMEOUT, "a warp-specialised GEMV gave up waiting for its own stage hand-over; its output is incomplete" + code);
+    case 3:
+        return fail(ctx, PRISM_E_TIMEOUT, "peer-memory all-reduce: a tensor-parallel peer did not deliver its partial sums within the wait "
+                                          "limit; the step went on with what had arrived and its result is not valid" + code);
+    case 4:
+        return fail(ctx, PRISM_E_TIMEOUT, "a grid-wide arrival inside a persistent kernel gave up; its output is incomplete" + code);
+    case 5:
+        return fail(ctx, PRISM_E_TIMEOUT, "a tcgen05 kernel gave up waiting on an mbarrier; its output is incomplete" + code);
+    default:
+        return fail(ctx, PRISM_E_STATE, "a kernel reported an unknown error" + code);
     }
-    return PRISM_OK;
 }
 
 LutTensor *get_tensor(prism_cuda_ctx *ctx, int32_t handle) {
@@ -150,7 +167,7 @@ int prism_cuda_create(int device, prism_cuda_ctx **out) {
     cudaError_t e = cudaGetDeviceCount(&n);
     if (e != cudaSuccess || n == 0)
         return fail(nullptr, PRISM_E_CUDA, std::string("No CUDA device: ") + cudaGetErrorString(e));
-    if (device < 0 || device >= n) return fail(nullptr, PRISM_E_ARG, "device index out of range");
+    if (device < 0 || device >= n || device >= PRISM_MAX_DEVICES) return fail(nullptr, PRISM_E_ARG, "device index out of range");
     cudaDeviceProp p;
     if ((e = cudaGetDeviceProperties(&p, device)) != cudaSuccess) return cuda_fail(nullptr, e, "cudaGetDeviceProperties");
     if (p.major != 10)
@@ -197,6 +214,8 @@ void prism_cuda_destroy(prism_cuda_ctx *ctx) {
     cudaFree(ctx->act_scratch);
     cudaFree(ctx->tmp_scratch);
     cudaFree(ctx->dev_err);
+    cudaFree(ctx->kv_k);
+    cudaFree(ctx->kv_v);
     extern void prism_tp_shutdown(prism_cuda_ctx *);
     prism_tp_shutdown(ctx);
     cudaStreamDestroy(ctx->stream);
@@ -239,9 +258,15 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
         ctx->tp_peer_ar = value ? 1 : 0;
     } else if (!strcmp(key, "pdl")) {
         ctx->pdl = value ? 1 : 0;
+    } else if (!strcmp(key, "cimage_cache")) {
+        ctx->cimage_cache = value ? 1 : 0;
+    } else if (!strcmp(key, "wait_limit_polls")) {
+        if (value < 0 || value > 0x7FFFFFFF) return fail(ctx, PRISM_E_ARG, "wait_limit_polls must be in 0..2^31-1");
+        ctx->wait_limit_polls = (uint32_t)value;
     } else {
         return fail(ctx, PRISM_E_ARG, std::string("unknown option ") + key);
     }
+    ctx->option_epoch++;
     return PRISM_OK;
 }
 
@@ -657,6 +682,62 @@ int prism_cuda_attention(prism_cuda_ctx *ctx, const uint16_t *q, const uint16_t 
     a.pos_dev = nullptr; a.pos_host = (int32_t)seq_len - 1; a.slot_mul = 1; a.slot_add = 0;
     a.nh = num_heads; a.nkv = kv_heads; a.hd = head_dim; a.batch = 1;
     a.seq_stride = 0; a.int8 = 0; a.max_seq = seq_len ? seq_len : 1;
+    PRISM_TRY(launch_attention(ctx, a));
+    return host_call_end(ctx, out, qb);
+}
+
+// ---- backend-held KV cache: the kv_bufs of MetalBackend (engine_impl.rs:47-49, 109-119, 256-286) --------
+
+int prism_cuda_kv_init(prism_cuda_ctx *ctx, uint32_t num_layers, uint32_t kv_dim, uint32_t max_seq) {
+    if (!ctx) return PRISM_E_NULL;
+    if (!num_layers || !kv_dim || !max_seq || kv_dim % 8) return fail(ctx, PRISM_E_ARG, "kv_init: zero dimension, or kv_dim not a multiple of 8");
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    cudaFree(ctx->kv_k);
+    cudaFree(ctx->kv_v);
+    ctx->kv_k = ctx->kv_v = nullptr;
+    ctx->kv_layers = ctx->kv_dim = ctx->kv_max_seq = 0;
+    const size_t bytes = (size_t)num_layers * max_seq * kv_dim * 2;
+    PRISM_CUDA_TRY(ctx, cudaMalloc((void **)&ctx->kv_k, bytes));
+    cudaError_t e = cudaMalloc((void **)&ctx->kv_v, bytes);
+    if (e != cudaSuccess) {
+        cudaFree(ctx->kv_k);
+        ctx->kv_k = nullptr;
+        return cuda_fail(ctx, e, "cudaMalloc(kv cache)");
+    }
+    ctx->kv_layers = num_layers; ctx->kv_dim = kv_dim; ctx->kv_max_seq = max_seq;
+    return PRISM_OK;
+}
+
+int prism_cuda_kv_append(prism_cuda_ctx *ctx, uint32_t layer, const uint16_t *k, const uint16_t *v, uint64_t token_idx) {
+    if (!ctx || !k || !v) return fail(ctx, PRISM_E_NULL, "null argument");
+    if (!ctx->kv_k) return fail(ctx, PRISM_E_STATE, "kv_append: no cache (prism_cuda_kv_init first)");
+    if (layer >= ctx->kv_layers || token_idx >= ctx->kv_max_seq)
+        return fail(ctx, PRISM_E_ARG, "kv_append: layer or token index outside the cache");
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const size_t off = ((size_t)layer * ctx->kv_max_seq + token_idx) * ctx->kv_dim, bytes = (size_t)ctx->kv_dim * 2;
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->kv_k + off, k, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->kv_v + off, v, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return PRISM_OK;
+}
+
+int prism_cuda_attention_kv(prism_cuda_ctx *ctx, uint32_t layer, const uint16_t *q, uint32_t seq_len, uint32_t num_heads,
+                            uint32_t kv_heads, uint32_t head_dim, uint16_t *out) {
+    if (!ctx || !q || !out) return fail(ctx, PRISM_E_NULL, "null argument");
+    if (!ctx->kv_k) return fail(ctx, PRISM_E_STATE, "attention_kv: no cache (prism_cuda_kv_init first)");
+    if (!num_heads || !kv_heads || !head_dim || num_heads % kv_heads) return fail(ctx, PRISM_E_ARG, "attention: bad head configuration");
+    if (layer >= ctx->kv_layers || kv_heads * head_dim != ctx->kv_dim || seq_len == 0 || seq_len > ctx->kv_max_seq)
+        return fail(ctx, PRISM_E_ARG, "attention_kv: layer, kv width or seq_len does not match the cache");
+    const size_t qb = (size_t)num_heads * head_dim * 2;
+    PRISM_TRY(host_call_begin(ctx, q, qb, qb));
+    AttnArgs a{};
+    const size_t off = (size_t)layer * ctx->kv_max_seq * ctx->kv_dim;
+    a.q = (const uint16_t *)ctx->stage_in; a.q_stride = num_heads * head_dim;
+    a.k = ctx->kv_k + off; a.v = ctx->kv_v + off; a.out = (uint16_t *)ctx->stage_out;
+    a.pos_dev = nullptr; a.pos_host = (int32_t)seq_len - 1; a.slot_mul = 1; a.slot_add = 0;
+    a.nh = num_heads; a.nkv = kv_heads; a.hd = head_dim; a.batch = 1;
+    a.seq_stride = 0; a.int8 = 0; a.max_seq = seq_len;
     PRISM_TRY(launch_attention(ctx, a));
     return host_call_end(ctx, out, qb);
 }

@@ -238,11 +238,11 @@ bool attn_fused_eligible(const AttnArgs &a) {
 
 template <int VEC>
 static int launch_attn_fused_v(prism_cuda_ctx *ctx, const FusedAttnArgs &fa, uint32_t S, size_t smem) {
-    static bool configured[8] = {false};
-    if (smem > 32 * 1024 && !configured[ctx->device & 7]) {
+    static bool configured[PRISM_MAX_DEVICES] = {false};
+    if (smem > 32 * 1024 && !configured[ctx->device]) {
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attn_fused_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  160 * 1024));
-        configured[ctx->device & 7] = true;
+        configured[ctx->device] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(fa.nh * S, fa.batch);

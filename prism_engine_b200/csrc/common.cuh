@@ -14,6 +14,10 @@
 
 namespace prism {
 
+// Device ordinals a context may be created on (prism_cuda_create refuses larger ones); sizes the
+// per-device "kernel attributes set" caches.
+constexpr int PRISM_MAX_DEVICES = 64;
+
 // ---------------------------------------------------------------------------
 // Device layout of one palettized tensor ("re-laid" form of the .cimage
 // split-block payload, src/quantization/cimage.rs:98-125).
@@ -75,8 +79,16 @@ struct prism_cuda_ctx {
     int attn_cluster = 0;    // CTAs per (head, sequence) of the fused attention kernel; 0: chosen from max_seq
     int gemm_reuse_x = 0;    // set by a caller for the second of two GEMMs over the same activations: skip the re-lay
     int pdl = 1;  // programmatic dependent launch between the kernels of the decode chain
+    int cimage_cache = 0;  // engine_load_cimage keeps / uses the cache of the re-laid image beside the file
+    // Upper bound, in polls, of the device-side waits on something outside the waiting CTA (a peer
+    // GPU's flag, a grid-wide arrival); a wait that runs out sets the device error word and the
+    // kernel goes on.  0: the built-in limits (seconds).  Option "wait_limit_polls".  The mbarrier
+    // hand-overs between the warps of one CTA keep their fixed bounds.
+    uint32_t wait_limit_polls = 0;
+    uint64_t option_epoch = 0;  // bumped by every set_option: a captured decode graph is valid for one epoch
     uint64_t launches = 0;
     // staging for host-pointer entry points (grown on demand)
+    // (each pointer is null exactly when its element count is zero)
     uint8_t *stage_in = nullptr, *stage_out = nullptr;
     size_t stage_in_bytes = 0, stage_out_bytes = 0;
     // scratch for split-K partial sums, arrival counters, MLP activation
@@ -103,6 +115,17 @@ struct prism_cuda_ctx {
     void *tp_peer_map[32] = {nullptr};   // what cudaIpcOpenMemHandle returned: [q] receive area, [16+q] flags of peer q
     size_t tp_cap = 0;                 // floats per rank slot; 0: peer path unavailable, NCCL is used
     int tp_peer_ar = 1;                // option "tp_peer_ar": use the peer-memory all-reduce when available
+    std::string tp_peer_reason;        // why the peer path is unavailable ("" when it is set up)
+    bool tp_loopback = false;          // prism_cuda_tp_init_loopback: every "peer" is this GPU's own receive area
+    // backend-held KV cache of the MetalBackend-style entry points (prism_cuda_kv_init / kv_append / attention_kv)
+    uint16_t *kv_k = nullptr, *kv_v = nullptr;
+    uint32_t kv_layers = 0, kv_dim = 0, kv_max_seq = 0;
+    // execution plan of the last .cimage that was loaded (src/lut/graph.rs:552-589); version 0: none / unparseable
+    struct PlanInfo {
+        uint32_t version = 0, num_layers = 0, n_nodes = 0, n_gemm_nodes = 0;
+        int kv_fp16 = -1;              // 1: "Fp16", 0: "Int8", -1: absent
+        std::string architecture, attention_strategy, lm_head_backend;
+    } plan;
 };
 
 namespace prism {
@@ -187,8 +210,20 @@ int tp_all_gather_bytes(prism_cuda_ctx *ctx, const void *send, void *recv, size_
 // matmul's fp32 partial sums fused with the residual add, through peer memory (one kernel, no NCCL).
 bool tp_peer_ar_ok(prism_cuda_ctx *ctx, size_t n);
 int tp_all_reduce_resid_peer(prism_cuda_ctx *ctx, const float *part, uint16_t *h, size_t n);
-// Reads the device error word; a non-zero value becomes PRISM_E_STATE.
+// Synchronises the stream and reads the device error word.  Codes kernels leave there:
+//   1  a kernel found its shared-memory layout assumption broken and refused to run  -> PRISM_E_STATE
+//   2  an mbarrier hand-over inside a warp-specialised GEMV gave up                    -> PRISM_E_TIMEOUT
+//   3  the peer-memory all-reduce gave up waiting for a peer's slice                   -> PRISM_E_TIMEOUT
+//   4  a grid-wide arrival inside a persistent kernel gave up                          -> PRISM_E_TIMEOUT
+//   5  an mbarrier wait inside a tcgen05 kernel gave up                                -> PRISM_E_TIMEOUT
+// The word is cleared, so the context stays usable.
 int check_device_error(prism_cuda_ctx *ctx);
+// The same translation for a caller that has already copied the word to the host (clears it if set).
+int device_error_result(prism_cuda_ctx *ctx, unsigned int word);
+// The wait bound kernels use: the option when set, else `builtin`.
+inline uint32_t wait_limit(const prism_cuda_ctx *ctx, uint32_t builtin) {
+    return ctx->wait_limit_polls ? ctx->wait_limit_polls : builtin;
+}
 
 // ---- kernels' host-side launchers (device pointers, context stream) -------
 

@@ -49,7 +49,7 @@ struct prism_cuda_engine {
     bool guard_skip = false;     // down_guard && inter != hidden
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_batch = 0;
-    int graph_variant = -1, graph_fuse = -1;
+    uint64_t graph_epoch = ~0ull;  // option epoch of the context when the graph (or its eager warm-up) was made
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr, ev3 = nullptr;
     double last_ms = 0.0, last_device_ms = 0.0;
     uint32_t kernels_per_step = 0;
@@ -341,22 +341,21 @@ static int capacity_ok(prism_cuda_engine *e, uint32_t steps) {
 // graph, later ones replay it.
 static int run_step(prism_cuda_engine *e) {
     prism_cuda_ctx *ctx = e->ctx;
-    const bool graph_ok = e->graph && e->graph_batch == e->batch && e->graph_variant == ctx->gemv_variant &&
-                          e->graph_fuse == ctx->fuse;
-    if (graph_ok) {
+    // every option can change which kernels a step launches, so a graph is good for one option epoch
+    const bool same_cfg = e->graph_batch == e->batch && e->graph_epoch == ctx->option_epoch;
+    if (e->graph && same_cfg) {
         PRISM_CUDA_TRY(ctx, cudaGraphLaunch(e->graph, ctx->stream));
         ctx->launches += 1;
         return PRISM_OK;
     }
-    if (e->graph_batch != e->batch || e->graph_variant != ctx->gemv_variant || e->graph_fuse != ctx->fuse) {
+    if (!same_cfg) {
         // configuration changed: drop the old graph and warm up eagerly once
         if (e->graph) {
             cudaGraphExecDestroy(e->graph);
             e->graph = nullptr;
         }
         e->graph_batch = e->batch;
-        e->graph_variant = ctx->gemv_variant;
-        e->graph_fuse = ctx->fuse;
+        e->graph_epoch = ctx->option_epoch;
         const uint64_t l0 = ctx->launches;
         PRISM_TRY(enqueue_step(e));
         e->kernels_per_step = (uint32_t)(ctx->launches - l0);
@@ -409,6 +408,7 @@ int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg,
     if (c.bits != 2 && c.bits != 4) return fail(ctx, PRISM_E_ARG, "bits must be 2 or 4");
     if (c.head_dim & 1) return fail(ctx, PRISM_E_ARG, "head_dim must be even");
     const int T = ctx->tp_world, r = ctx->tp_rank;
+    if (ctx->tp_loopback) return fail(ctx, PRISM_E_STATE, "a loopback tensor-parallel context has no peers: it cannot run a model");
     if (T > 1) {
         if (c.num_kv_heads % T || c.num_heads % T)
             return fail(ctx, PRISM_E_ARG, "tensor parallel degree must divide the head counts");
@@ -636,8 +636,10 @@ int prism_cuda_engine_step(prism_cuda_engine *e, const uint32_t *tokens, uint32_
         PRISM_CUDA_TRY(ctx, cudaMemcpy2DAsync(logits, (size_t)e->V_l * 2, e->logits, (size_t)ls * 2, (size_t)e->V_l * 2,
                                               e->batch, cudaMemcpyDeviceToHost, ctx->stream));
     }
+    unsigned int errw = 0;
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(&errw, ctx->dev_err, 4, cudaMemcpyDeviceToHost, ctx->stream));
     PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    return PRISM_OK;
+    return device_error_result(ctx, errw);
 }
 
 int prism_cuda_engine_decode(prism_cuda_engine *e, const uint32_t *tokens_in, uint32_t n_steps, uint32_t *out_tokens) {
@@ -658,13 +660,15 @@ int prism_cuda_engine_decode(prism_cuda_engine *e, const uint32_t *tokens_in, ui
     PRISM_CUDA_TRY(ctx, cudaMemcpy2DAsync(out_tokens, (size_t)n_steps * 4, e->out_tokens, (size_t)e->out_cap * 4,
                                           (size_t)n_steps * 4, e->batch, cudaMemcpyDeviceToHost, ctx->stream));
     PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev1, ctx->stream));
+    unsigned int errw = 0;
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(&errw, ctx->dev_err, 4, cudaMemcpyDeviceToHost, ctx->stream));
     PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     float ms = 0.f;
     cudaEventElapsedTime(&ms, e->ev0, e->ev1);
     e->last_ms = ms;
     cudaEventElapsedTime(&ms, e->ev2, e->ev3);
     e->last_device_ms = ms;
-    return PRISM_OK;
+    return device_error_result(ctx, errw);
 }
 
 int prism_cuda_engine_generate(prism_cuda_engine *e, const uint32_t *prompts, uint32_t batch, uint32_t n_prompt,
@@ -717,11 +721,13 @@ int prism_cuda_engine_generate(prism_cuda_engine *e, const uint32_t *prompts, ui
         PRISM_CUDA_TRY(ctx, cudaMemcpy2DAsync(last_logits, (size_t)e->V_l * 2, e->logits, (size_t)ls * 2,
                                               (size_t)e->V_l * 2, batch, cudaMemcpyDeviceToHost, ctx->stream));
     }
+    unsigned int errw = 0;
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(&errw, ctx->dev_err, 4, cudaMemcpyDeviceToHost, ctx->stream));
     PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     float ms = 0.f;
     cudaEventElapsedTime(&ms, e->ev0, e->ev1);
     e->last_ms = ms;
-    return PRISM_OK;
+    return device_error_result(ctx, errw);
 }
 
 uint64_t prism_cuda_engine_step_bytes(prism_cuda_engine *e) {

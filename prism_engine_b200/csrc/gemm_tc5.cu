@@ -298,11 +298,11 @@ bool gemm_tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t m_tok) 
 
 template <int NT>
 static int launch_gemm_nt(prism_cuda_ctx *ctx, GemmArgs &a, const LutTensor &t, const uint16_t *X) {
-    static bool configured[8] = {false};
-    if (!configured[ctx->device & 7]) {
+    static bool configured[PRISM_MAX_DEVICES] = {false};
+    if (!configured[ctx->device]) {
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemm_tc5_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)GM_SMEM_BYTES));
-        configured[ctx->device & 7] = true;
+        configured[ctx->device] = true;
     }
     a.m_tok_pad = round_up_u32(a.m_tok, NT);
     a.n_tt = a.m_tok_pad / NT;

@@ -384,12 +384,12 @@ constexpr int MMA_KNOWN_SBASE = 1024;  // dynamic shared memory starts after the
 
 template <int MODE, int SBASE>
 static int launch_mma_v(prism_cuda_ctx *ctx, const MmaGemvArgs &a, dim3 grid) {
-    static bool configured[8] = {false};
-    if (!configured[ctx->device & 7]) {
+    static bool configured[PRISM_MAX_DEVICES] = {false};
+    if (!configured[ctx->device]) {
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_mma_kernel<MODE, SBASE>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)MMA_SMEM_BYTES));
-        configured[ctx->device & 7] = true;
+        configured[ctx->device] = true;
     }
     lut_gemv_mma_kernel<MODE, SBASE><<<grid, MMA_THREADS, MMA_SMEM_BYTES, ctx->stream>>>(a);
     return after_launch(ctx, "lut_gemv_mma_kernel");
@@ -575,13 +575,14 @@ static __device__ __align__(256) float g_static_splitk[STATIC_PARTIAL_FLOATS + S
 
 // In host code `g_static_splitk` is only a stand-in for the symbol; the device address has to be
 // asked for, once per device, with that device current.
-static float *g_static_splitk_dev[64] = {nullptr};
+static float *g_static_splitk_dev[PRISM_MAX_DEVICES] = {nullptr};
 
 static int static_scratch_ptr(prism_cuda_ctx *ctx, float **out) {
-    if (ctx->device < 0 || ctx->device >= 64) return fail(ctx, PRISM_E_ARG, "device index above 63");
+    // every call: the launch and the memset below must go to the context's device whatever the
+    // calling thread had current
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     if (!g_static_splitk_dev[ctx->device]) {
         void *p = nullptr;
-        PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
         PRISM_CUDA_TRY(ctx, cudaGetSymbolAddress(&p, g_static_splitk));
         g_static_splitk_dev[ctx->device] = static_cast<float *>(p);
     }

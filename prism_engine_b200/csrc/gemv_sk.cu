@@ -18,25 +18,13 @@
 
 namespace prism {
 
-#ifndef SK_WARPS_N
-#define SK_WARPS_N 8
-#endif
-#ifndef SK_CTAS_N
-#define SK_CTAS_N 3
-#endif
-#ifndef SK_NACC_N
-#define SK_NACC_N 2
-#endif
-constexpr int SK_WARPS = SK_WARPS_N;
-constexpr int SK_CTAS_PER_SM = SK_CTAS_N;
-constexpr int SK_NACC = SK_NACC_N;        // independent accumulator sets (2 or 4)
+constexpr int SK_WARPS = 8;
+constexpr int SK_CTAS_PER_SM = 3;
+constexpr int SK_NACC = 2;                // independent accumulator sets (2 or 4)
 constexpr int SK_THREADS = SK_WARPS * 32;
 constexpr int SK_TBL_BYTES = 256 * 256;   // 256 entries x (2 half-blocks x 32 lanes x 4 B)
 constexpr int SK_PIECE_CHUNKS = SK_WARPS * 16;  // chunks of x staged at a time (8 warps: 4096 halves, 8 KB)
-#ifndef SK_PF_N
-#define SK_PF_N 2
-#endif
-constexpr int SK_PF = SK_PF_N;           // index chunks in flight per warp (1, 2 or 4)
+constexpr int SK_PF = 2;                 // index chunks in flight per warp (1, 2 or 4)
 constexpr int SK_KNOWN_SBASE = 1024;      // dynamic shared memory starts after the 1 KB the driver reserves
 constexpr size_t SK_SMEM_BYTES = SK_TBL_BYTES + SK_PIECE_CHUNKS * 64 + SK_WARPS * 64 * 4 + 32;
 
@@ -342,11 +330,11 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
 
 template <int MODE, int SBASE>
 static int launch_sk_v(prism_cuda_ctx *ctx, const SkArgs &a, dim3 grid) {
-    static bool configured[8] = {false};
-    if (!configured[ctx->device & 7]) {
+    static bool configured[PRISM_MAX_DEVICES] = {false};
+    if (!configured[ctx->device]) {
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_sk_kernel<MODE, SBASE>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_BYTES));
-        configured[ctx->device & 7] = true;
+        configured[ctx->device] = true;
     }
     launch_pdl(ctx, "lut_gemv_sk_kernel", lut_gemv_sk_kernel<MODE, SBASE>, grid, SK_THREADS, SK_SMEM_BYTES, a);
     return after_launch(ctx, "lut_gemv_sk_kernel");

@@ -63,16 +63,8 @@ struct Tc5Args {
     float *partials;            // [ksplit][n_tiles*128]
     unsigned int *counters;     // [n_tiles]
     unsigned int *err;
-    unsigned long long *dbg;    // optional cycle counters (builds with -DT5_TIMING only)
 };
 
-#ifdef T5_TIMING
-#define T5_T0() const long long _t0 = clock64()
-#define T5_ACC(slot) do { if (a.dbg && blockIdx.x == 0 && lane == 0) atomicAdd(a.dbg + (slot) + 8 * (warp == T5_DEQ_WARPS ? 1 : 0), (unsigned long long)(clock64() - _t0)); } while (0)
-#else
-#define T5_T0() do {} while (0)
-#define T5_ACC(slot) do {} while (0)
-#endif
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
@@ -238,9 +230,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
             const bool second = (a.mode == GEMV_SWIGLU) && slot == 1;  // quarters 2,3 read the up tensor
             const bool ok = hb < a.n_hb1;
             const uint32_t h = ok ? hb : a.n_hb1 - 1;
-#ifdef T5_TIMING
-            long long _tt0 = clock64();
-#endif
             // ---- index stream: start the first loads before building the table ----
             const uint8_t *sp = (second ? a.idx2 : a.idx1) + ((size_t)h * a.n_chunks + c_begin) * 512 + lane * 16;
             uint4 r[T5_PF];
@@ -271,10 +260,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
                 }
             }
             asm volatile("bar.sync %0, 256;\n" ::"r"(1 + pair) : "memory");
-#ifdef T5_TIMING
-            if (a.dbg && blockIdx.x == 0 && tid == 0) { atomicAdd(a.dbg + 5, (unsigned long long)(clock64() - _tt0)); atomicAdd(a.dbg + 10, 1ull); }
-            _tt0 = clock64();
-#endif
             // ---- stream: lookups -> TMEM stage -> signal the MMA thread ----
             for (uint32_t c0 = j; c0 < nch; c0 += 4 * T5_PF) {
 #pragma unroll
@@ -282,17 +267,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
                     const uint32_t c = c0 + 4 * i;
                     if (c < nch) {
                         uint4 w;
-                        { T5_T0(); w = r[i]; asm volatile("" :: "r"(w.x), "r"(w.w)); T5_ACC(0); }
+                        w = r[i];
                         const uint32_t nc = c + 4 * T5_PF;
                         if (nc < nch) r[i] = ldg128_nc(sp + (size_t)nc * 512);
                         const uint32_t aw[4] = {w.x, w.y, w.z, w.w};
                         uint32_t A[16];
-#ifdef T5_NO_LDS
-                        if (true) {
-#pragma unroll
-                            for (int hh = 0; hh < 16; hh++) A[hh] = aw[hh & 3] + hh;
-                        } else
-#endif
                         if (slot == 0) {
 #pragma unroll
                             for (int hh = 0; hh < 4; hh++) {
@@ -312,34 +291,16 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
                             }
                         }
                         const uint32_t n = n_base + c, stage = n % T5_STAGES, ph = (n / T5_STAGES) & 1;
-                        { T5_T0(); asm volatile("" :: "r"(A[0]), "r"(A[15])); T5_ACC(1); }
-                        { T5_T0();
-#ifndef T5_NO_EMPTYWAIT
                         mbar_wait_warp(bar_empty + 8 * (stage / T5_GROUP), ph ^ 1, err_flag);  // MMAs that read this stage group are done
-#endif
-                        T5_ACC(2); }
                         tc_fence_after();
-                        { T5_T0();
-#ifndef T5_NO_ST
                         tc_st16(tmem_lane + stage * 16, A);
                         asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-#else
-                        asm volatile("" :: "r"(A[0]), "r"(A[3]), "r"(A[7]), "r"(A[15]));
-#endif
-                        T5_ACC(3); }
                         tc_fence_before();
                         if (lane == 0) mbar_arrive(bar_full + 8 * stage);
-#ifdef T5_TIMING
-                        if (a.dbg && blockIdx.x == 0 && lane == 0 && warp == 0) atomicAdd(a.dbg + 4, 1ull);
-#endif
                     }
                 }
             }
             n_base += nch;
-#ifdef T5_TIMING
-            if (a.dbg && blockIdx.x == 0 && tid == 0) atomicAdd(a.dbg + 6, (unsigned long long)(clock64() - _tt0));
-            _tt0 = clock64();
-#endif
             if (j != 0) continue;
             // ---- epilogue (warps 0..3 = the 128 rows of the tile): accumulator column 0 ----
             const uint32_t d = ti & 1;
@@ -377,9 +338,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
                 for (uint32_t sp2 = 0; sp2 < a.ksplit; sp2++)
                     sum += __ldcg(a.partials + (size_t)sp2 * a.n_tiles * 128 + pslot);
             }
-#ifdef T5_TIMING
-            if (a.dbg && blockIdx.x == 0 && tid == 0) atomicAdd(a.dbg + 7, (unsigned long long)(clock64() - _tt0));
-#endif
             if (a.mode == GEMV_SWIGLU) {
                 // quarters 0,1 hold gate rows, quarters 2,3 the up rows of the same output index
                 asm volatile("bar.sync 3, 128;\n" ::: "memory");  // ep of the previous tile has been read
@@ -421,25 +379,15 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
             const uint32_t dcol = tmem_base + T5_D_COL + d * (T5_NACC * 16);
             for (uint32_t c = 0; c < nch; c++, n++) {
                 const uint32_t stage = n % T5_STAGES, ph = (n / T5_STAGES) & 1;
-                { T5_T0(); mbar_wait(bar_full + 8 * stage, ph, err_flag); T5_ACC(0); }
-#ifndef T5_NO_FENCE
+                mbar_wait(bar_full + 8 * stage, ph, err_flag);
                 tc_fence_after();
-#endif
-                T5_T0();
                 const uint32_t acol = tmem_base + stage * 16;
                 const uint32_t m0 = 2 * c, m1 = 2 * c + 1;  // MMA number inside the tile
-#ifndef T5_NO_MMA
                 tc_mma_ts(dcol + (m0 % T5_NACC) * 16, acol, make_b_desc(xb_addr + c * 512), idesc, m0 >= T5_NACC);
                 tc_mma_ts(dcol + (m1 % T5_NACC) * 16, acol + 8, make_b_desc(xb_addr + c * 512 + 256), idesc, m1 >= T5_NACC);
-#else
-                (void)m0; (void)m1; (void)acol; (void)xb_addr; (void)idesc;
-#endif
                 // one commit per group of stages: a tcgen05.commit costs several hundred cycles of the
                 // tensor pipe's command stream, far more than the two small MMAs of a chunk
-#ifndef T5_NO_COMMIT
                 if (stage % T5_GROUP == T5_GROUP - 1) tc_commit(bar_empty + 8 * (stage / T5_GROUP));
-#endif
-                T5_ACC(1);
             }
             tc_commit(bar_dfull + 8 * d);
         }
@@ -460,11 +408,11 @@ bool tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t batch) {
 
 int launch_gemv_tc5(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
                     void *y, const uint16_t *resid) {
-    static bool configured[8] = {false};
-    if (!configured[ctx->device & 7]) {
+    static bool configured[PRISM_MAX_DEVICES] = {false};
+    if (!configured[ctx->device]) {
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)T5_SMEM_BYTES));
-        configured[ctx->device & 7] = true;
+        configured[ctx->device] = true;
     }
     Tc5Args a{};
     a.n_chunks = t.n_chunks;
@@ -509,28 +457,7 @@ int launch_gemv_tc5(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, cons
     if (grid == 0) grid = a.ksplit;
     const uint64_t tiles = (uint64_t)a.n_tiles * a.ksplit;
     if (grid > tiles) grid = (uint32_t)tiles;
-#ifdef T5_TIMING
-    static unsigned long long *dbg = nullptr;
-    if (!dbg) cudaMalloc((void **)&dbg, 128);
-    cudaMemsetAsync(dbg, 0, 128, ctx->stream);
-    a.dbg = dbg;
-#endif
     lut_gemv_tc5_kernel<<<grid, T5_THREADS, T5_SMEM_BYTES, ctx->stream>>>(a);
-#ifdef T5_TIMING
-    {
-        unsigned long long h[16];
-        cudaMemcpyAsync(h, dbg, 128, cudaMemcpyDeviceToHost, ctx->stream);
-        cudaStreamSynchronize(ctx->stream);
-        const double n = h[4] ? (double)h[4] : 1.0;  // chunks of warp 0 of CTA 0
-        fprintf(stderr, "[tc5 timing] m=%u k=%u ksplit=%u grid=%u | per chunk of one dequant warp (clk): ldg-wait %.0f lds-wait %.0f "
-                        "empty-wait %.0f st+wait %.0f | mma thread per chunk: full-wait %.0f issue %.0f (chunks/warp %.0f)\n",
-                t.m, t.k, a.ksplit, grid, h[0] / 16.0 / n, h[1] / 16.0 / n, h[2] / 16.0 / n, h[3] / 16.0 / n,
-                h[8] / (4.0 * n), h[9] / (4.0 * n), n);
-        const double nt = h[10] ? (double)h[10] : 1.0;
-        fprintf(stderr, "             warp 0 per tile (clk): build %.0f stream %.0f epilogue %.0f (tiles %.0f, chunks/tile %u)\n",
-                h[5] / nt, h[6] / nt, h[7] / nt, nt, a.chunks_per_split);
-    }
-#endif
     return after_launch(ctx, "lut_gemv_tc5_kernel");
 }
 

@@ -23,21 +23,12 @@
 
 namespace prism {
 
-#ifndef WS_NC_N
-#define WS_NC_N 20
-#endif
-#ifndef WS_NB_N
-#define WS_NB_N 4
-#endif
-#ifndef WS_PF_N
-#define WS_PF_N 2
-#endif
-constexpr int WS_NC = WS_NC_N;                  // compute warps
-constexpr int WS_NB = WS_NB_N;                  // builder warps
+constexpr int WS_NC = 20;                       // compute warps
+constexpr int WS_NB = 4;                        // builder warps
 static_assert(WS_NB * 32 == WS_COMMON_BTHREADS, "the finish step (scratch sizes, two groups of 64 threads) is written for 128 builder threads");
 constexpr int WS_THREADS = (WS_NC + WS_NB) * 32;
 constexpr int WS_BTHREADS = WS_NB * 32;
-constexpr int WS_PF = WS_PF_N;                  // index chunks in flight per compute warp (1, 2 or 4)
+constexpr int WS_PF = 2;                        // index chunks in flight per compute warp (1, 2 or 4)
 constexpr int WS_STAGE_CHUNKS = 256;            // chunks of x per stage (8192 halves, 16 KB)
 constexpr int WS_TBL_BYTES = 65536;             // one pair-table buffer
 constexpr int WS_X_OFF = 2 * WS_TBL_BYTES;      // two x buffers
@@ -48,14 +39,6 @@ constexpr int WS_BAR_OFF = WS_FIN_OFF + 256 * 4;            // full[2], empty[2]
 constexpr size_t WS_SMEM_BYTES = WS_BAR_OFF + 64;
 constexpr int WS_KNOWN_SBASE = 1024;
 
-#ifdef WS_TIMING
-// Debug builds: per-phase clock stamps of CTA 0 (SM clock cycles since kernel entry).
-__device__ unsigned long long g_ws_timing[16];
-#define WS_STAMP(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_ws_timing[i] = clock64() - g_ws_t0; } while (0)
-__device__ unsigned long long g_ws_t0;
-#else
-#define WS_STAMP(i) do { } while (0)
-#endif
 
 // One 32-weight chunk of the two half-blocks (see sk_chunk in gemv_sk.cu for the operand layout);
 // compute warps are WS_NC chunks apart.
@@ -120,9 +103,7 @@ __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint3
 #pragma unroll
             for (int i = 0; i < 2; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
         }
-        if (t == 0 && cw == 0) WS_STAMP(4);
         ws_wait(bar_full + 8 * xbuf, par, err_flag);
-        if (t == 0 && cw == 0) WS_STAMP(5);
         const uint32_t lane_off = lane * 4 | (tb << 16);
         uint32_t x_off = xbuf * WS_X_BYTES + cw * 64;
 #define WS_STEP(I)                                                                                            \
@@ -149,7 +130,6 @@ __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint3
             }
         }
         t5::mbar_arrive(bar_empty + 8 * xbuf);  // every lane: its reads of the buffers and its sums are done
-        if (cw == 0) WS_STAMP(6);  // overwritten every stage: the last one stays
     }
 }
 
@@ -295,11 +275,9 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
             }
         }
         if (!waited) {
-            if (bw == 0) WS_STAMP(1);
             // Everything above reads only weights.  x, the partial sums, the counters and y belong to
             // the stream order: wait for the kernels before this one.
             pdl_wait();
-            if (bw == 0) WS_STAMP(2);
             waited = true;
             // RMSNorm folded into the staging (rms_norm_inplace, src/lut/cpu_fallback.rs:39-54): every CTA
             // sums the squares of the whole row once (a few KB from L2) and scales the slices it stages.
@@ -399,9 +377,7 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
             }
         }
         t5::mbar_arrive(bar_full + 8 * xbuf);  // every builder thread: its table entries and x words are stored
-        if (t == 0 && bw == 0) WS_STAMP(3);
     }
-    if (bw == 0) WS_STAMP(7);
     // retire the last two stages in order
     const uint32_t n_stages = t;
     for (uint32_t r = (n_stages >= 2 ? n_stages - 2 : 0); r < n_stages; r++) {
@@ -409,7 +385,6 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
         ws_wait(bar_empty + 8 * xbuf, (r >> 1) & 1, err_flag);
         if (hist[xbuf].last) ws_finish<MODE>(a, smem, hist[xbuf], bt, cta, G, bat);
     }
-    if (bw == 0) WS_STAMP(8);
 }
 
 template <int MODE, int SBASE>
@@ -421,9 +396,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lut_gemv_ws_kernel(const SkArgs
         return;
     }
     pdl_launch_dependents();
-#ifdef WS_TIMING
-    if (blockIdx.x == 0 && threadIdx.x == 0) g_ws_t0 = clock64();
-#endif
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t cta = blockIdx.x, G = gridDim.x, bat = blockIdx.y;
     const uint32_t u_begin = sk_boundary(a.part, cta);
@@ -449,11 +421,11 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lut_gemv_ws_kernel(const SkArgs
 
 template <int MODE, int SBASE>
 static int launch_ws_v(prism_cuda_ctx *ctx, const SkArgs &a, dim3 grid) {
-    static bool configured[8] = {false};
-    if (!configured[ctx->device & 7]) {
+    static bool configured[PRISM_MAX_DEVICES] = {false};
+    if (!configured[ctx->device]) {
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_ws_kernel<MODE, SBASE>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM_BYTES));
-        configured[ctx->device & 7] = true;
+        configured[ctx->device] = true;
     }
     launch_pdl(ctx, "lut_gemv_ws_kernel", lut_gemv_ws_kernel<MODE, SBASE>, grid, WS_THREADS, WS_SMEM_BYTES, a);
     return after_launch(ctx, "lut_gemv_ws_kernel");
@@ -518,8 +490,3 @@ int launch_gemv_ws(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const
 
 }  // namespace prism
 
-#ifdef WS_TIMING
-extern "C" int prism_debug_ws_timing(unsigned long long *out) {
-    return (int)cudaMemcpyFromSymbol(out, prism::g_ws_timing, sizeof(unsigned long long) * 16);
-}
-#endif

@@ -21,10 +21,6 @@
 
 namespace prism {
 
-#ifdef WB_TIMING
-// Debug builds: cycles compute warp 0 of CTA 0 spends waiting (full barrier, sum buffer) and in total.
-__device__ unsigned long long g_wb_timing[8];
-#endif
 
 constexpr int WB_NC_MAX = 16;                    // compute warps: 16 for one or two sequence pairs, 12 (more registers) for three or four
 constexpr int WB_NB = 4;                         // builder warps
@@ -162,13 +158,7 @@ __device__ __forceinline__ void wb_compute(const SkArgs &a, uint8_t *smem, uint3
 #pragma unroll
                 for (int i = 0; i < 2; i++) acc[p][i][0] = acc[p][i][1] = acc[p][i][2] = acc[p][i][3] = 0.f;
         }
-#ifdef WB_TIMING
-        const long long tw0 = clock64();
-#endif
         ws_wait(bar_full + 8 * xbuf, par, err_flag);
-#ifdef WB_TIMING
-        if (blockIdx.x == 0 && cw == 0 && lane == 0) { g_wb_timing[0] += clock64() - tw0; g_wb_timing[3] += 1; }
-#endif
         const uint32_t lane_off = lane * 4 | (tb << 16);
         uint32_t x_off = xbuf * WB_X_BYTES + (lane >> 4) * Geo::ROW_BYTES + cw * 64;
         if (CONT) {
@@ -195,13 +185,7 @@ __device__ __forceinline__ void wb_compute(const SkArgs &a, uint8_t *smem, uint3
         }
         if (st.last) {
             // the builders have read the sums of the segment before this one
-#ifdef WB_TIMING
-            const long long tr0 = clock64();
-#endif
             if (segs_done > 0) ws_wait(bar_red, (segs_done - 1) & 1, err_flag);
-#ifdef WB_TIMING
-            if (blockIdx.x == 0 && cw == 0 && lane == 0) g_wb_timing[1] += clock64() - tr0;
-#endif
             // lane (g, t): accumulator columns 2t, 2t+1 of MMA rows g (half-block 1) and g+8 (half-block 2):
             // column n belongs to lane 4g + n%4 and to sequence 2p + n/4
             const uint32_t r = (lane >> 2) * 4 + (lane & 1) * 2;
@@ -443,14 +427,7 @@ __global__ void __launch_bounds__(WbGeom<NBP>::THREADS, 1) lut_gemv_wsb_kernel(c
     }
     __syncthreads();
     if (warp < NC) {
-#ifdef WB_TIMING
-        const long long tk0 = clock64();
-        if (blockIdx.x == 0 && tid == 0) { g_wb_timing[0] = g_wb_timing[1] = g_wb_timing[3] = 0; }
-#endif
         wb_compute<SBASE, NBP>(a, smem, smem_base, u_begin, u_end, warp, lane, err_flag);
-#ifdef WB_TIMING
-        if (blockIdx.x == 0 && tid == 0) g_wb_timing[2] = clock64() - tk0;
-#endif
     } else {
         wb_build<MODE, NBP>(wa, smem, smem_base, u_begin, u_end, tid - NC * 32, cta, G, err_flag);
         if (*err_flag && tid == NC * 32) atomicExch(a.err, 2u);  // a hand-over wait gave up
@@ -459,11 +436,11 @@ __global__ void __launch_bounds__(WbGeom<NBP>::THREADS, 1) lut_gemv_wsb_kernel(c
 
 template <int MODE, int SBASE, int NBP>
 static int launch_wsb_v(prism_cuda_ctx *ctx, const WbArgs &wa, dim3 grid) {
-    static bool configured[8] = {false};
-    if (!configured[ctx->device & 7]) {
+    static bool configured[PRISM_MAX_DEVICES] = {false};
+    if (!configured[ctx->device]) {
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_wsb_kernel<MODE, SBASE, NBP>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WB_SMEM_BYTES));
-        configured[ctx->device & 7] = true;
+        configured[ctx->device] = true;
     }
     launch_pdl(ctx, "lut_gemv_wsb_kernel", lut_gemv_wsb_kernel<MODE, SBASE, NBP>, grid, WbGeom<NBP>::THREADS, WB_SMEM_BYTES, wa);
     return after_launch(ctx, "lut_gemv_wsb_kernel");
@@ -526,8 +503,3 @@ int launch_gemv_wsb(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, cons
 
 }  // namespace prism
 
-#ifdef WB_TIMING
-extern "C" int prism_debug_wb_timing(unsigned long long *out) {
-    return (int)cudaMemcpyFromSymbol(out, prism::g_wb_timing, sizeof(unsigned long long) * 8);
-}
-#endif

@@ -487,16 +487,16 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_f16_kernel(AttnArgs a)
 int launch_attention(prism_cuda_ctx *ctx, const AttnArgs &a) {
     if (a.hd > 256 || a.hd == 0 || ATTN_THREADS % a.hd != 0)
         return fail(ctx, PRISM_E_ARG, "attention: head_dim must divide 256");
-    static bool configured[8] = {false};
+    static bool configured[PRISM_MAX_DEVICES] = {false};
     const size_t smem = (size_t)a.max_seq * sizeof(float);
     if (smem > 160 * 1024) return fail(ctx, PRISM_E_ARG, "attention: max_seq too large for the score buffer");
-    if (smem > 32 * 1024 && !configured[ctx->device & 7]) {
+    if (smem > 32 * 1024 && !configured[ctx->device]) {
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_f16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_f16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_f16_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_f16_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        configured[ctx->device & 7] = true;
+        configured[ctx->device] = true;
     }
     dim3 grid(a.nh, a.batch);
     const bool vec_ok = !a.int8 && (a.hd == 32 || a.hd == 64 || a.hd == 128 || a.hd == 256) &&

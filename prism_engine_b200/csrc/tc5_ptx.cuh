@@ -47,9 +47,7 @@ __device__ __forceinline__ void mbar_wait_warp(uint32_t addr, uint32_t parity, v
             if (mbar_test(addr, parity)) break;
             if ((i & 63) == 63 && *err_flag) break;
             if (i + 1 == limit) *err_flag = 1;
-#ifndef T5_NO_SLEEP
             __nanosleep(32);
-#endif
         }
     }
     __syncwarp();

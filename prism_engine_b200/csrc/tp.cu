@@ -59,6 +59,7 @@ static prism_nccl_api *load_nccl(std::string &err) {
 
 int tp_all_reduce_f32(prism_cuda_ctx *ctx, float *buf, size_t n) {
     if (ctx->tp_world <= 1) return PRISM_OK;
+    if (!ctx->nccl || !ctx->nccl_comm) return fail(ctx, PRISM_E_STATE, "no NCCL communicator on this context");
     ncclResult_t r = ctx->nccl->AllReduce(buf, buf, n, ncclFloat32, ncclSum, (ncclComm_t)ctx->nccl_comm, ctx->stream);
     if (r != ncclSuccess) return fail(ctx, PRISM_E_COMM, std::string("ncclAllReduce: ") + ctx->nccl->GetErrorString(r));
     ctx->launches++;
@@ -67,6 +68,7 @@ int tp_all_reduce_f32(prism_cuda_ctx *ctx, float *buf, size_t n) {
 
 int tp_all_gather_bytes(prism_cuda_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank) {
     if (ctx->tp_world <= 1) return PRISM_OK;
+    if (!ctx->nccl || !ctx->nccl_comm) return fail(ctx, PRISM_E_STATE, "no NCCL communicator on this context");
     ncclResult_t r = ctx->nccl->AllGather(send, recv, bytes_per_rank, ncclUint8, (ncclComm_t)ctx->nccl_comm, ctx->stream);
     if (r != ncclSuccess) return fail(ctx, PRISM_E_COMM, std::string("ncclAllGather: ") + ctx->nccl->GetErrorString(r));
     ctx->launches++;
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(TP_AR_THREADS) tp_ar_resid_kernel(const float 
                                                                     float *recv, unsigned int *flags,
                                                                     unsigned int *state, uint32_t world,
                                                                     uint32_t rank, uint32_t cap,
-                                                                    unsigned int *err) {
+                                                                    unsigned int *err, uint32_t spin_limit) {
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t cta = blockIdx.x, tid = threadIdx.x;
@@ -119,14 +121,14 @@ __global__ void __launch_bounds__(TP_AR_THREADS) tp_ar_resid_kernel(const float 
         unsigned int *f = static_cast<unsigned int *>(peer_tab[world + tid]) + rank * TP_AR_MAX_CTAS + cta;
         asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(f), "r"(e) : "memory");
     }
-    // ---- wait for the same slice of every rank ----
+    // ---- wait for the same slice of every rank (bounded: spin_limit polls, then error code 3) ----
     if (tid < world) {
         const unsigned int *f = flags + tid * TP_AR_MAX_CTAS + cta;
         unsigned int seen = 0, polls = 0;
         for (;;) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(f) : "memory");
             if ((int)(seen - e) >= 0) break;  // a peer that is already one all-reduce ahead has delivered this one too
-            if (++polls > TP_AR_SPIN_LIMIT) {
+            if (++polls > spin_limit) {
                 atomicExch(err, 3u);  // a peer did not deliver: reported by the next host call
                 break;
             }
@@ -169,87 +171,17 @@ bool tp_peer_ar_ok(prism_cuda_ctx *ctx, size_t n) {
 }
 
 int tp_all_reduce_resid_peer(prism_cuda_ctx *ctx, const float *part, uint16_t *h, size_t n) {
-    if (!tp_peer_ar_ok(ctx, n)) return fail(ctx, PRISM_E_STATE, "peer-memory all-reduce not available for this size");
+    if (!tp_peer_ar_ok(ctx, n))
+        return fail(ctx, PRISM_E_STATE, "peer-memory all-reduce not available" +
+                                            (ctx->tp_peer_reason.empty() ? std::string(" for this size") : ": " + ctx->tp_peer_reason));
     const unsigned ctas = (unsigned)((n + TP_AR_THREADS * 4 - 1) / (TP_AR_THREADS * 4));
     launch_pdl(ctx, "tp_ar_resid_kernel", tp_ar_resid_kernel, dim3(ctas), dim3(TP_AR_THREADS), 0, part, h, (uint32_t)n,
                (void *const *)ctx->tp_peer_tab, ctx->tp_recv, ctx->tp_flags, ctx->tp_state, (uint32_t)ctx->tp_world,
-               (uint32_t)ctx->tp_rank, (uint32_t)ctx->tp_cap, ctx->dev_err);
+               (uint32_t)ctx->tp_rank, (uint32_t)ctx->tp_cap, ctx->dev_err, wait_limit(ctx, TP_AR_SPIN_LIMIT));
     return after_launch(ctx, "tp_ar_resid_kernel");
 }
 
-// Allocates this rank's receive area and flags, exchanges the IPC handles through NCCL and maps the
-// peers'.  Any failure leaves tp_cap = 0: the engine then reduces with ncclAllReduce.
-static int tp_peer_setup(prism_cuda_ctx *ctx) {
-    const int T = ctx->tp_world;
-    if (T > 16) return PRISM_OK;
-    const size_t recv_bytes = 2ull * T * TP_AR_CAP_FLOATS * sizeof(float);
-    const size_t flag_bytes = (size_t)T * TP_AR_MAX_CTAS * sizeof(unsigned int);
-    struct Handles { cudaIpcMemHandle_t recv, flags; };
-    Handles mine{}, *all_dev = nullptr;
-    std::vector<Handles> all(T);
-    auto give_up = [&](const char *why) {
-        (void)why;
-        (void)cudaGetLastError();
-        ctx->tp_cap = 0;
-        return PRISM_OK;
-    };
-    if (cudaMalloc((void **)&ctx->tp_recv, recv_bytes) != cudaSuccess) return give_up("cudaMalloc");
-    if (cudaMalloc((void **)&ctx->tp_flags, flag_bytes) != cudaSuccess) return give_up("cudaMalloc");
-    if (cudaMalloc((void **)&ctx->tp_state, 2 * sizeof(unsigned int)) != cudaSuccess) return give_up("cudaMalloc");
-    if (cudaMalloc((void **)&ctx->tp_peer_tab, 2 * T * sizeof(void *)) != cudaSuccess) return give_up("cudaMalloc");
-    cudaMemsetAsync(ctx->tp_flags, 0, flag_bytes, ctx->stream);
-    cudaMemsetAsync(ctx->tp_state, 0, 2 * sizeof(unsigned int), ctx->stream);
-    if (cudaIpcGetMemHandle(&mine.recv, ctx->tp_recv) != cudaSuccess) return give_up("cudaIpcGetMemHandle");
-    if (cudaIpcGetMemHandle(&mine.flags, ctx->tp_flags) != cudaSuccess) return give_up("cudaIpcGetMemHandle");
-    if (cudaMalloc((void **)&all_dev, sizeof(Handles) * (T + 1)) != cudaSuccess) return give_up("cudaMalloc");
-    cudaMemcpyAsync(all_dev + T, &mine, sizeof(Handles), cudaMemcpyHostToDevice, ctx->stream);
-    int rc = tp_all_gather_bytes(ctx, all_dev + T, all_dev, sizeof(Handles));
-    if (rc == PRISM_OK) {
-        cudaMemcpyAsync(all.data(), all_dev, sizeof(Handles) * T, cudaMemcpyDeviceToHost, ctx->stream);
-        if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = PRISM_E_CUDA;
-    }
-    cudaFree(all_dev);
-    if (rc != PRISM_OK) return give_up("all-gather of handles");
-    std::vector<void *> tab(2 * T, nullptr);
-    bool ok = true;
-    for (int q = 0; q < T && ok; q++) {
-        if (q == ctx->tp_rank) {
-            tab[q] = ctx->tp_recv;
-            tab[T + q] = ctx->tp_flags;
-            continue;
-        }
-        void *pr = nullptr, *pf = nullptr;
-        if (cudaIpcOpenMemHandle(&pr, all[q].recv, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
-            cudaIpcOpenMemHandle(&pf, all[q].flags, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
-            ctx->tp_peer_map[q] = pr;  // closed at shutdown if it was opened
-            ok = false;
-            break;
-        }
-        tab[q] = pr;
-        tab[T + q] = pf;
-        ctx->tp_peer_map[q] = pr;
-        ctx->tp_peer_map[16 + q] = pf;
-    }
-    // every rank must take the same path: agree on the outcome (min over ranks)
-    float flag_host = ok ? 1.0f : 0.0f, *flag_dev = nullptr;
-    if (cudaMalloc((void **)&flag_dev, sizeof(float)) != cudaSuccess) return give_up("cudaMalloc");
-    cudaMemcpyAsync(flag_dev, &flag_host, sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
-    ncclResult_t r = ctx->nccl->AllReduce(flag_dev, flag_dev, 1, ncclFloat32, ncclMin, (ncclComm_t)ctx->nccl_comm, ctx->stream);
-    cudaMemcpyAsync(&flag_host, flag_dev, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
-    cudaStreamSynchronize(ctx->stream);
-    cudaFree(flag_dev);
-    if (r != ncclSuccess || flag_host < 0.5f) return give_up("a rank could not map its peers");
-    if (cudaMemcpy(ctx->tp_peer_tab, tab.data(), 2 * T * sizeof(void *), cudaMemcpyHostToDevice) != cudaSuccess)
-        return give_up("cudaMemcpy");
-    ctx->tp_cap = TP_AR_CAP_FLOATS;
-    return PRISM_OK;
-}
-
-}  // namespace prism
-
-using namespace prism;
-
-extern "C" void prism_tp_shutdown(prism_cuda_ctx *ctx) {
+static void tp_peer_release(prism_cuda_ctx *ctx) {
     for (int q = 0; q < 32; q++) {
         if (ctx->tp_peer_map[q]) {
             cudaIpcCloseMemHandle(ctx->tp_peer_map[q]);
@@ -262,6 +194,129 @@ extern "C" void prism_tp_shutdown(prism_cuda_ctx *ctx) {
     cudaFree(ctx->tp_peer_tab);
     ctx->tp_recv = nullptr; ctx->tp_flags = nullptr; ctx->tp_state = nullptr; ctx->tp_peer_tab = nullptr;
     ctx->tp_cap = 0;
+}
+
+// This rank's receive area, flags, epoch state and the (still empty) pointer table.
+static bool tp_peer_alloc(prism_cuda_ctx *ctx, int T, std::string &why) {
+    const size_t recv_bytes = 2ull * T * TP_AR_CAP_FLOATS * sizeof(float);
+    const size_t flag_bytes = (size_t)T * TP_AR_MAX_CTAS * sizeof(unsigned int);
+    cudaError_t e;
+    if ((e = cudaMalloc((void **)&ctx->tp_recv, recv_bytes)) != cudaSuccess ||
+        (e = cudaMalloc((void **)&ctx->tp_flags, flag_bytes)) != cudaSuccess ||
+        (e = cudaMalloc((void **)&ctx->tp_state, 2 * sizeof(unsigned int))) != cudaSuccess ||
+        (e = cudaMalloc((void **)&ctx->tp_peer_tab, 2 * T * sizeof(void *))) != cudaSuccess ||
+        (e = cudaMemsetAsync(ctx->tp_flags, 0, flag_bytes, ctx->stream)) != cudaSuccess ||
+        (e = cudaMemsetAsync(ctx->tp_state, 0, 2 * sizeof(unsigned int), ctx->stream)) != cudaSuccess) {
+        why = std::string("receive area allocation: ") + cudaGetErrorString(e);
+        (void)cudaGetLastError();
+        return false;
+    }
+    return true;
+}
+
+// Allocates this rank's receive area and flags, exchanges the IPC handles through NCCL and maps the
+// peers'.  A rank on which a local step fails still takes part in both collectives (with a zeroed
+// handle and a "not ok" vote), so no peer is left waiting inside NCCL; the outcome is agreed with a
+// min-reduce and every rank takes the same path.  On failure tp_cap stays 0 (the engine then reduces
+// with ncclAllReduce), everything allocated here is freed and tp_peer_reason says why.
+static int tp_peer_setup(prism_cuda_ctx *ctx) {
+    const int T = ctx->tp_world;
+    ctx->tp_peer_reason.clear();
+    if (T > 16) {
+        ctx->tp_peer_reason = "more than 16 ranks";
+        return PRISM_OK;
+    }
+    struct Handles { cudaIpcMemHandle_t recv, flags; };
+    Handles mine{};
+    std::vector<Handles> all(T);
+    std::string why;
+    bool ok = tp_peer_alloc(ctx, T, why);
+    if (ok) {
+        cudaError_t e;
+        if ((e = cudaIpcGetMemHandle(&mine.recv, ctx->tp_recv)) != cudaSuccess ||
+            (e = cudaIpcGetMemHandle(&mine.flags, ctx->tp_flags)) != cudaSuccess) {
+            why = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e);
+            (void)cudaGetLastError();
+            mine = Handles{};
+            ok = false;
+        }
+    }
+    // ---- collective 1: everybody's handles (a rank that failed above sends zeros) ----
+    Handles *all_dev = nullptr;
+    float *flag_dev = nullptr;
+    const bool have_tmp = cudaMalloc((void **)&all_dev, sizeof(Handles) * (T + 1)) == cudaSuccess &&
+                          cudaMalloc((void **)&flag_dev, sizeof(float)) == cudaSuccess;
+    if (!have_tmp) {
+        // Without these few bytes this rank cannot even vote; the peers' collectives would wait for it.
+        // Report it as an error of tp_init instead of silently degrading.
+        (void)cudaGetLastError();
+        cudaFree(all_dev);
+        cudaFree(flag_dev);
+        tp_peer_release(ctx);
+        return fail(ctx, PRISM_E_CUDA, "tensor parallel set-up: out of device memory for the handle exchange");
+    }
+    cudaMemcpyAsync(all_dev + T, &mine, sizeof(Handles), cudaMemcpyHostToDevice, ctx->stream);
+    int rc = tp_all_gather_bytes(ctx, all_dev + T, all_dev, sizeof(Handles));
+    if (rc == PRISM_OK) {
+        cudaMemcpyAsync(all.data(), all_dev, sizeof(Handles) * T, cudaMemcpyDeviceToHost, ctx->stream);
+        if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = PRISM_E_CUDA;
+    }
+    if (rc != PRISM_OK && ok) {
+        why = "all-gather of the IPC handles failed";
+        ok = false;
+    }
+    std::vector<void *> tab(2 * T, nullptr);
+    for (int q = 0; q < T && ok; q++) {
+        if (q == ctx->tp_rank) {
+            tab[q] = ctx->tp_recv;
+            tab[T + q] = ctx->tp_flags;
+            continue;
+        }
+        void *pr = nullptr, *pf = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&pr, all[q].recv, cudaIpcMemLazyEnablePeerAccess);
+        if (e == cudaSuccess) {
+            ctx->tp_peer_map[q] = pr;
+            e = cudaIpcOpenMemHandle(&pf, all[q].flags, cudaIpcMemLazyEnablePeerAccess);
+            if (e == cudaSuccess) ctx->tp_peer_map[16 + q] = pf;
+        }
+        if (e != cudaSuccess) {
+            why = "cudaIpcOpenMemHandle(rank " + std::to_string(q) + "): " + cudaGetErrorString(e);
+            (void)cudaGetLastError();
+            ok = false;
+            break;
+        }
+        tab[q] = pr;
+        tab[T + q] = pf;
+    }
+    if (ok && cudaMemcpy(ctx->tp_peer_tab, tab.data(), 2 * T * sizeof(void *), cudaMemcpyHostToDevice) != cudaSuccess) {
+        why = "copy of the peer pointer table failed";
+        (void)cudaGetLastError();
+        ok = false;
+    }
+    // ---- collective 2: every rank must take the same path: agree on the outcome (min over ranks) ----
+    float flag_host = ok ? 1.0f : 0.0f;
+    cudaMemcpyAsync(flag_dev, &flag_host, sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+    ncclResult_t r = ctx->nccl->AllReduce(flag_dev, flag_dev, 1, ncclFloat32, ncclMin, (ncclComm_t)ctx->nccl_comm, ctx->stream);
+    cudaMemcpyAsync(&flag_host, flag_dev, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(all_dev);
+    cudaFree(flag_dev);
+    if (r != ncclSuccess || flag_host < 0.5f) {
+        if (ok) why = r != ncclSuccess ? "the agreement all-reduce failed" : "another rank could not map its peers";
+        tp_peer_release(ctx);
+        ctx->tp_peer_reason = why;
+        return PRISM_OK;
+    }
+    ctx->tp_cap = TP_AR_CAP_FLOATS;
+    return PRISM_OK;
+}
+
+}  // namespace prism
+
+using namespace prism;
+
+extern "C" void prism_tp_shutdown(prism_cuda_ctx *ctx) {
+    tp_peer_release(ctx);
     if (ctx->nccl_comm && ctx->nccl) {
         ctx->nccl->CommDestroy((ncclComm_t)ctx->nccl_comm);
         ctx->nccl_comm = nullptr;
@@ -317,9 +372,49 @@ int prism_cuda_tp_world(prism_cuda_ctx *ctx, int *world, int *rank) {
 
 int prism_cuda_tp_peer_ready(prism_cuda_ctx *ctx) { return (ctx && ctx->tp_world > 1 && ctx->tp_cap != 0) ? 1 : 0; }
 
+const char *prism_cuda_tp_peer_reason(prism_cuda_ctx *ctx) { return ctx ? ctx->tp_peer_reason.c_str() : ""; }
+
+int prism_cuda_tp_init_loopback(prism_cuda_ctx *ctx, int world, int rank) {
+    if (!ctx) return PRISM_E_NULL;
+    if (world < 2 || world > 16 || rank < 0 || rank >= world) return fail(ctx, PRISM_E_ARG, "bad world/rank");
+    if (ctx->nccl_comm || ctx->tp_cap) return fail(ctx, PRISM_E_STATE, "tensor parallel group already initialised");
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    std::string why;
+    if (!tp_peer_alloc(ctx, world, why)) {
+        tp_peer_release(ctx);
+        return fail(ctx, PRISM_E_CUDA, why);
+    }
+    // every "peer" is this GPU's own receive area and flag array: rank `rank` delivers to itself, the
+    // other ranks' slices and flags are never written
+    std::vector<void *> tab(2 * world, nullptr);
+    for (int q = 0; q < world; q++) {
+        tab[q] = ctx->tp_recv;
+        tab[world + q] = ctx->tp_flags;
+    }
+    cudaError_t e = cudaMemcpy(ctx->tp_peer_tab, tab.data(), 2 * world * sizeof(void *), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        tp_peer_release(ctx);
+        return cuda_fail(ctx, e, "cudaMemcpy(peer table)");
+    }
+    ctx->tp_world = world;
+    ctx->tp_rank = rank;
+    ctx->tp_loopback = true;
+    ctx->tp_cap = TP_AR_CAP_FLOATS;
+    return PRISM_OK;
+}
+
+int prism_cuda_tp_all_reduce_resid_dev(prism_cuda_ctx *ctx, const void *partial_f32_dev, void *h_f16_dev, size_t n) {
+    if (!ctx || !partial_f32_dev || !h_f16_dev) return fail(ctx, PRISM_E_NULL, "null argument");
+    if (n == 0) return PRISM_OK;
+    if ((reinterpret_cast<uintptr_t>(partial_f32_dev) & 15) || (reinterpret_cast<uintptr_t>(h_f16_dev) & 7))
+        return fail(ctx, PRISM_E_ARG, "all_reduce_resid: partial sums must be 16-byte aligned, h 8-byte aligned");
+    return tp_all_reduce_resid_peer(ctx, static_cast<const float *>(partial_f32_dev), static_cast<uint16_t *>(h_f16_dev), n);
+}
+
 int prism_cuda_tp_all_reduce_dev(prism_cuda_ctx *ctx, void *buf_dev, size_t n_halfs) {
     if (!ctx || !buf_dev) return fail(ctx, PRISM_E_NULL, "null argument");
     if (ctx->tp_world <= 1) return PRISM_OK;
+    if (!ctx->nccl || !ctx->nccl_comm) return fail(ctx, PRISM_E_STATE, "no NCCL communicator on this context");
     ncclResult_t r = ctx->nccl->AllReduce(buf_dev, buf_dev, n_halfs, ncclFloat16, ncclSum,
                                           (ncclComm_t)ctx->nccl_comm, ctx->stream);
     if (r != ncclSuccess) return fail(ctx, PRISM_E_COMM, std::string("ncclAllReduce: ") + ctx->nccl->GetErrorString(r));
