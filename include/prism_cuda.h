@@ -246,6 +246,14 @@ int prism_cuda_kv_init(prism_cuda_ctx *ctx, uint32_t num_layers, uint32_t kv_dim
 int prism_cuda_kv_append(prism_cuda_ctx *ctx, uint32_t layer, const uint16_t *k, const uint16_t *v, uint64_t token_idx);
 int prism_cuda_attention_kv(prism_cuda_ctx *ctx, uint32_t layer, const uint16_t *q, uint32_t seq_len, uint32_t num_heads,
                             uint32_t kv_heads, uint32_t head_dim, uint16_t *out);
+/* One decode step's attention nodes on the backend-held cache, as ONE kernel (the one the engine's step
+ * uses): RoPE of q (rope_inplace, cpu_fallback.rs:131-143; `rope_base` explicit), RoPE of k when rope_k
+ * is set (the reference caches K un-rotated, engine_impl.rs:1131 precedes :1211), KVCache::append of this
+ * token's k and v at position token_idx, and attention_cpu over positions 0..token_idx.  head_dim must be
+ * 32, 64, 128 or 256.  q: num_heads*head_dim, k / v: kv_dim values (host). */
+int prism_cuda_attention_step_kv(prism_cuda_ctx *ctx, uint32_t layer, const uint16_t *q, const uint16_t *k,
+                                 const uint16_t *v, uint64_t token_idx, uint32_t num_heads, uint32_t kv_heads,
+                                 uint32_t head_dim, uint32_t rope_k, float rope_base, uint16_t *out);
 /* argmax (engine_impl.rs:1448-1459): first strictly greatest. */
 int prism_cuda_argmax(prism_cuda_ctx *ctx, const uint16_t *logits, uint32_t n, uint32_t *index);
 
@@ -317,21 +325,6 @@ double prism_cuda_engine_last_device_ms(prism_cuda_engine *eng);
 uint32_t prism_cuda_engine_position(prism_cuda_engine *eng);
 /* Kernels one step launches (counted when the step was first enqueued). */
 uint32_t prism_cuda_engine_kernels_per_step(prism_cuda_engine *eng);
-/* Measurement: times only the palettized GEMV launches of a decode step, `reps`
- * passes over every weight of the model between two events on the context
- * stream; returns elapsed ms, algorithmic bytes moved and launches issued. */
-int prism_cuda_engine_profile_gemv(prism_cuda_engine *eng, uint32_t reps, double *ms_out,
-                                   uint64_t *bytes_out, uint32_t *launches_out);
-/* Measurement: cycles through n_sets distinct weight sets (working set > L2) inside one
- * CUDA graph replayed `reps` times.  kind 0 = GEMV (1 handle per set), 1 = fused
- * gate/up (gate, up), 2 = MLP (gate, up, down). */
-int prism_cuda_bench_cycle(prism_cuda_ctx *ctx, int kind, const int32_t *handles, uint32_t n_sets,
-                           uint32_t reps, double *ms_out);
-/* Measurement: `reps` prefill GEMMs of m_tok activation rows against one tensor between two
- * events on the context stream (activations are pattern data made on the device). */
-int prism_cuda_bench_gemm(prism_cuda_ctx *ctx, int32_t handle, uint32_t m_tok, uint32_t reps,
-                          double *ms_out);
-
 /* ---- tensor parallelism (not in the reference; column/row-sharded linears
  *      with an all-reduce after each row-parallel matmul) ------------------- */
 

@@ -8,4 +8,4 @@ from ._lib import ModelConfig, PrismCudaError  # noqa: F401
 from .backend import (QWEN25_0P5B, QWEN25_7B, QWEN25_72B, CudaBackend, PrismEngine,  # noqa: F401
                       model_config)
 from .cimage import CImageReader, CImageWriter  # noqa: F401
-from .graph import ModelGraph, UnifiedConfig  # noqa: F401
+from .graph import ModelGraph, UnifiedConfig, generate_plan  # noqa: F401

@@ -44,7 +44,7 @@ class CImagePlan(C.Structure):
                 ("attention_strategy", C.c_char * 24), ("lm_head_backend", C.c_char * 16)]
 
 
-# name -> (restype, argtypes); every symbol include/prism_cuda.h declares
+# name -> (restype, argtypes); every symbol include/prism_cuda.h and include/prism_cuda_bench.h declare
 _vp, _i32, _u32, _u64, _sz = C.c_void_p, C.c_int32, C.c_uint32, C.c_uint64, C.c_size_t
 _cp = C.c_char_p
 _pi32, _pu32 = C.POINTER(C.c_int32), C.POINTER(C.c_uint32)
@@ -100,9 +100,10 @@ SIGNATURES = {
     "prism_cuda_engine_last_device_ms": (C.c_double, [_vp]),
     "prism_cuda_engine_kernels_per_step": (_u32, [_vp]),
     "prism_cuda_engine_profile_gemv": (C.c_int, [_vp, _u32, C.POINTER(C.c_double), C.POINTER(_u64), _pu32]),
-    "prism_cuda_bench_cycle": (C.c_int, [_vp, C.c_int, _pi32, _u32, _u32, C.POINTER(C.c_double)]),
+    "prism_cuda_bench_cycle": (C.c_int, [_vp, C.c_int, _pi32, _u32, _u32, _vp, C.POINTER(C.c_double)]),
+    "prism_cuda_engine_profile_part": (C.c_int, [_vp, _u32, _u32, C.POINTER(C.c_double), _pu32]),
     "prism_cuda_load_cimage": (C.c_int, [_vp, _cp, _pu32]),
-    "prism_cuda_bench_gemm": (C.c_int, [_vp, _i32, _u32, _u32, C.POINTER(C.c_double)]),
+    "prism_cuda_bench_gemm": (C.c_int, [_vp, _i32, _vp, _u32, _u32, C.POINTER(C.c_double)]),
     "prism_cuda_tp_unique_id": (C.c_int, [_vp]),
     "prism_cuda_tp_init": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
     "prism_cuda_tp_world": (C.c_int, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
@@ -119,6 +120,7 @@ SIGNATURES = {
     "prism_cuda_kv_init": (C.c_int, [_vp, _u32, _u32, _u32]),
     "prism_cuda_kv_append": (C.c_int, [_vp, _u32, _vp, _vp, _u64]),
     "prism_cuda_attention_kv": (C.c_int, [_vp, _u32, _vp, _u32, _u32, _u32, _u32, _vp]),
+    "prism_cuda_attention_step_kv": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _u64, _u32, _u32, _u32, _u32, C.c_float, _vp]),
     "prism_cuda_load_cimage_cached": (C.c_int, [_vp, _cp, _cp, _pu32, C.POINTER(C.c_int)]),
     "prism_cuda_cimage_plan": (C.c_int, [_vp, C.POINTER(CImagePlan)]),
 }

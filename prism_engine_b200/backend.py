@@ -247,19 +247,20 @@ class CudaBackend:
         self._ck(self.L.prism_cuda_argmax(self.ctx, _ptr(lg), lg.size, C.byref(idx)))
         return idx.value
 
-    def bench_cycle(self, kind: int, handles, reps: int) -> float:
-        """ms for `reps` replays of a graph cycling through the given weight sets (see prism_cuda_bench_cycle)."""
+    def bench_cycle(self, kind: int, handles, reps: int, x_dev: int) -> float:
+        """ms for `reps` replays of a graph cycling through the given weight sets with the device activations
+        ``x_dev`` (see prism_cuda_bench_cycle)."""
         hs = np.ascontiguousarray(handles, dtype=np.int32).reshape(-1)
         per = kind + 1
         ms = C.c_double()
         self._ck(self.L.prism_cuda_bench_cycle(self.ctx, kind, hs.ctypes.data_as(C.POINTER(C.c_int32)),
-                                               hs.size // per, reps, C.byref(ms)))
+                                               hs.size // per, reps, x_dev, C.byref(ms)))
         return ms.value
 
-    def bench_gemm(self, handle: int, m_tok: int, reps: int) -> float:
-        """ms for `reps` prefill GEMMs of m_tok rows against one tensor (see prism_cuda_bench_gemm)."""
+    def bench_gemm(self, handle: int, X_dev: int, m_tok: int, reps: int) -> float:
+        """ms for `reps` prefill GEMMs of the device activations ``X_dev`` [m_tok][dim_n] against one tensor."""
         ms = C.c_double()
-        self._ck(self.L.prism_cuda_bench_gemm(self.ctx, handle, m_tok, reps, C.byref(ms)))
+        self._ck(self.L.prism_cuda_bench_gemm(self.ctx, handle, X_dev, m_tok, reps, C.byref(ms)))
         return ms.value
 
     def load_cimage(self, path: str, cache: Optional[str] = None):
@@ -332,6 +333,15 @@ class CudaBackend:
     def tp_peer_ready(self) -> bool:
         """True when the row-parallel partial sums are reduced through peer memory (else NCCL)."""
         return bool(self.L.prism_cuda_tp_peer_ready(self.ctx))
+
+    def attention_step_kv(self, layer: int, q, k, v, token_idx: int, num_heads: int, kv_heads: int, head_dim: int,
+                          rope_k: bool = True, rope_base: float = 10000.0) -> np.ndarray:
+        """Rope(q), Rope(k), cache append and attention of one decode step in one kernel, on the backend-held cache."""
+        q, k, v = _u16(q), _u16(k), _u16(v)
+        out = np.zeros(num_heads * head_dim, np.uint16)
+        self._ck(self.L.prism_cuda_attention_step_kv(self.ctx, layer, _ptr(q), _ptr(k), _ptr(v), token_idx, num_heads,
+                                                     kv_heads, head_dim, int(rope_k), rope_base, _ptr(out)))
+        return out
 
     def tp_peer_reason(self) -> str:
         r = self.L.prism_cuda_tp_peer_reason(self.ctx)
@@ -466,6 +476,12 @@ class PrismEngine:
 
     def kernels_per_step(self) -> int:
         return int(self.L.prism_cuda_engine_kernels_per_step(self.h))
+
+    def profile_part(self, part: int, reps: int = 1):
+        """(ms, launches) of `reps` passes over one kind of launch of a step: 1 = attention, 2 = TP reductions."""
+        ms, ln = C.c_double(), C.c_uint32()
+        self._ck(self.L.prism_cuda_engine_profile_part(self.h, part, reps, C.byref(ms), C.byref(ln)))
+        return ms.value, ln.value
 
     def profile_gemv(self, reps: int = 1):
         """(ms, algorithmic bytes, launches) of `reps` passes over the model's GEMV launches only."""

@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <cstring>
 
+#include "../../include/prism_cuda_bench.h"
 #include "common.cuh"
 #include "pair_table.cuh"
 #include "scratch.hpp"
@@ -524,23 +525,23 @@ int prism_cuda_gemm(prism_cuda_ctx *ctx, int32_t handle, const uint16_t *X, uint
 // graph replayed `reps` times between two events.  kind 0: gemv (1 handle per set); 1: fused
 // gate/up (2 handles: gate, up); 2: whole MLP (3 handles: gate, up, down).
 int prism_cuda_bench_cycle(prism_cuda_ctx *ctx, int kind, const int32_t *handles, uint32_t n_sets, uint32_t reps,
-                           double *ms_out) {
-    if (!ctx || !handles || !ms_out) return fail(ctx, PRISM_E_NULL, "null argument");
+                           const void *x_dev, double *ms_out) {
+    if (!ctx || !handles || !ms_out || !x_dev) return fail(ctx, PRISM_E_NULL, "null argument");
+    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(ctx, PRISM_E_ARG, "activations must be 16-byte aligned");
     if (kind < 0 || kind > 2 || n_sets == 0 || reps == 0) return fail(ctx, PRISM_E_ARG, "bad bench arguments");
     const int per = kind + 1;
     for (uint32_t i = 0; i < n_sets * per; i++)
         if (!get_tensor(ctx, handles[i])) return PRISM_E_NOTFOUND;
     PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     const LutTensor &t0 = ctx->tensors[handles[0]];
-    const size_t in_b = (size_t)round_up_u32(t0.k, 64) * 2, mid_b = (size_t)t0.m_pad * 2;
-    PRISM_TRY(ensure_stage(ctx, in_b, mid_b + 4096));
-    PRISM_CUDA_TRY(ctx, cudaMemsetAsync(ctx->stage_in, 0x2C, in_b, ctx->stream));  // x = fp16 0x2C2C ~ 0.065
+    const size_t mid_b = (size_t)t0.m_pad * 2;
+    PRISM_TRY(ensure_stage(ctx, 0, mid_b + 4096));
     auto pass = [&]() -> int {
         for (uint32_t s = 0; s < n_sets; s++) {
             const int32_t *h = handles + (size_t)s * per;
-            if (kind == 0) PRISM_TRY(prism_cuda_gemv_dev(ctx, h[0], ctx->stage_in, ctx->stage_out));
-            else if (kind == 1) PRISM_TRY(prism_cuda_fused_gate_up_dev(ctx, h[0], h[1], ctx->stage_in, ctx->stage_out));
-            else PRISM_TRY(prism_cuda_mlp_dev(ctx, h[0], h[1], h[2], ctx->stage_in, ctx->stage_out));
+            if (kind == 0) PRISM_TRY(prism_cuda_gemv_dev(ctx, h[0], x_dev, ctx->stage_out));
+            else if (kind == 1) PRISM_TRY(prism_cuda_fused_gate_up_dev(ctx, h[0], h[1], x_dev, ctx->stage_out));
+            else PRISM_TRY(prism_cuda_mlp_dev(ctx, h[0], h[1], h[2], x_dev, ctx->stage_out));
         }
         return PRISM_OK;
     };
@@ -577,24 +578,25 @@ int prism_cuda_bench_cycle(prism_cuda_ctx *ctx, int kind, const int32_t *handles
     return PRISM_OK;
 }
 
-// Measurement: `reps` prefill GEMMs of m_tok activation rows (fp16 pattern data generated on the
-// device) against one tensor, between two events on the context stream.
-int prism_cuda_bench_gemm(prism_cuda_ctx *ctx, int32_t handle, uint32_t m_tok, uint32_t reps, double *ms_out) {
+// Measurement: `reps` prefill GEMMs of the caller's m_tok activation rows against one tensor, between
+// two events on the context stream.
+int prism_cuda_bench_gemm(prism_cuda_ctx *ctx, int32_t handle, const void *X_dev, uint32_t m_tok, uint32_t reps,
+                          double *ms_out) {
     LutTensor *t = get_tensor(ctx, handle);
     if (!t) return ctx ? PRISM_E_NOTFOUND : PRISM_E_NULL;
-    if (!ms_out || m_tok == 0 || reps == 0) return fail(ctx, PRISM_E_ARG, "bad bench arguments");
+    if (!ms_out || !X_dev || m_tok == 0 || reps == 0) return fail(ctx, PRISM_E_ARG, "bad bench arguments");
+    if (reinterpret_cast<uintptr_t>(X_dev) & 15) return fail(ctx, PRISM_E_ARG, "activations must be 16-byte aligned");
     PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    const size_t in_b = (size_t)m_tok * t->k * 2, out_b = (size_t)m_tok * t->m * 2;
-    PRISM_TRY(ensure_stage(ctx, in_b, out_b));
-    PRISM_CUDA_TRY(ctx, cudaMemsetAsync(ctx->stage_in, 0x2C, in_b, ctx->stream));  // fp16 0x2C2C ~ 0.065
-    PRISM_TRY(launch_gemm(ctx, *t, (const uint16_t *)ctx->stage_in, m_tok, (uint16_t *)ctx->stage_out));  // warm-up
+    const size_t out_b = (size_t)m_tok * t->m * 2;
+    PRISM_TRY(ensure_stage(ctx, 0, out_b));
+    PRISM_TRY(launch_gemm(ctx, *t, (const uint16_t *)X_dev, m_tok, (uint16_t *)ctx->stage_out));  // warm-up
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
     cudaEventRecord(e0, ctx->stream);
     int rc = PRISM_OK;
     for (uint32_t r = 0; r < reps && rc == PRISM_OK; r++)
-        rc = launch_gemm(ctx, *t, (const uint16_t *)ctx->stage_in, m_tok, (uint16_t *)ctx->stage_out);
+        rc = launch_gemm(ctx, *t, (const uint16_t *)X_dev, m_tok, (uint16_t *)ctx->stage_out);
     cudaEventRecord(e1, ctx->stream);
     cudaError_t ce = cudaStreamSynchronize(ctx->stream);
     float ms = 0.f;
@@ -740,6 +742,35 @@ int prism_cuda_attention_kv(prism_cuda_ctx *ctx, uint32_t layer, const uint16_t 
     a.seq_stride = 0; a.int8 = 0; a.max_seq = seq_len;
     PRISM_TRY(launch_attention(ctx, a));
     return host_call_end(ctx, out, qb);
+}
+
+int prism_cuda_attention_step_kv(prism_cuda_ctx *ctx, uint32_t layer, const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                                 uint64_t token_idx, uint32_t num_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t rope_k,
+                                 float rope_base, uint16_t *out) {
+    if (!ctx || !q || !k || !v || !out) return fail(ctx, PRISM_E_NULL, "null argument");
+    if (!ctx->kv_k) return fail(ctx, PRISM_E_STATE, "attention_step_kv: no cache (prism_cuda_kv_init first)");
+    if (!num_heads || !kv_heads || !head_dim || num_heads % kv_heads) return fail(ctx, PRISM_E_ARG, "attention: bad head configuration");
+    if (layer >= ctx->kv_layers || kv_heads * head_dim != ctx->kv_dim || token_idx >= ctx->kv_max_seq)
+        return fail(ctx, PRISM_E_ARG, "attention_step_kv: layer, kv width or token index does not match the cache");
+    const uint32_t qd = num_heads * head_dim, kvd = ctx->kv_dim, stride = round_up_u32(qd + 2 * kvd, 8);
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    PRISM_TRY(ensure_stage(ctx, (size_t)stride * 2, (size_t)qd * 2));
+    uint16_t *row = reinterpret_cast<uint16_t *>(ctx->stage_in);
+    int32_t *pos_dev = reinterpret_cast<int32_t *>(ctx->dev_err + 4);
+    const int32_t pos = (int32_t)token_idx;
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(row, q, (size_t)qd * 2, cudaMemcpyHostToDevice, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(row + qd, k, (size_t)kvd * 2, cudaMemcpyHostToDevice, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(row + qd + kvd, v, (size_t)kvd * 2, cudaMemcpyHostToDevice, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(pos_dev, &pos, 4, cudaMemcpyHostToDevice, ctx->stream));
+    AttnArgs a{};
+    const size_t off = (size_t)layer * ctx->kv_max_seq * kvd;
+    a.q = row; a.q_stride = stride; a.k = ctx->kv_k + off; a.v = ctx->kv_v + off; a.out = (uint16_t *)ctx->stage_out;
+    a.pos_dev = pos_dev; a.pos_host = pos; a.slot_mul = 1; a.slot_add = 0;
+    a.nh = num_heads; a.nkv = kv_heads; a.hd = head_dim; a.batch = 1;
+    a.seq_stride = 0; a.int8 = 0; a.max_seq = ctx->kv_max_seq;
+    if (!attn_fused_eligible(a)) return fail(ctx, PRISM_E_ARG, "attention_step_kv: head_dim must be 32, 64, 128 or 256");
+    PRISM_TRY(launch_attn_fused(ctx, a, row + qd, row + qd + kvd, rope_k, rope_base));
+    return host_call_end(ctx, out, (size_t)qd * 2);
 }
 
 int prism_cuda_argmax(prism_cuda_ctx *ctx, const uint16_t *logits, uint32_t n, uint32_t *index) {

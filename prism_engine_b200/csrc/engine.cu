@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <cstring>
 
+#include "../../include/prism_cuda_bench.h"
 #include "common.cuh"
 
 namespace prism {
@@ -183,12 +184,37 @@ static int linear(prism_cuda_engine *e, GemvMode mode, const LutTensor &t, const
     return launch_silu_mul(ctx, y, g, u, B * t.m);
 }
 
+// Rope(q), Rope(k), KV append and Attention of layer l (cache slot li): one fused kernel when the
+// configuration allows, else the four separate ones.
+static int enqueue_attention(prism_cuda_engine *e, uint32_t l, uint32_t li) {
+    prism_cuda_ctx *ctx = e->ctx;
+    const prism_model_config &c = e->cfg;
+    const uint32_t B = e->batch, qs = e->qkv_stride;
+    const float base = c.rope_use_theta ? c.rope_theta : 10000.0f;
+    const int32_t *pos_dev = e->scalars;
+    const uint32_t slot_mul = e->guard_skip ? c.num_layers : 1, slot_add = e->guard_skip ? l : 0;
+    KvAppendArgs ka{};
+    ka.k = e->k; ka.v = e->v; ka.src_stride = qs;
+    ka.kc = (char *)e->kc + (size_t)li * e->kv_layer_bytes;
+    ka.vc = (char *)e->vc + (size_t)li * e->kv_layer_bytes;
+    ka.pos_dev = pos_dev; ka.slot_mul = slot_mul; ka.slot_add = slot_add;
+    ka.kvd = e->kvd_l; ka.batch = B; ka.seq_stride = e->kv_seq_stride; ka.int8 = c.kv_int8; ka.max_seq = e->kv_slots;
+    AttnArgs aa{};
+    aa.q = e->q; aa.q_stride = qs; aa.k = ka.kc; aa.v = ka.vc; aa.out = e->att;
+    aa.pos_dev = pos_dev; aa.slot_mul = slot_mul; aa.slot_add = slot_add;
+    aa.nh = e->nh_l; aa.nkv = e->nkv_l; aa.hd = e->hd; aa.batch = B;
+    aa.seq_stride = e->kv_seq_stride; aa.int8 = c.kv_int8; aa.max_seq = e->kv_slots;
+    if (ctx->fuse != 0 && attn_fused_eligible(aa)) return launch_attn_fused(ctx, aa, e->k, e->v, c.rope_k, base);
+    if (c.rope_k) PRISM_TRY(launch_rope(ctx, e->k, e->kvd_l, pos_dev, 0, e->hd, base, B, qs));
+    PRISM_TRY(launch_kv_append(ctx, ka));
+    PRISM_TRY(launch_rope(ctx, e->q, e->qd_l, pos_dev, 0, e->hd, base, B, qs));
+    return launch_attention(ctx, aa);
+}
+
 static int enqueue_step(prism_cuda_engine *e) {
     prism_cuda_ctx *ctx = e->ctx;
     const prism_model_config &c = e->cfg;
     const uint32_t B = e->batch, H = e->H;
-    const float base = c.rope_use_theta ? c.rope_theta : 10000.0f;
-    const int32_t *pos_dev = e->scalars;
     const bool tp = e->T > 1;
     const bool fused = ctx->fuse != 0;
     const LutTensor &emb = ctx->tensors[e->embed];
@@ -212,27 +238,7 @@ static int enqueue_step(prism_cuda_engine *e) {
             PRISM_TRY(linear(e, GEMV_PLAIN, tk, nullptr, e->xn, H, e->k, qs, nullptr, B));
             PRISM_TRY(linear(e, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, qs, nullptr, B));
         }
-        const uint32_t slot_mul = e->guard_skip ? c.num_layers : 1, slot_add = e->guard_skip ? l : 0;
-        KvAppendArgs ka{};
-        ka.k = e->k; ka.v = e->v; ka.src_stride = qs;
-        ka.kc = (char *)e->kc + (size_t)li * e->kv_layer_bytes;
-        ka.vc = (char *)e->vc + (size_t)li * e->kv_layer_bytes;
-        ka.pos_dev = pos_dev; ka.slot_mul = slot_mul; ka.slot_add = slot_add;
-        ka.kvd = e->kvd_l; ka.batch = B; ka.seq_stride = e->kv_seq_stride; ka.int8 = c.kv_int8; ka.max_seq = e->kv_slots;
-        AttnArgs aa{};
-        aa.q = e->q; aa.q_stride = qs; aa.k = ka.kc; aa.v = ka.vc; aa.out = e->att;
-        aa.pos_dev = pos_dev; aa.slot_mul = slot_mul; aa.slot_add = slot_add;
-        aa.nh = e->nh_l; aa.nkv = e->nkv_l; aa.hd = e->hd; aa.batch = B;
-        aa.seq_stride = e->kv_seq_stride; aa.int8 = c.kv_int8; aa.max_seq = e->kv_slots;
-        if (fused && attn_fused_eligible(aa)) {
-            // Rope(q), Rope(k), cache append and Attention as one kernel
-            PRISM_TRY(launch_attn_fused(ctx, aa, e->k, e->v, c.rope_k, base));
-        } else {
-            if (c.rope_k) PRISM_TRY(launch_rope(ctx, e->k, e->kvd_l, pos_dev, 0, e->hd, base, B, qs));
-            PRISM_TRY(launch_kv_append(ctx, ka));
-            PRISM_TRY(launch_rope(ctx, e->q, e->qd_l, pos_dev, 0, e->hd, base, B, qs));
-            PRISM_TRY(launch_attention(ctx, aa));
-        }
+        PRISM_TRY(enqueue_attention(e, l, li));
         if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, to, nullptr, e->att, e->qd_l, (uint16_t *)e->part, H, nullptr, B));
             PRISM_TRY(tp_reduce_add_resid(e, B * H));
@@ -709,7 +715,9 @@ int prism_cuda_engine_generate(prism_cuda_engine *e, const uint32_t *prompts, ui
         int32_t one = 1;  // record = 1; pos and step are already right (step stayed 0 while not recording)
         PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->scalars + 2, &one, 4, cudaMemcpyHostToDevice, ctx->stream));
     }
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev2, ctx->stream));
     for (uint32_t i = 0; i < max_new; i++) PRISM_TRY(run_step(e));
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev3, ctx->stream));
     e->pos += max_new;
     PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev1, ctx->stream));
     if (max_new)
@@ -727,6 +735,8 @@ int prism_cuda_engine_generate(prism_cuda_engine *e, const uint32_t *prompts, ui
     float ms = 0.f;
     cudaEventElapsedTime(&ms, e->ev0, e->ev1);
     e->last_ms = ms;
+    cudaEventElapsedTime(&ms, e->ev2, e->ev3);
+    e->last_device_ms = ms;  // the decode steps alone (prefill excluded)
     return device_error_result(ctx, errw);
 }
 
@@ -806,6 +816,41 @@ extern "C" int prism_cuda_engine_profile_gemv(prism_cuda_engine *e, uint32_t rep
     if (bytes_out) *bytes_out = bytes;
     if (launches_out) *launches_out = launches;
     return PRISM_OK;
+}
+extern "C" int prism_cuda_engine_profile_part(prism_cuda_engine *e, uint32_t part, uint32_t reps, double *ms_out,
+                                              uint32_t *launches_out) {
+    if (!e || !ms_out) return fail(e ? e->ctx : nullptr, PRISM_E_NULL, "null argument");
+    prism_cuda_ctx *ctx = e->ctx;
+    if (part != 1 && part != 2) return fail(ctx, PRISM_E_ARG, "profile_part: 1 = attention, 2 = tensor-parallel reductions");
+    PRISM_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    PRISM_TRY(check_bound(e));
+    const uint32_t L = e->cfg.num_layers, B = e->batch ? e->batch : 1;
+    // the attention kernel appends at the current position: keep that inside the cache
+    PRISM_TRY(capacity_ok(e, 1));
+    PRISM_TRY(set_scalars(e, (int32_t)e->pos, 0, 0));
+    const uint64_t l0 = ctx->launches;
+    auto one_pass = [&]() -> int {
+        for (uint32_t l = 0; l < L; l++) {
+            if (part == 1) {
+                PRISM_TRY(enqueue_attention(e, l, e->guard_skip ? 0 : l));
+            } else if (e->T > 1) {
+                PRISM_TRY(tp_reduce_add_resid(e, B * e->H));
+                PRISM_TRY(tp_reduce_add_resid(e, B * e->H));
+            }
+        }
+        return PRISM_OK;
+    };
+    PRISM_TRY(one_pass());
+    const uint64_t per_pass = ctx->launches - l0;
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev2, ctx->stream));
+    for (uint32_t r = 0; r < reps; r++) PRISM_TRY(one_pass());
+    PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev3, ctx->stream));
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e->ev2, e->ev3);
+    *ms_out = ms;
+    if (launches_out) *launches_out = (uint32_t)(per_pass * reps);
+    return check_device_error(ctx);
 }
 prism_cuda_ctx *prism_cuda_engine_ctx(prism_cuda_engine *e) { return e ? e->ctx : nullptr; }
 uint32_t prism_cuda_engine_position(prism_cuda_engine *e) { return e ? e->pos : 0; }

@@ -111,3 +111,19 @@ class ModelGraph:
     def embedding(self):
         n = self.nodes[0]
         return n[1], n[2], n[3]
+
+
+def generate_plan(graph: ModelGraph, has_gpu: bool = True) -> str:
+    """``generate_plan`` (src/lut/graph.rs:592-654) serialised as serde_json writes ``ExecutionPlan``
+    (:552-589): one backend assignment per node, the KV format and the attention strategy the compiler
+    assumed.  ``has_gpu`` plays the role of ``has_metal``; the variant names are the reference's."""
+    gemm = "MetalGemm" if has_gpu else "CpuGemm"
+    per_node = {"TokenEmbedding": "Skip", "Norm": "CpuNorm", "PalettizedMatmul": gemm, "RotaryEmbedding": "CpuRope",
+                "ScaledDotProductAttention": "MetalAttention" if has_gpu else "CpuSoftmaxAttn",
+                "Activation": "CpuActivation", "LanguageModelHead": gemm}
+    plan = {"version": 1, "architecture": "prism-engine", "num_layers": graph.num_layers,
+            "node_backends": [per_node[n[0]] for n in graph.nodes],
+            "kv_cache": "Fp16" if has_gpu else "Int8",
+            "attention_strategy": "MetalKernel" if has_gpu else "CpuSoftmax",
+            "lm_head_backend": "metal" if has_gpu else "cpu"}
+    return json.dumps(plan, separators=(",", ":"))

@@ -1,4 +1,4 @@
-"""The C-ABI library loads and exports every symbol include/prism_cuda.h declares (CPU: no compute calls)."""
+"""The C-ABI library loads and exports every symbol the headers under include/ declare (CPU: no compute calls)."""
 import ctypes
 import os
 import re
@@ -9,9 +9,15 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _declared():
-    src = open(os.path.join(ROOT, "include", "prism_cuda.h")).read()
-    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
-    return sorted(set(re.findall(r"\b(prism_cuda_[a-z0-9_]+)\s*\(", src)))
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for h in sorted(os.listdir(inc)):
+        if not h.endswith(".h"):
+            continue
+        src = open(os.path.join(inc, h)).read()
+        src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+        names |= set(re.findall(r"\b(prism_cuda_[a-z0-9_]+)\s*\(", src))
+    return sorted(names)
 
 
 @pytest.fixture(scope="module")

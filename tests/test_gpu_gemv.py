@@ -127,3 +127,28 @@ def test_gemm_full_size_rows_match_gemv(backend):
         y = backend.gemv(h, X[t])
         assert rel_l2(Y[t], y) <= TOL and np.mean(Y[t] == y) > 0.9, t
     backend.free(h)
+
+
+CONFIG4 = [("q", 3584, 3584), ("kv", 512, 3584), ("gate_up", 18944, 3584), ("down", 3584, 18944)]
+SAMPLED_TOKENS = [0, 1, 127, 128, 255, 256, 1000, 2047]   # first, last, and both sides of the 128- and 256-token tile edges
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("name,m,k", CONFIG4)
+def test_gemm_prefill_shapes_match_oracle(backend, oracle, name, m, k):
+    """The Qwen2.5-7B prefill shapes at M = 2048 tokens of N(0,1) activations through the tensor-core GEMM:
+    sampled token rows against prefill_cpu (one lut_gemv_cpu per row, engine_impl.rs:1046-1053)."""
+    m_tok = 2048
+    pay = synth.make_payload(m, k, 4, seed=40 + m % 7)
+    h = backend.upload(f"c4.{name}", pay, m, k)
+    X = synth.make_activation((m_tok, k), seed=m + k)
+    l0 = backend.launch_count()
+    Y = backend.gemm(h, X)
+    assert backend.launch_count() > l0
+    want = oracle.lut_gemm(X[SAMPLED_TOKENS], pay, m, k, threads=oracle.max_threads())
+    got = Y[SAMPLED_TOKENS]
+    assert rel_l2(got.reshape(-1), want.reshape(-1)) <= TOL
+    assert np.mean(got == want) > 0.9
+    for i, t in enumerate(SAMPLED_TOKENS):
+        assert rel_l2(got[i], want[i]) <= TOL, (name, t)
+    backend.free(h)

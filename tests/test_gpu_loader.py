@@ -75,3 +75,82 @@ def test_rejects_bad_arguments(backend):
     backend.free(h)
     with pytest.raises(PrismCudaError):
         backend.dims(h)                          # freed handle
+
+
+def _write_tiny_cimage(path, plan):
+    import prism_engine_b200 as p
+
+    graph = p.ModelGraph.build(p.UnifiedConfig(vocab_size=256, hidden_size=64, intermediate_size=96, num_layers=2,
+                                               num_heads=4, num_kv_heads=2, head_dim=16, tie_word_embeddings=True))
+    w = p.CImageWriter(path)
+    payloads = {}
+    for i, (key, dm, dn) in enumerate(graph.palettized_tensors() + [graph.embedding()]):
+        payloads[key] = synth.make_payload(dm, dn, seed=300 + i)
+        w.append_palettized(key, payloads[key], dm, dn)
+    w.append_blob("tokenizer.blob", np.arange(100, dtype=np.uint8))
+    if plan == "reference":
+        w.set_execution_plan(p.generate_plan(graph, has_gpu=True))
+    elif plan is not None:
+        w.set_execution_plan(plan)
+    w.finalize()
+    return graph, payloads
+
+
+def test_cimage_execution_plan_is_parsed_and_bad_plans_tolerated(tmp_path):
+    import prism_engine_b200 as p
+
+    for plan, want_version in (("reference", 1), (None, 0), ('{"schema":"compute-core","ops":[1,2]}', 0), ("{not json", 0)):
+        be = p.CudaBackend(device=0)
+        path = str(tmp_path / f"m{want_version}{abs(hash(plan)) % 97}.cimage")
+        graph, payloads = _write_tiny_cimage(path, plan)
+        assert be.load_cimage(path) == len(payloads)            # the load itself never depends on the plan
+        pl = be.cimage_plan()
+        assert pl["version"] == want_version
+        if want_version:
+            assert pl["num_layers"] == 2 and pl["n_nodes"] == len(graph.nodes) and pl["n_gemm_nodes"] == 14
+            assert pl["kv_cache"] == "Fp16" and pl["attention_strategy"] == "MetalKernel" and pl["lm_head_backend"] == "metal"
+        be.close()
+
+
+def test_cimage_relaid_cache_round_trip(tmp_path):
+    """First load writes the device layout beside the container; the second load takes it from there (no
+    re-lay kernels) and holds byte-identical tensors; a changed container invalidates the cache."""
+    import os
+
+    import prism_engine_b200 as p
+
+    path = str(tmp_path / "m.cimage")
+    graph, payloads = _write_tiny_cimage(path, "reference")
+    be = p.CudaBackend(device=0)
+    n, hit = be.load_cimage(path, cache="")
+    assert n == len(payloads) and not hit and os.path.exists(path + ".b200relay")
+    be.close()
+    be = p.CudaBackend(device=0)
+    l0 = be.launch_count()
+    n, hit = be.load_cimage(path, cache="")
+    assert n == len(payloads) and hit and be.launch_count() == l0       # copies only
+    for key, pay in payloads.items():
+        assert np.array_equal(be.download_payload(be.find(key)), pay), key
+    x = synth.make_activation(64, seed=1)
+    key = "model.layers.1.mlp.gate_proj.weight"
+    y_cached = be.gemv(key, x)
+    be.close()
+    be = p.CudaBackend(device=0)
+    be.load_cimage(path)
+    assert np.array_equal(be.gemv(key, x), y_cached)
+    be.close()
+    # another model under the same name: the key (header + size) differs, the stale cache is replaced
+    _write_tiny_cimage(path, None)                                     # same tensors, different header bytes
+    be = p.CudaBackend(device=0)
+    n, hit = be.load_cimage(path, cache="")
+    assert not hit
+    be.close()
+    # option-driven use by the engine loader
+    be = p.CudaBackend(device=0)
+    be.set_option("cimage_cache", 1)
+    mc = p.model_config(num_layers=2, hidden_size=64, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=96,
+                        vocab_size=256, tie_word_embeddings=True, max_seq=32, profile="baseline")
+    eng = p.PrismEngine.load(be, path, mc)
+    toks = eng.generate(np.array([1, 2, 3], np.uint32), 5)
+    assert toks.shape == (5,)
+    eng.close(); be.close()
