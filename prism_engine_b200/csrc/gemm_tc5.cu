@@ -12,10 +12,14 @@
 //    no-swizzle core-matrix layout the B operand descriptor addresses;
 //  * one thread issues two tcgen05.mma (M = 128, N = 256, K = 16) per 32-k chunk; the fp32
 //    accumulators (256 TMEM columns) are read back with tcgen05.ld, rounded to fp16 and stored.
+// 2-bit tensors (4-entry palettes; BITS = 2) run the same pipeline: a 16-byte index chunk then holds
+// 64 weights of a row and expands into two 32-k chunks of the A operand through a 16-entry pair table
+// indexed by nibbles (sk_expand2, pair_table.cuh).
 // Every mbarrier wait is bounded; a wait that gives up raises the context's device error word.
 #include <algorithm>
 
 #include "common.cuh"
+#include "pair_table.cuh"
 #include "tc5_ptx.cuh"
 
 namespace prism {
@@ -55,7 +59,8 @@ constexpr size_t GM_SMEM_BYTES = GM_STATE_OFF + 64;
 struct GemmArgs {
     const uint8_t *idx;
     const uint16_t *pal;
-    uint32_t n_chunks, n_hb, m;       // chunks per row (K/32), half-blocks, valid weight rows
+    uint32_t n_chunks, n_hb, m;       // 32-k chunks per row (K/32), half-blocks, valid weight rows
+    uint32_t n_ichunks;               // 16-byte index chunks per row (K/32 at 4 bit, K/64 at 2 bit)
     uint32_t n_rt, n_tt;              // row tiles (128 rows), token tiles (256 tokens)
     uint32_t m_tok, m_tok_pad;
     const uint8_t *xc;                // [token tile][K/8][NT][16 B]
@@ -90,12 +95,34 @@ __device__ __forceinline__ uint32_t gm_lds(uint32_t off, int slot) {
     return v;
 }
 
-template <int NT>
+// The 16 table lookups of one 32-k chunk of a row: bytes of the index words -> half2 entries.
+__device__ __forceinline__ void gm_lookup16(uint32_t (&A)[16], const uint4 &wv, uint32_t laneq, uint32_t slot) {
+    const uint32_t aw[4] = {wv.x, wv.y, wv.z, wv.w};
+    if (slot == 0) {
+#pragma unroll
+        for (int hh = 0; hh < 4; hh++) {
+            A[4 * hh + 0] = gm_lds(__byte_perm(aw[hh], laneq, 0x7604), 0);
+            A[4 * hh + 1] = gm_lds(__byte_perm(aw[hh], laneq, 0x7614), 0);
+            A[4 * hh + 2] = gm_lds(__byte_perm(aw[hh], laneq, 0x7624), 0);
+            A[4 * hh + 3] = gm_lds(__byte_perm(aw[hh], laneq, 0x7634), 0);
+        }
+    } else {
+#pragma unroll
+        for (int hh = 0; hh < 4; hh++) {
+            A[4 * hh + 0] = gm_lds(__byte_perm(aw[hh], laneq, 0x7604), 1);
+            A[4 * hh + 1] = gm_lds(__byte_perm(aw[hh], laneq, 0x7614), 1);
+            A[4 * hh + 2] = gm_lds(__byte_perm(aw[hh], laneq, 0x7624), 1);
+            A[4 * hh + 3] = gm_lds(__byte_perm(aw[hh], laneq, 0x7634), 1);
+        }
+    }
+}
+
+template <int NT, int BITS>
 __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmArgs a) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     if (smem_base != (uint32_t)GM_SBASE) {  // layout assumption broken: refuse to compute
-        if (threadIdx.x == 0) atomicExch(a.err, 4u);
+        if (threadIdx.x == 0) atomicExch(a.err, 1u);
         return;
     }
     // Tables, barriers and TMEM are set up from weights alone while the previous kernel drains; the
@@ -107,6 +134,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
     const uint32_t b_afull = bar, b_aempty = bar + 8 * GM_SA, b_xfull = bar + 16 * GM_SA,
                    b_xempty = b_xfull + 8 * GM_SX_MAX, b_dfull = b_xempty + 8 * GM_SX_MAX, b_dempty = b_dfull + 8;
     constexpr int SX = GmX<NT>::SX, XSTAGE = GmX<NT>::STAGE_BYTES, CPS = GmX<NT>::CPS, SA = GmX<NT>::SA, XC = GmX<NT>::XC;
+    constexpr int ICPS = BITS == 4 ? CPS : CPS / 2;  // 16-byte index chunks per weight stage
+    constexpr int NSI = GM_PF / ICPS;                // stages whose index chunks a warp keeps in flight
     volatile uint32_t *err_flag = reinterpret_cast<volatile uint32_t *>(smem + GM_STATE_OFF);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + GM_STATE_OFF + 8);
     const uint32_t nch = a.n_chunks;
@@ -138,30 +167,43 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
             const uint32_t hb = 4 * rt + q;
             const bool ok = hb < a.n_hb;
             const uint32_t h = ok ? hb : a.n_hb - 1;
-            const uint8_t *sp = a.idx + (size_t)h * nch * 512 + lane * 16;
+            const uint32_t nich = a.n_ichunks;
+            const uint8_t *sp = a.idx + (size_t)h * nich * 512 + lane * 16;
             uint4 r[GM_PF];
 #pragma unroll
-            for (int i = 0; i < GM_PF; i++) {  // r[i]: chunk (i % CPS) of this warp's stage number i / CPS
-                const uint32_t c = (j + 4 * (i / CPS)) * CPS + (i % CPS);
-                if (c < nch) r[i] = t5::ldg128_nc(sp + (size_t)c * 512);
+            for (int i = 0; i < GM_PF; i++) {  // r[i]: index chunk (i % ICPS) of this warp's stage number i / ICPS
+                const uint32_t c = (j + 4 * (i / ICPS)) * ICPS + (i % ICPS);
+                if (c < nich) r[i] = t5::ldg128_nc(sp + (size_t)c * 512);
             }
             if (rt != cur_rt) {  // same decision in all warps: they walk the same item list
                 cur_rt = rt;
                 asm volatile("bar.sync %0, 256;\n" ::"r"(1 + pair) : "memory");  // lookups of the previous tile are done
-                const uint16_t *prow = a.pal + ((size_t)h * 32 + lane) * 16;
-                const uint4 p0 = *reinterpret_cast<const uint4 *>(prow);
-                const uint4 p1 = *reinterpret_cast<const uint4 *>(prow + 8);
-                const uint32_t cbp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-                const uint32_t hp0 = reinterpret_cast<const uint32_t *>(prow)[2 * j];
-                const uint32_t hp1 = reinterpret_cast<const uint32_t *>(prow)[2 * j + 1];
-                uint8_t *tb = smem + pair * 65536 + j * 16384 + lane * 4 + slot * 128;
+                if (BITS == 4) {
+                    const uint16_t *prow = a.pal + ((size_t)h * 32 + lane) * 16;
+                    const uint4 p0 = *reinterpret_cast<const uint4 *>(prow);
+                    const uint4 p1 = *reinterpret_cast<const uint4 *>(prow + 8);
+                    const uint32_t cbp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                    const uint32_t hp0 = reinterpret_cast<const uint32_t *>(prow)[2 * j];
+                    const uint32_t hp1 = reinterpret_cast<const uint32_t *>(prow)[2 * j + 1];
+                    uint8_t *tb = smem + pair * 65536 + j * 16384 + lane * 4 + slot * 128;
 #pragma unroll
-                for (int lo = 0; lo < 16; lo++) {
+                    for (int lo = 0; lo < 16; lo++) {
 #pragma unroll
-                    for (int hs = 0; hs < 4; hs++) {
-                        const uint32_t sel = (((hs & 1) ? 0x76u : 0x54u) << 8) | ((lo & 1) ? 0x32u : 0x10u);
-                        *reinterpret_cast<uint32_t *>(tb + lo * 256 + hs * 4096) =
-                            __byte_perm(cbp[lo >> 1], (hs & 2) ? hp1 : hp0, sel);
+                        for (int hs = 0; hs < 4; hs++) {
+                            const uint32_t sel = (((hs & 1) ? 0x76u : 0x54u) << 8) | ((lo & 1) ? 0x32u : 0x10u);
+                            *reinterpret_cast<uint32_t *>(tb + lo * 256 + hs * 4096) =
+                                __byte_perm(cbp[lo >> 1], (hs & 2) ? hp1 : hp0, sel);
+                        }
+                    }
+                } else {
+                    // 16-entry nibble table: entry e = i0 | i1 << 2 -> half2{pal[i0], pal[i1]}; slot j writes e = 4j..4j+3
+                    const uint2 pp = *reinterpret_cast<const uint2 *>(a.pal + ((size_t)h * 32 + lane) * 4);
+                    const uint32_t v1 = ((j & 2) ? pp.y : pp.x) >> ((j & 1) * 16) & 0xFFFFu;  // pal[i1], i1 = j
+                    uint8_t *tb = smem + pair * 65536 + lane * 4 + slot * 128;
+#pragma unroll
+                    for (uint32_t i0 = 0; i0 < 4; i0++) {
+                        const uint32_t v0 = ((i0 & 2) ? pp.y : pp.x) >> ((i0 & 1) * 16) & 0xFFFFu;
+                        *reinterpret_cast<uint32_t *>(tb + (4 * j + i0) * 256) = v0 | (v1 << 16);
                     }
                 }
                 asm volatile("bar.sync %0, 256;\n" ::"r"(1 + pair) : "memory");
@@ -169,35 +211,25 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
             // ---- K loop: lookups -> TMEM stage -> signal the MMA thread ----
             // a stage is CPS consecutive chunks; warp slot j takes the stages j, j+4, ...
             const uint32_t nst = nch / CPS;
-            for (uint32_t s0 = j; s0 < nst; s0 += 4 * (GM_PF / CPS)) {
+            for (uint32_t s0 = j; s0 < nst; s0 += 4 * NSI) {
 #pragma unroll
-                for (int i = 0; i < GM_PF / CPS; i++) {
+                for (int i = 0; i < NSI; i++) {
                     const uint32_t su = s0 + 4 * i;
                     if (su < nst) {
                         uint32_t A[CPS][16];
 #pragma unroll
-                        for (int cc = 0; cc < CPS; cc++) {
-                            const uint32_t c = su * CPS + cc;
-                            const uint4 wv = r[i * CPS + cc];
+                        for (int cc = 0; cc < ICPS; cc++) {
+                            const uint32_t c = su * ICPS + cc;
+                            const uint4 wv = r[i * ICPS + cc];
                             const uint32_t nc = c + 4 * GM_PF;
-                            if (nc < nch) r[i * CPS + cc] = t5::ldg128_nc(sp + (size_t)nc * 512);
-                            const uint32_t aw[4] = {wv.x, wv.y, wv.z, wv.w};
-                            if (slot == 0) {
-#pragma unroll
-                                for (int hh = 0; hh < 4; hh++) {
-                                    A[cc][4 * hh + 0] = gm_lds(__byte_perm(aw[hh], laneq, 0x7604), 0);
-                                    A[cc][4 * hh + 1] = gm_lds(__byte_perm(aw[hh], laneq, 0x7614), 0);
-                                    A[cc][4 * hh + 2] = gm_lds(__byte_perm(aw[hh], laneq, 0x7624), 0);
-                                    A[cc][4 * hh + 3] = gm_lds(__byte_perm(aw[hh], laneq, 0x7634), 0);
-                                }
+                            if (nc < nich) r[i * ICPS + cc] = t5::ldg128_nc(sp + (size_t)nc * 512);
+                            if (BITS == 4) {
+                                gm_lookup16(A[cc], wv, laneq, slot);
                             } else {
-#pragma unroll
-                                for (int hh = 0; hh < 4; hh++) {
-                                    A[cc][4 * hh + 0] = gm_lds(__byte_perm(aw[hh], laneq, 0x7604), 1);
-                                    A[cc][4 * hh + 1] = gm_lds(__byte_perm(aw[hh], laneq, 0x7614), 1);
-                                    A[cc][4 * hh + 2] = gm_lds(__byte_perm(aw[hh], laneq, 0x7624), 1);
-                                    A[cc][4 * hh + 3] = gm_lds(__byte_perm(aw[hh], laneq, 0x7634), 1);
-                                }
+                                uint4 pa, pb;
+                                sk_expand2(pa, pb, wv);
+                                gm_lookup16(A[2 * cc], pa, laneq, slot);
+                                gm_lookup16(A[2 * cc + 1], pb, laneq, slot);
                             }
                         }
                         const uint32_t n = n_base + su, stage = n % SA, ph = (n / SA) & 1;
@@ -293,14 +325,15 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
 // ---- host side ---------------------------------------------------------------------------------
 
 bool gemm_tc5_eligible(prism_cuda_ctx *ctx, const LutTensor &t, uint32_t m_tok) {
-    return ctx->smem_base == GM_SBASE && t.bits == 4 && t.k % 128 == 0 && m_tok >= 8;  // whole stages of two or four chunks
+    // whole weight stages of 128 k (four 32-k chunks: four index chunks at 4 bit, two at 2 bit)
+    return ctx->smem_base == GM_SBASE && (t.bits == 4 || t.bits == 2) && t.k % 128 == 0 && m_tok >= 8;
 }
 
-template <int NT>
+template <int NT, int BITS>
 static int launch_gemm_nt(prism_cuda_ctx *ctx, GemmArgs &a, const LutTensor &t, const uint16_t *X) {
     static bool configured[PRISM_MAX_DEVICES] = {false};
     if (!configured[ctx->device]) {
-        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemm_tc5_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemm_tc5_kernel<NT, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)GM_SMEM_BYTES));
         configured[ctx->device] = true;
     }
@@ -321,7 +354,7 @@ static int launch_gemm_nt(prism_cuda_ctx *ctx, GemmArgs &a, const LutTensor &t, 
     uint32_t grid;
     if (a.n_rt <= G) grid = a.n_rt * std::max(1u, std::min(G / a.n_rt, a.n_tt));
     else grid = G;
-    launch_pdl(ctx, "lut_gemm_tc5_kernel", lut_gemm_tc5_kernel<NT>, dim3(grid), dim3(GM_THREADS), GM_SMEM_BYTES, a);
+    launch_pdl(ctx, "lut_gemm_tc5_kernel", lut_gemm_tc5_kernel<NT, BITS>, dim3(grid), dim3(GM_THREADS), GM_SMEM_BYTES, a);
     return after_launch(ctx, "lut_gemm_tc5_kernel");
 }
 
@@ -329,16 +362,22 @@ int launch_gemm_tc5(prism_cuda_ctx *ctx, const LutTensor &t, const uint16_t *X, 
     if (reinterpret_cast<uintptr_t>(X) & 15) return fail(ctx, PRISM_E_ARG, "gemm: X must be 16-byte aligned");
     GemmArgs a{};
     a.idx = t.idx; a.pal = t.pal;
-    a.n_chunks = t.n_chunks; a.n_hb = t.n_hb; a.m = t.m;
+    a.n_chunks = t.k / 32; a.n_ichunks = t.n_chunks; a.n_hb = t.n_hb; a.m = t.m;
     a.n_rt = (t.n_hb + 3) / 4;
     a.m_tok = m_tok;
     a.y = Y; a.err = ctx->dev_err;
     // token tile = N of the MMA: as small as the batch allows (the activation tile is the operand
     // that has to come through L2 for every 32-k chunk)
-    if (m_tok <= 32) return launch_gemm_nt<32>(ctx, a, t, X);
-    if (m_tok <= 64) return launch_gemm_nt<64>(ctx, a, t, X);
-    if (m_tok <= 128) return launch_gemm_nt<128>(ctx, a, t, X);
-    return launch_gemm_nt<256>(ctx, a, t, X);
+    if (t.bits == 2) {
+        if (m_tok <= 32) return launch_gemm_nt<32, 2>(ctx, a, t, X);
+        if (m_tok <= 64) return launch_gemm_nt<64, 2>(ctx, a, t, X);
+        if (m_tok <= 128) return launch_gemm_nt<128, 2>(ctx, a, t, X);
+        return launch_gemm_nt<256, 2>(ctx, a, t, X);
+    }
+    if (m_tok <= 32) return launch_gemm_nt<32, 4>(ctx, a, t, X);
+    if (m_tok <= 64) return launch_gemm_nt<64, 4>(ctx, a, t, X);
+    if (m_tok <= 128) return launch_gemm_nt<128, 4>(ctx, a, t, X);
+    return launch_gemm_nt<256, 4>(ctx, a, t, X);
 }
 
 }  // namespace prism

@@ -1,7 +1,11 @@
 // Palettized GEMV, persistent "stream-K" form of the pair-table tensor-core kernel.
 //
 // y = W x with W stored as 4-bit palette indices + a 16-entry fp16 palette per row
-// (lut_gemv_cpu, src/lut/cpu_fallback.rs:12-35; fused gate/up: engine_impl.rs FusedGateUp).
+// (lut_gemv_cpu, src/lut/cpu_fallback.rs:12-35; fused gate/up: engine_impl.rs FusedGateUp), or as
+// 2-bit indices + a 4-entry palette (BITS = 2; no such format in the reference).  At 2 bits a
+// 16-byte chunk holds 64 weights of a row; every NIBBLE (two weights) is looked up in a 16-entry pair
+// table, through the same lookup and mma.sync code as the 4-bit bytes: the two nibble planes of an
+// index word are separated and re-interleaved into two "pseudo-words" whose bytes are table indices.
 //
 // Work is counted in units of (block, chunk): a block is two half-blocks of 32 rows (64 output
 // rows, or 32 gate + 32 up rows), a chunk is 32 weights (16 index bytes) of every row of the block,
@@ -23,10 +27,10 @@ constexpr int SK_CTAS_PER_SM = 3;
 constexpr int SK_NACC = 2;                // independent accumulator sets (2 or 4)
 constexpr int SK_THREADS = SK_WARPS * 32;
 constexpr int SK_TBL_BYTES = 256 * 256;   // 256 entries x (2 half-blocks x 32 lanes x 4 B)
-constexpr int SK_PIECE_CHUNKS = SK_WARPS * 16;  // chunks of x staged at a time (8 warps: 4096 halves, 8 KB)
+constexpr int SK_PIECE_BYTES = SK_WARPS * 16 * 64;  // x staged at a time: 4096 halves, 8 KB (128 chunks at 4 bit, 64 at 2 bit)
 constexpr int SK_PF = 2;                 // index chunks in flight per warp (1, 2 or 4)
 constexpr int SK_KNOWN_SBASE = 1024;      // dynamic shared memory starts after the 1 KB the driver reserves
-constexpr size_t SK_SMEM_BYTES = SK_TBL_BYTES + SK_PIECE_CHUNKS * 64 + SK_WARPS * 64 * 4 + 32;
+constexpr size_t SK_SMEM_BYTES = SK_TBL_BYTES + SK_PIECE_BYTES + SK_WARPS * 64 * 4 + 32;
 
 
 // One 32-weight chunk of the two half-blocks: 8 tensor-core steps of 4 k each.  The MMA's 16 x 16
@@ -63,8 +67,30 @@ __device__ __forceinline__ void sk_chunk(float (&acc)[SK_NACC][4], uint4 &w1, ui
     sk_mma(acc[H + 1], A1[4], A1[5], A1[6], A1[7], xb[1].z, xb[1].w);
 }
 
-template <int MODE, int SBASE>
+// A 2-bit chunk (64 weights per row) as two pseudo 4-bit chunks of 32 weights each.
+struct SkNoNext {
+    template <int OFF> __device__ __forceinline__ uint4 load1() const { return make_uint4(0, 0, 0, 0); }
+    template <int OFF> __device__ __forceinline__ uint4 load2() const { return make_uint4(0, 0, 0, 0); }
+};
+template <int SBASE, int NEXT_IMM, typename SRC>
+__device__ __forceinline__ void sk_chunk2(float (&acc)[SK_NACC][4], uint4 &w1, uint4 &w2, uint4 (&xb)[2], uint32_t lane_off,
+                                          uint32_t x_off, uint32_t diag, uint32_t base, const SRC &next, bool more) {
+    uint4 a1, b1, a2, b2;
+    sk_expand2(a1, b1, w1);
+    sk_expand2(a2, b2, w2);
+    if (more) {  // the index words are dead once expanded: the chunk PF steps ahead goes into them
+        w1 = next.template load1<NEXT_IMM>();
+        w2 = next.template load2<NEXT_IMM>();
+    }
+    const SkNoNext none;
+    sk_chunk<SBASE, 0>(acc, a1, a2, xb, lane_off, x_off, diag, base, none, false);
+    sk_chunk<SBASE, 0>(acc, b1, b2, xb, lane_off, x_off + 64, diag, base, none, false);
+}
+
+template <int MODE, int SBASE, int BITS>
 __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel(const SkArgs a) {
+    constexpr uint32_t XB = BITS == 4 ? 64 : 128;               // bytes of x per chunk (32 or 64 halves)
+    constexpr uint32_t SK_PIECE_CHUNKS = SK_PIECE_BYTES / XB;   // chunks of x staged at a time
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     if (SBASE >= 0 && smem_base != (uint32_t)SBASE) {  // layout assumption broken: refuse to compute
@@ -73,7 +99,7 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
     }
     uint32_t *tbl = reinterpret_cast<uint32_t *>(smem);
     uint16_t *xs = reinterpret_cast<uint16_t *>(smem + SK_TBL_BYTES);
-    float *red = reinterpret_cast<float *>(smem + SK_TBL_BYTES + SK_PIECE_CHUNKS * 64);  // [SK_WARPS][64]
+    float *red = reinterpret_cast<float *>(smem + SK_TBL_BYTES + SK_PIECE_BYTES);  // [SK_WARPS][64]
     unsigned int &s_last = *reinterpret_cast<unsigned int *>(red + SK_WARPS * 64);
     float &s_inv = *reinterpret_cast<float *>(red + SK_WARPS * 64 + 1);
 
@@ -117,22 +143,26 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
         __syncthreads();  // the previous segment is done with the tables, x and the reduction buffer
         // ---- pair tables: entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]} ------------------------
         // warp w writes the entries with hi = w, w + SK_WARPS, ...; lane L writes its own bank.
+        if (BITS == 4) {
 #pragma unroll
-        for (int t = 0; t < 2; t++) {
-            const uint32_t row = (t == 0 ? hb1 : hb2) * 32 + lane;
-            const uint16_t *prow = (t == 0 ? a.pal1 : a.pal2) + (size_t)row * 16;
-            const uint4 p0 = *reinterpret_cast<const uint4 *>(prow);
-            const uint4 pp = *reinterpret_cast<const uint4 *>(prow + 8);
-            const uint32_t cbp[8] = {p0.x, p0.y, p0.z, p0.w, pp.x, pp.y, pp.z, pp.w};
-            for (uint32_t hi = warp; hi < 16; hi += SK_WARPS) {
-                const uint32_t hi_pair = reinterpret_cast<const uint32_t *>(prow)[hi >> 1];  // {pal[hi&~1], pal[hi|1]}
-                const uint32_t hsel = (hi & 1) ? 0x7600u : 0x5400u;
+            for (int t = 0; t < 2; t++) {
+                const uint32_t row = (t == 0 ? hb1 : hb2) * 32 + lane;
+                const uint16_t *prow = (t == 0 ? a.pal1 : a.pal2) + (size_t)row * 16;
+                const uint4 p0 = *reinterpret_cast<const uint4 *>(prow);
+                const uint4 pp = *reinterpret_cast<const uint4 *>(prow + 8);
+                const uint32_t cbp[8] = {p0.x, p0.y, p0.z, p0.w, pp.x, pp.y, pp.z, pp.w};
+                for (uint32_t hi = warp; hi < 16; hi += SK_WARPS) {
+                    const uint32_t hi_pair = reinterpret_cast<const uint32_t *>(prow)[hi >> 1];  // {pal[hi&~1], pal[hi|1]}
+                    const uint32_t hsel = (hi & 1) ? 0x7600u : 0x5400u;
 #pragma unroll
-                for (int lo = 0; lo < 16; lo++) {
-                    const uint32_t v = __byte_perm(cbp[lo >> 1], hi_pair, hsel | ((lo & 1) ? 0x32u : 0x10u));
-                    tbl[((uint32_t)lo + 16u * hi) * 64 + t * 32 + lane] = v;
+                    for (int lo = 0; lo < 16; lo++) {
+                        const uint32_t v = __byte_perm(cbp[lo >> 1], hi_pair, hsel | ((lo & 1) ? 0x32u : 0x10u));
+                        tbl[((uint32_t)lo + 16u * hi) * 64 + t * 32 + lane] = v;
+                    }
                 }
             }
+        } else {
+            sk_build_table2(tbl, a.pal1, a.pal2, hb1, hb2, lane, warp, SK_WARPS);
         }
 
         if (!waited) {
@@ -176,8 +206,8 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
             // ---- stage this piece of x (fp16, normalised on the way if asked) --------------------
             if (pb != cb) __syncthreads();  // every warp has finished reading the previous piece
             {
-                const uint32_t n16 = (min(ce, pb + SK_PIECE_CHUNKS) - pb) * 4;  // 16-byte units
-                const uint4 *xg = reinterpret_cast<const uint4 *>(xrow + (size_t)pb * 32);
+                const uint32_t n16 = (min(ce, pb + SK_PIECE_CHUNKS) - pb) * (XB / 16);  // 16-byte units
+                const uint4 *xg = reinterpret_cast<const uint4 *>(xrow + (size_t)pb * (XB / 2));
                 uint4 *xd = reinterpret_cast<uint4 *>(xs);
                 if (a.norm_n == 0) {
                     for (uint32_t i = tid; i < n16; i += SK_THREADS) xd[i] = xg[i];
@@ -197,15 +227,21 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
             __syncthreads();
             // ---- stream this warp's chunks of the piece: 16 per full piece ------------------------
             const uint32_t j_end = min(nj, j + SK_PIECE_CHUNKS / SK_WARPS);
-            uint32_t x_off = warp * 64;
+            uint32_t x_off = warp * XB;
 #define SK_STEP(I)                                                                                              \
-    if ((I) < SK_PF && ((I) == 0 || j + (I) < j_end))                                                           \
-        sk_chunk<SBASE, (I) * SK_WARPS * 512>(acc, q1[(I) % SK_PF], q2[(I) % SK_PF], xb, lane_off,                  \
-                                              x_off + (I) * SK_WARPS * 64, diag, smem_base, src,                 \
-                                              j + (I) + SK_PF < nj);
+    if ((I) < SK_PF && ((I) == 0 || j + (I) < j_end)) {                                                         \
+        if (BITS == 4)                                                                                          \
+            sk_chunk<SBASE, (I) * SK_WARPS * 512>(acc, q1[(I) % SK_PF], q2[(I) % SK_PF], xb, lane_off,              \
+                                                  x_off + (I) * SK_WARPS * XB, diag, smem_base, src,             \
+                                                  j + (I) + SK_PF < nj);                                        \
+        else                                                                                                    \
+            sk_chunk2<SBASE, (I) * SK_WARPS * 512>(acc, q1[(I) % SK_PF], q2[(I) % SK_PF], xb, lane_off,             \
+                                                   x_off + (I) * SK_WARPS * XB, diag, smem_base, src,            \
+                                                   j + (I) + SK_PF < nj);                                       \
+    }
             for (; j < j_end; j += SK_PF) {
                 SK_STEP(0) SK_STEP(1) SK_STEP(2) SK_STEP(3)
-                x_off += SK_PF * SK_WARPS * 64;
+                x_off += SK_PF * SK_WARPS * XB;
                 src.advance(SK_PF * SK_WARPS * 512);
             }
 #undef SK_STEP
@@ -328,25 +364,32 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
     }
 }
 
-template <int MODE, int SBASE>
+template <int MODE, int SBASE, int BITS>
 static int launch_sk_v(prism_cuda_ctx *ctx, const SkArgs &a, dim3 grid) {
     static bool configured[PRISM_MAX_DEVICES] = {false};
     if (!configured[ctx->device]) {
-        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_sk_kernel<MODE, SBASE>,
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(lut_gemv_sk_kernel<MODE, SBASE, BITS>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_BYTES));
         configured[ctx->device] = true;
     }
-    launch_pdl(ctx, "lut_gemv_sk_kernel", lut_gemv_sk_kernel<MODE, SBASE>, grid, SK_THREADS, SK_SMEM_BYTES, a);
+    launch_pdl(ctx, "lut_gemv_sk_kernel", lut_gemv_sk_kernel<MODE, SBASE, BITS>, grid, SK_THREADS, SK_SMEM_BYTES, a);
     return after_launch(ctx, "lut_gemv_sk_kernel");
 }
 
 template <int MODE>
-static int launch_sk(prism_cuda_ctx *ctx, const SkArgs &a, dim3 grid) {
-    if (ctx->smem_base == SK_KNOWN_SBASE) return launch_sk_v<MODE, SK_KNOWN_SBASE>(ctx, a, grid);
-    return launch_sk_v<MODE, -1>(ctx, a, grid);
+static int launch_sk(prism_cuda_ctx *ctx, const SkArgs &a, dim3 grid, uint32_t bits) {
+    if (bits == 2) {
+        if (ctx->smem_base == SK_KNOWN_SBASE) return launch_sk_v<MODE, SK_KNOWN_SBASE, 2>(ctx, a, grid);
+        return launch_sk_v<MODE, -1, 2>(ctx, a, grid);
+    }
+    if (ctx->smem_base == SK_KNOWN_SBASE) return launch_sk_v<MODE, SK_KNOWN_SBASE, 4>(ctx, a, grid);
+    return launch_sk_v<MODE, -1, 4>(ctx, a, grid);
 }
 
-bool sk_eligible(const LutTensor &t) { return t.bits == 4 && t.k % 32 == 0 && t.k >= 32; }
+// 4 bit: whole 32-weight chunks; 2 bit: whole 64-weight chunks
+bool sk_eligible(const LutTensor &t) {
+    return (t.bits == 4 && t.k % 32 == 0 && t.k >= 32) || (t.bits == 2 && t.k % 64 == 0 && t.k >= 64);
+}
 
 // Chooses the partition (see SkPart) for one activation vector of a batch.
 SkPart sk_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch) {
@@ -380,10 +423,10 @@ int launch_gemv_sk(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const
     a.counters = ctx->splitk_counters;
     const dim3 grid(G, batch);
     switch (mode) {
-    case GEMV_PLAIN: return launch_sk<GEMV_PLAIN>(ctx, a, grid);
-    case GEMV_RESID: return launch_sk<GEMV_RESID>(ctx, a, grid);
-    case GEMV_F32: return launch_sk<GEMV_F32>(ctx, a, grid);
-    default: return launch_sk<GEMV_SWIGLU>(ctx, a, grid);
+    case GEMV_PLAIN: return launch_sk<GEMV_PLAIN>(ctx, a, grid, t.bits);
+    case GEMV_RESID: return launch_sk<GEMV_RESID>(ctx, a, grid, t.bits);
+    case GEMV_F32: return launch_sk<GEMV_F32>(ctx, a, grid, t.bits);
+    default: return launch_sk<GEMV_SWIGLU>(ctx, a, grid, t.bits);
     }
 }
 

@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     if (smem_base != (uint32_t)T5_SBASE) {  // layout assumption broken: refuse to compute
-        if (threadIdx.x == 0) atomicExch(a.err, 2u);
+        if (threadIdx.x == 0) atomicExch(a.err, 1u);
         return;
     }
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -397,7 +397,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) lut_gemv_tc5_kernel(const Tc5Ar
     if (warp == T5_DEQ_WARPS) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)T5_TMEM_COLS) : "memory");
     }
-    if (tid == 0 && *err_flag) atomicExch(a.err, 3u);
+    if (tid == 0 && *err_flag) atomicExch(a.err, 5u);
 }
 
 // ---- host side ---------------------------------------------------------------------------------

@@ -179,4 +179,38 @@ __device__ __forceinline__ void sk_lookup(uint32_t (&A)[8], uint32_t w1, uint32_
     A[6] = sk_lds<SBASE, 0>(o13, base);   A[7] = sk_lds<SBASE, 128>(o23, base);
 }
 
+// ---- 2-bit indices (4-entry palette) through the same lookups ------------------------------------
+// A 2-bit index word holds 16 weights; a NIBBLE (two weights) indexes a 16-entry pair table laid out
+// like the 4-bit one (entry e at byte e*256 + t*128 + lane*4).  The even and odd nibble planes of the
+// word are separated and re-interleaved so that the bytes of each resulting word are the table indices
+// of four consecutive weight pairs -- exactly what a 4-bit index word is to sk_lookup.
+__device__ __forceinline__ void sk_expand2_word(uint32_t &lo, uint32_t &hi, uint32_t w) {
+    const uint32_t we = w & 0x0F0F0F0Fu, wo = (w >> 4) & 0x0F0F0F0Fu;  // pairs (0,1),(4,5),.. and (2,3),(6,7),..
+    lo = __byte_perm(we, wo, 0x5140);  // weights 0..7
+    hi = __byte_perm(we, wo, 0x7362);  // weights 8..15
+}
+// 16 bytes of 2-bit indices (64 weights) -> two pseudo 4-bit chunks of 32 weights
+__device__ __forceinline__ void sk_expand2(uint4 &a, uint4 &b, const uint4 &w) {
+    sk_expand2_word(a.x, a.y, w.x);
+    sk_expand2_word(a.z, a.w, w.y);
+    sk_expand2_word(b.x, b.y, w.z);
+    sk_expand2_word(b.z, b.w, w.w);
+}
+// Pair table of a block of 2-bit rows: entry e = i0 | i1 << 2 -> half2{pal[i0], pal[i1]}, 16 entries per
+// row.  `n_warps` warps share the entries; lane L writes its own bank.
+__device__ __forceinline__ void sk_build_table2(uint32_t *tbl, const uint16_t *pal1, const uint16_t *pal2, uint32_t hb1,
+                                                uint32_t hb2, uint32_t lane, uint32_t warp, uint32_t n_warps) {
+#pragma unroll
+    for (int t = 0; t < 2; t++) {
+        const uint32_t row = (t == 0 ? hb1 : hb2) * 32 + lane;
+        const uint2 p = *reinterpret_cast<const uint2 *>((t == 0 ? pal1 : pal2) + (size_t)row * 4);  // 4 fp16
+        for (uint32_t e = warp; e < 16; e += n_warps) {
+            const uint32_t i0 = e & 3, i1 = e >> 2;
+            const uint32_t v0 = ((i0 & 2) ? p.y : p.x) >> ((i0 & 1) * 16) & 0xFFFFu;
+            const uint32_t v1 = ((i1 & 2) ? p.y : p.x) >> ((i1 & 1) * 16) & 0xFFFFu;
+            tbl[e * 64 + t * 32 + lane] = v0 | (v1 << 16);
+        }
+    }
+}
+
 }  // namespace prism

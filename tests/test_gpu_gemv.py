@@ -13,6 +13,8 @@ from prism_engine_b200 import synth
 pytestmark = pytest.mark.gpu
 TOL = 1e-3
 
+SAMPLED_TOKENS = [0, 1, 127, 128, 255, 256, 1000, 2047]   # first, last, and both sides of the 128- and 256-token tile edges
+
 GEMV_SHAPES = [(64, 32), (33, 64), (100, 96), (4864, 896), (896, 4864), (128, 896), (896, 896), (1000, 8),
                (72, 40), (8192, 1024), (2368, 8192), (3712, 256),
                (640, 29568), (20000, 512), (9000, 1312)]
@@ -37,12 +39,61 @@ def test_gemv_matches_oracle(backend, oracle, variant, m, k):
     backend.set_option("gemv_variant", 1)
 
 
-@pytest.mark.parametrize("m,k", [(65, 64), (512, 3584), (96, 128)])
-def test_gemv_2bit(backend, oracle, m, k):
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("m,k", [(65, 64), (512, 3584), (96, 128), (100, 48), (3584, 18944), (18944, 3584), (4864, 896)])
+def test_gemv_2bit(backend, oracle, variant, m, k):
+    """2-bit indices / 4-entry palettes (no such format in the reference: the oracle's generalisation is the pin).
+    variant 1 takes the pair-table tensor-core kernel when K is a whole number of 64-weight chunks, the plain
+    kernel otherwise; variant 0 is always the plain kernel."""
+    backend.set_option("gemv_variant", variant)
     pay = synth.make_payload(m, k, 2, seed=m + k)
     x = synth.make_activation(k, seed=3)
     h = backend.upload("g2", pay, m, k, bits=2)
-    assert rel_l2(backend.gemv(h, x), oracle.lut_gemv(x, pay, m, k, bits=2)) <= TOL
+    y = backend.gemv(h, x)
+    want = oracle.lut_gemv(x, pay, m, k, bits=2, threads=8)
+    assert rel_l2(y, want) <= TOL
+    assert np.mean(y == want) > 0.9
+    backend.free(h)
+    backend.set_option("gemv_variant", 1)
+
+
+def test_gemv_2bit_one_hot_is_exact(backend, oracle):
+    m, k = 512, 3584
+    pay = synth.make_payload(m, k, 2, seed=9)
+    W = oracle.dequant(pay, m, k, bits=2)
+    h = backend.upload("oh2", pay, m, k, bits=2)
+    for j in (0, 1, 2, 3, 63, 64, 1000, 3583):
+        x = np.zeros(k, np.uint16)
+        x[j] = 0x3C00
+        want = W[:, j].copy()
+        want[want == 0x8000] = 0
+        assert np.array_equal(backend.gemv(h, x), want), j
+    backend.free(h)
+
+
+@pytest.mark.parametrize("name,m,k", [("kv", 512, 3584), ("q", 3584, 3584), ("gate_up", 18944, 3584), ("down", 3584, 18944)])
+def test_gemm_2bit_prefill_shapes_match_oracle(backend, oracle, name, m, k):
+    """The 2-bit variant of the prefill configuration through the tensor-core GEMM (parity unpinned by the reference)."""
+    m_tok = 2048
+    pay = synth.make_payload(m, k, 2, seed=70 + m % 5)
+    h = backend.upload(f"c4b2.{name}", pay, m, k, bits=2)
+    X = synth.make_activation((m_tok, k), seed=m + 2 * k)
+    Y = backend.gemm(h, X)
+    want = oracle.lut_gemm(X[SAMPLED_TOKENS], pay, m, k, bits=2, threads=oracle.max_threads())
+    got = Y[SAMPLED_TOKENS]
+    assert rel_l2(got.reshape(-1), want.reshape(-1)) <= TOL
+    assert np.mean(got == want) > 0.9
+    backend.free(h)
+
+
+@pytest.mark.parametrize("m,k,m_tok", [(192, 256, 37), (130, 128, 9), (640, 1024, 300)])
+def test_gemm_2bit_small_shapes(backend, oracle, m, k, m_tok):
+    pay = synth.make_payload(m, k, 2, seed=8)
+    X = synth.make_activation((m_tok, k), seed=8)
+    h = backend.upload("gm2", pay, m, k, bits=2)
+    Y = backend.gemm(h, X)
+    want = oracle.lut_gemm(X, pay, m, k, bits=2, threads=8)
+    assert rel_l2(Y.reshape(-1), want.reshape(-1)) <= TOL and np.mean(Y == want) > 0.9
     backend.free(h)
 
 
@@ -130,7 +181,6 @@ def test_gemm_full_size_rows_match_gemv(backend):
 
 
 CONFIG4 = [("q", 3584, 3584), ("kv", 512, 3584), ("gate_up", 18944, 3584), ("down", 3584, 18944)]
-SAMPLED_TOKENS = [0, 1, 127, 128, 255, 256, 1000, 2047]   # first, last, and both sides of the 128- and 256-token tile edges
 
 
 @pytest.mark.timeout(900)
