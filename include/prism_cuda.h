@@ -74,6 +74,9 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
  * "sk_min_chunks" (default 8: fewest 1 KB index chunks the GEMV gives one CTA of a small matrix),
  * "sk_stream_chunks" (default 64: chunks per CTA from which the GEMV deals contiguous, balanced
  * ranges to a persistent grid instead of cutting every 64-row block into equal parts),
+ * "cl_max_units" (default 8192: matrices of at most this many (64-row block x 1 KB index chunk) units go to
+ * the cluster GEMV, whose CTAs hold all their indices in registers before the previous kernel has
+ * finished and reduce through distributed shared memory; 0 = never),
  * "wait_limit_polls" (default 0 = built-in, about fifteen seconds: polls after which a kernel stops
  * waiting for a tensor-parallel peer or a grid-wide arrival, records a device error code and goes on;
  * the next synchronising call then returns PRISM_E_TIMEOUT and the context stays usable),

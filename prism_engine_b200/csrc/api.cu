@@ -97,6 +97,8 @@ int device_error_result(prism_cuda_ctx *ctx, unsigned int v) {
                                           "limit; the step went on with what had arrived and its result is not valid" + code);
     case 4:
         return fail(ctx, PRISM_E_TIMEOUT, "a grid-wide arrival inside a persistent kernel gave up; its output is incomplete" + code);
+    case 6:
+        return fail(ctx, PRISM_E_STATE, "the cluster GEMV was not launched with the cluster shape it was given" + code);
     case 5:
         return fail(ctx, PRISM_E_TIMEOUT, "a tcgen05 kernel gave up waiting on an mbarrier; its output is incomplete" + code);
     default:
@@ -217,6 +219,10 @@ void prism_cuda_destroy(prism_cuda_ctx *ctx) {
     cudaFree(ctx->dev_err);
     cudaFree(ctx->kv_k);
     cudaFree(ctx->kv_v);
+    for (auto *t : ctx->rope_tabs) {
+        cudaFree(t->dev);
+        delete t;
+    }
     extern void prism_tp_shutdown(prism_cuda_ctx *);
     prism_tp_shutdown(ctx);
     cudaStreamDestroy(ctx->stream);
@@ -248,6 +254,9 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
     } else if (!strcmp(key, "sk_stream_chunks")) {
         if (value < 8 || value > (1 << 20)) return fail(ctx, PRISM_E_ARG, "sk_stream_chunks must be in 8..2^20");
         ctx->sk_stream_chunks = (int)value;
+    } else if (!strcmp(key, "cl_max_units")) {
+        if (value < 0 || value > (1 << 24)) return fail(ctx, PRISM_E_ARG, "cl_max_units must be in 0..2^24");
+        ctx->cl_max_units = (int)value;
     } else if (!strcmp(key, "batch_gemv_max")) {
         if (value < 1 || value > 4096) return fail(ctx, PRISM_E_ARG, "batch_gemv_max must be in 1..4096");
         ctx->batch_gemv_max = (int)value;
@@ -257,6 +266,8 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
         ctx->attn_cluster = (int)value;
     } else if (!strcmp(key, "tp_peer_ar")) {
         ctx->tp_peer_ar = value ? 1 : 0;
+    } else if (!strcmp(key, "tp_fused_ar")) {
+        ctx->tp_fused_ar = value ? 1 : 0;
     } else if (!strcmp(key, "pdl")) {
         ctx->pdl = value ? 1 : 0;
     } else if (!strcmp(key, "cimage_cache")) {

@@ -5,12 +5,18 @@
 // rope_inplace, cpu_fallback.rs:131-143), with the same fp16 rounding points: q and k are rounded
 // to fp16 after the rotation, the output after the weighted sum.
 //
-// A thread-block cluster of S CTAs serves one (query head, sequence): CTA r scores and weighs the
-// positions [r*chunk, (r+1)*chunk) of the cache.  The softmax is the reference's two-pass form
-// (global maximum, exp, global sum, `* inv` inside the weighted sum); the S CTAs exchange their
-// maxima, sums and partial outputs through distributed shared memory, so nothing goes through
-// global scratch and the result does not depend on scheduling.
+// A thread-block cluster of S CTAs serves one (KV head, sequence) and ALL the query heads that
+// share that KV head (grouped-query attention: up to GT = 8 heads per pass over the cache), so a
+// cached row is read once per group instead of once per query head.  CTA r scores and weighs the
+// positions [r*chunk, (r+1)*chunk): one warp per cached row, every row of a pass in flight at once,
+// the value rows requested together with the key rows so that their latency hides behind the
+// softmax.  The softmax is the reference's two-pass form (global maximum, exp, global sum, `* inv`
+// inside the weighted sum); the S CTAs exchange their maxima, sums and partial outputs through
+// distributed shared memory, so nothing goes through global scratch and the result does not
+// depend on scheduling.
 #include <cooperative_groups.h>
+
+#include <cmath>
 
 #include "common.cuh"
 
@@ -20,15 +26,9 @@ namespace prism {
 
 constexpr int FA_THREADS = 256;
 constexpr int FA_WARPS = FA_THREADS / 32;
-constexpr int FA_INFLIGHT = 8;  // cached rows a warp has in flight
 
 __device__ __forceinline__ float fa_h2f(uint16_t v) { return __half2float(__ushort_as_half(v)); }
 __device__ __forceinline__ uint16_t fa_f2h(float v) { return __half_as_ushort(__float2half_rn(v)); }
-__device__ __forceinline__ float fa_warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-    return v;
-}
 
 struct FusedAttnArgs {
     const uint16_t *q, *k, *v;  // this step's projections: rows of nh*hd / nkv*hd halfs, src_stride apart
@@ -40,45 +40,111 @@ struct FusedAttnArgs {
     uint32_t nh, nkv, batch;
     uint64_t seq_stride;        // halfs between sequences in the cache
     uint32_t max_seq;           // slots per sequence
-    uint32_t chunk_cap;         // floats of score buffer per CTA
+    uint32_t chunk_cap;         // positions of score buffer per CTA
     uint32_t rope_k;
-    float rope_base;
+    const float *inv_freq;      // [hd/2] rotation frequencies base^(-2j/hd), computed once on the host
 };
 
-// Rotates the VEC elements a lane owns (elements lane*VEC .. +VEC-1 of a head of 32*VEC): the
-// partner element j +- hd/2 lives in lane ^ 16.
+// cos / sin of the rotation of the VEC elements a lane owns (elements lane*VEC .. +VEC-1 of a head
+// of 32*VEC): the angle depends on the position and the pair index only, so it is computed once
+// and applied to every query head and to k.
 template <int VEC>
-__device__ __forceinline__ void fa_rope(float (&x)[VEC], uint32_t lane, float pos, float base) {
-    constexpr uint32_t hd = 32 * VEC, half = hd / 2;
+__device__ __forceinline__ void fa_rope_angles(float (&ca)[VEC], float (&sa)[VEC], uint32_t lane, float pos,
+                                               const float *__restrict__ inv_freq) {
+    constexpr uint32_t half = 16 * VEC;
+#pragma unroll
+    for (int i = 0; i < VEC; i++) {
+        const uint32_t d = lane * VEC + i;
+        const uint32_t j = d < half ? d : d - half;
+        const float ang = pos * __ldg(inv_freq + j);
+        sincosf(ang, &sa[i], &ca[i]);
+    }
+}
+
+// Values of the same shared-memory word in every CTA of the cluster (at most 8), requested together:
+// a loop with a run-time trip count would issue the remote loads one after the other.
+template <typename G>
+__device__ __forceinline__ void fa_gather(float (&v)[8], G &cluster, float *word, uint32_t S, float neutral) {
+#pragma unroll
+    for (uint32_t r = 0; r < 8; r++) v[r] = r < S ? *cluster.map_shared_rank(word, r) : neutral;
+}
+// Rotates a lane's elements; the partner element j +- hd/2 lives in lane ^ 16.
+template <int VEC>
+__device__ __forceinline__ void fa_rope_apply(float (&x)[VEC], const float (&ca)[VEC], const float (&sa)[VEC], uint32_t lane) {
+    constexpr uint32_t half = 16 * VEC;
 #pragma unroll
     for (int i = 0; i < VEC; i++) {
         const float other = __shfl_xor_sync(0xFFFFFFFFu, x[i], 16);
         const uint32_t d = lane * VEC + i;
-        const uint32_t j = d < half ? d : d - half;
-        const float ang = pos * powf(base, -2.0f * (float)j / (float)hd);
-        float sa, ca;
-        sincosf(ang, &sa, &ca);
         // d < half: (a, b) = (mine, other) -> a*cos - b*sin;  else (a, b) = (other, mine) -> a*sin + b*cos
-        const float r = d < half ? __fsub_rn(__fmul_rn(x[i], ca), __fmul_rn(other, sa))
-                                 : __fadd_rn(__fmul_rn(other, sa), __fmul_rn(x[i], ca));
+        const float r = d < half ? __fsub_rn(__fmul_rn(x[i], ca[i]), __fmul_rn(other, sa[i]))
+                                 : __fadd_rn(__fmul_rn(other, sa[i]), __fmul_rn(x[i], ca[i]));
         x[i] = fa_h2f(fa_f2h(r));
     }
 }
 
-template <int VEC>
+// Sums each of GT per-lane values over the 32 lanes of a warp.  log2(GT) exchange rounds halve the
+// number of values a lane carries (offsets 16, 8, ...), the rest are plain butterfly adds: 9
+// shuffles for GT = 8 instead of 40.  Returns the total of value number (lane >> (5 - log2 GT)).
+template <int GT>
+__device__ __forceinline__ float fa_reduce_heads(float (&s)[GT], uint32_t lane) {
+    int off = 16;
+#pragma unroll
+    for (int n = GT; n > 1; n >>= 1, off >>= 1) {
+        const bool up = (lane & off) != 0;
+#pragma unroll
+        for (int j = 0; j < n / 2; j++) {
+            const float send = up ? s[j] : s[j + n / 2];
+            const float keep = up ? s[j + n / 2] : s[j];
+            s[j] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, off);
+        }
+    }
+    float v = s[0];
+#pragma unroll
+    for (; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    return v;
+}
+
+// 16-byte asynchronous copy global -> shared (the cached rows of a pass are all requested before any is used)
+__device__ __forceinline__ void fa_cp16(void *dst_smem, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void fa_cp_wait_all() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+}
+
+// rows of a tile: K and V tiles together take 48 KB of shared memory
+__host__ __device__ constexpr uint32_t fa_tile_rows(uint32_t hd) { return 24576u / (hd * 2u); }
+
+// The loops over cached rows are real loops (two rows per trip): a kernel that runs once per layer and
+// token pays for every instruction it has to fetch, so the code is kept small and the memory
+// parallelism comes from the asynchronous copies, not from unrolling.
+template <int VEC, int GT>
 __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t S = cluster.dim_blocks().x, rank = cluster.block_rank();
-    extern __shared__ float sc[];                 // [chunk_cap] scores, then exp
-    __shared__ float sh[32];
-    __shared__ float xch[2];                      // this CTA's maximum and sum, read by its peers
-    __shared__ float part[FA_WARPS * 32 * VEC];   // per-warp partial outputs; row 0 ends as the CTA's partial
     constexpr uint32_t hd = 32 * VEC;
-    const uint32_t h = blockIdx.x / S, b = blockIdx.y;
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t g = a.nh / a.nkv, kh = h / g, kvd = a.nkv * hd;
+    constexpr uint32_t PR = fa_tile_rows(hd);      // cached rows staged per pass
+    constexpr uint32_t HL = 32 / GT;               // lanes that end up with the same head's score
+    extern __shared__ __align__(16) float fa_dyn[];
+    float *sc = fa_dyn;                                            // [chunk_cap][GT] scores, then exp
+    float *qs = fa_dyn + (((size_t)a.chunk_cap * GT + 3) & ~(size_t)3);  // [GT][hd] rotated q (16-byte aligned)
+    uint16_t *newk = reinterpret_cast<uint16_t *>(qs + GT * hd);   // [hd] this token's rotated k, [hd] its v
+    uint16_t *newv = newk + hd;
+    uint16_t *kt = newv + hd;                                      // [PR][hd] key tile
+    uint16_t *vt = kt + PR * hd;                                   // [PR][hd] value tile
+    float *part = reinterpret_cast<float *>(kt);                   // after the last tile: [FA_WARPS][GT*hd] partial outputs
+    __shared__ float sh[FA_WARPS][GT];
+    __shared__ float xch[2][GT];                   // this CTA's maxima and sums, read by its peers
+    __shared__ float sinv[GT];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, b = blockIdx.y;
+    const uint32_t g = a.nh / a.nkv, n_tiles = (g + GT - 1) / GT, kvd = a.nkv * hd;
+    const uint32_t cl = blockIdx.x / S, kh = cl / n_tiles, tile = cl - kh * n_tiles;
+    const uint32_t h0 = kh * g + tile * GT;        // first query head of this cluster
+    const uint32_t nhl = min((uint32_t)GT, g - tile * GT);
 
     const int32_t pos = *a.pos_dev;
     const int64_t slot64 = (int64_t)pos * a.slot_mul + a.slot_add;
@@ -90,144 +156,207 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
     uint32_t chunk = (sl + S - 1) / S;
     if (chunk > a.chunk_cap) chunk = a.chunk_cap;  // cannot happen with chunk_cap = ceil(max_seq / S)
     const uint32_t p_begin = min(sl, rank * chunk), p_end = min(sl, p_begin + chunk);
+    const uint32_t n_loc = p_end - p_begin;
+    const uint32_t n_pass = (n_loc + PR - 1) / PR;
 
-    // ---- q, and the new token's k and v, in registers (lane: elements lane*VEC..) ---------------
-    float qf[VEC], kn[VEC], vn[VEC];
+    uint16_t *kcb = a.kc + (size_t)b * a.seq_stride + (size_t)kh * hd;
+    uint16_t *vcb = a.vc + (size_t)b * a.seq_stride + (size_t)kh * hd;
+    constexpr uint32_t PPR = hd / 8;               // 16-byte pieces per row
+    // rows [r0, r0 + n) of this CTA's range into the tiles (the new token's row comes from registers instead)
+    auto stage = [&](uint32_t r0, uint32_t n, bool with_k) {
+        for (uint32_t i = threadIdx.x; i < n * PPR; i += FA_THREADS) {
+            const uint32_t r = i / PPR, c = i - r * PPR, p = p_begin + r0 + r;
+            if (p == new_slot) continue;
+            if (with_k) fa_cp16(kt + r * hd + c * 8, kcb + (size_t)p * kvd + c * 8);
+            fa_cp16(vt + r * hd + c * 8, vcb + (size_t)p * kvd + c * 8);
+        }
+    };
+    stage(0, min(n_loc, PR), true);                // requested before anything else is computed
+
+    // ---- rotation: warp w prepares query head w of the group, warp 0 also the new token's k and v ----
     {
-        const uint16_t *q = a.q + (size_t)b * a.src_stride + (size_t)h * hd + lane * VEC;
-        const uint16_t *k = a.k + (size_t)b * a.src_stride + (size_t)kh * hd + lane * VEC;
-        const uint16_t *v = a.v + (size_t)b * a.src_stride + (size_t)kh * hd + lane * VEC;
+        float ca[VEC], sa[VEC];
+        fa_rope_angles<VEC>(ca, sa, lane, (float)pos, a.inv_freq);
+        for (uint32_t hh = warp; hh < (uint32_t)GT; hh += FA_WARPS) {
+            float x[VEC];
+            const uint16_t *q = a.q + (size_t)b * a.src_stride + (size_t)(h0 + hh) * hd + lane * VEC;
 #pragma unroll
-        for (int i = 0; i < VEC; i++) {
-            qf[i] = fa_h2f(q[i]);
-            kn[i] = fa_h2f(k[i]);
-            vn[i] = fa_h2f(v[i]);
+            for (int i = 0; i < VEC; i++) x[i] = hh < nhl ? fa_h2f(q[i]) : 0.0f;
+            fa_rope_apply<VEC>(x, ca, sa, lane);
+#pragma unroll
+            for (int i = 0; i < VEC; i++) qs[hh * hd + lane * VEC + i] = x[i];
         }
-        fa_rope<VEC>(qf, lane, (float)pos, a.rope_base);
-        if (a.rope_k) fa_rope<VEC>(kn, lane, (float)pos, a.rope_base);
-    }
-    uint16_t *kcb = a.kc + (size_t)b * a.seq_stride + (size_t)kh * hd + lane * VEC;
-    uint16_t *vcb = a.vc + (size_t)b * a.seq_stride + (size_t)kh * hd + lane * VEC;
-    const bool own_new = have_new && new_slot >= p_begin && new_slot < p_end;
-    // KVCache::append: the first query head of a group stores the row for all later steps
-    if (own_new && h % g == 0 && warp == 0) {
+        if (warp == 0) {
+            float kn[VEC];
+            const uint16_t *k = a.k + (size_t)b * a.src_stride + (size_t)kh * hd + lane * VEC;
+            const uint16_t *v = a.v + (size_t)b * a.src_stride + (size_t)kh * hd + lane * VEC;
 #pragma unroll
-        for (int i = 0; i < VEC; i++) {
-            kcb[(size_t)new_slot * kvd + i] = fa_f2h(kn[i]);
-            vcb[(size_t)new_slot * kvd + i] = fa_f2h(vn[i]);
-        }
-    }
-
-    // ---- scores of this CTA's positions: one warp per position, FA_INFLIGHT rows in flight -------
-    const float div = sqrtf((float)hd);
-    struct alignas(2 * VEC) Row { uint16_t e[VEC]; };
-    for (uint32_t p0 = p_begin + warp; p0 < p_end; p0 += FA_INFLIGHT * FA_WARPS) {
-        Row r[FA_INFLIGHT];
+            for (int i = 0; i < VEC; i++) kn[i] = fa_h2f(k[i]);
+            if (a.rope_k) fa_rope_apply<VEC>(kn, ca, sa, lane);
+            const bool own_new = have_new && new_slot >= p_begin && new_slot < p_end;
 #pragma unroll
-        for (int u = 0; u < FA_INFLIGHT; u++) {
-            const uint32_t p = p0 + u * FA_WARPS;
-            if (p < p_end && p != new_slot) r[u] = *reinterpret_cast<const Row *>(kcb + (size_t)p * kvd);
-        }
-#pragma unroll
-        for (int u = 0; u < FA_INFLIGHT; u++) {
-            const uint32_t p = p0 + u * FA_WARPS;
-            if (p < p_end) {  // warp-uniform
-                float s = 0.0f;
-                if (p == new_slot) {
-#pragma unroll
-                    for (int i = 0; i < VEC; i++) s += qf[i] * kn[i];
-                } else {
-#pragma unroll
-                    for (int i = 0; i < VEC; i++) s += qf[i] * fa_h2f(r[u].e[i]);
+            for (int i = 0; i < VEC; i++) {
+                const uint16_t kb = fa_f2h(kn[i]), vb = v[i];
+                newk[lane * VEC + i] = kb;
+                newv[lane * VEC + i] = vb;
+                // KVCache::append: the first head tile of a group stores the row for all later steps
+                if (own_new && tile == 0) {
+                    kcb[(size_t)new_slot * kvd + lane * VEC + i] = kb;
+                    vcb[(size_t)new_slot * kvd + lane * VEC + i] = vb;
                 }
-                s = fa_warp_sum(s);
-                if (lane == 0) sc[p - p_begin] = s / div;
             }
         }
     }
+    fa_cp_wait_all();
     __syncthreads();
 
-    // ---- maximum over all positions: local, then across the cluster ------------------------------
-    const uint32_t n_loc = p_end - p_begin;
-    float mx = -INFINITY;
-    for (uint32_t p = threadIdx.x; p < n_loc; p += FA_THREADS) mx = fmaxf(mx, sc[p]);
+    // ---- q of every head of the group in registers --------------------------------------------------
+    float qf[GT][VEC];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-    if (lane == 0) sh[warp] = mx;
+    for (int hh = 0; hh < GT; hh++)
+#pragma unroll
+        for (int i = 0; i < VEC; i++) qf[hh][i] = qs[hh * hd + lane * VEC + i];
+
+    // ---- scores of this CTA's positions: one warp per position, GT heads per row -------------------
+    const float div = sqrtf((float)hd);
+    for (uint32_t ps = 0; ps < n_pass; ps++) {
+        const uint32_t r0 = ps * PR, n = min(PR, n_loc - r0);
+        if (ps > 0) {
+            __syncthreads();                       // every warp is done with the previous tile
+            stage(r0, n, true);
+            fa_cp_wait_all();
+            __syncthreads();
+        }
+#pragma unroll 2
+        for (uint32_t r = warp; r < n; r += FA_WARPS) {
+            const uint32_t p = p_begin + r0 + r;
+            const uint16_t *krow = (p == new_slot ? newk : kt + r * hd) + lane * VEC;
+            float kf[VEC], s[GT];
+#pragma unroll
+            for (int i = 0; i < VEC; i++) kf[i] = fa_h2f(krow[i]);
+#pragma unroll
+            for (int hh = 0; hh < GT; hh++) {
+                s[hh] = 0.0f;
+#pragma unroll
+                for (int i = 0; i < VEC; i++) s[hh] += qf[hh][i] * kf[i];
+            }
+            const float tot = fa_reduce_heads<GT>(s, lane);
+            if ((lane & (HL - 1)) == 0) sc[(size_t)(r0 + r) * GT + lane / HL] = tot / div;
+        }
+    }
     __syncthreads();
-    if (threadIdx.x == 0) {
+
+    // ---- maximum over all positions, per head: local, then across the cluster --------------------
+    // entry idx of the score buffer belongs to head idx % GT; FA_THREADS is a multiple of GT, so a
+    // thread only ever sees its own head hm = threadIdx.x % GT
+    const uint32_t hm = threadIdx.x % GT;
+    float mx = -INFINITY;
+    for (uint32_t idx = threadIdx.x; idx < n_loc * GT; idx += FA_THREADS) mx = fmaxf(mx, sc[idx]);
+#pragma unroll
+    for (int o = 16; o >= GT; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if (lane < GT) sh[warp][lane] = mx;
+    __syncthreads();
+    if (threadIdx.x < GT) {
         float m = -INFINITY;
-        for (int w = 0; w < FA_WARPS; w++) m = fmaxf(m, sh[w]);
-        xch[0] = m;
+        for (int w = 0; w < FA_WARPS; w++) m = fmaxf(m, sh[w][threadIdx.x]);
+        xch[0][threadIdx.x] = m;
     }
     cluster.sync();
-    mx = -INFINITY;
-    for (uint32_t r = 0; r < S; r++) mx = fmaxf(mx, *cluster.map_shared_rank(&xch[0], r));
+    {
+        float v[8];
+        fa_gather(v, cluster, &xch[0][hm], S, -INFINITY);
+        mx = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < 8; r++) mx = fmaxf(mx, v[r]);
+    }
 
     // ---- exp and its sum: local in warp order, then across the cluster in rank order -------------
     float es = 0.0f;
-    for (uint32_t p = threadIdx.x; p < n_loc; p += FA_THREADS) {
-        const float e = expf(sc[p] - mx);
-        sc[p] = e;
+    for (uint32_t idx = threadIdx.x; idx < n_loc * GT; idx += FA_THREADS) {
+        const float e = expf(sc[idx] - mx);
+        sc[idx] = e;
         es += e;
     }
-    es = fa_warp_sum(es);
-    if (lane == 0) sh[warp] = es;
+#pragma unroll
+    for (int o = 16; o >= GT; o >>= 1) es += __shfl_xor_sync(0xFFFFFFFFu, es, o);
+    if (lane < GT) sh[warp][lane] = es;
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < GT) {
         float t = 0.0f;
-        for (int w = 0; w < FA_WARPS; w++) t += sh[w];
-        xch[1] = t;
+        for (int w = 0; w < FA_WARPS; w++) t += sh[w][threadIdx.x];
+        xch[1][threadIdx.x] = t;
     }
     cluster.sync();
-    es = 0.0f;
-    for (uint32_t r = 0; r < S; r++) es += *cluster.map_shared_rank(&xch[1], r);
-    const float inv = 1.0f / (es + 1e-10f);
+    if (threadIdx.x < GT) {
+        float v[8];
+        fa_gather(v, cluster, &xch[1][threadIdx.x], S, 0.0f);
+        float t = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; r++) t += v[r];  // rank order
+        sinv[threadIdx.x] = 1.0f / (t + 1e-10f);
+    }
+    __syncthreads();
+    float inv[GT];
+#pragma unroll
+    for (int hh = 0; hh < GT; hh++) inv[hh] = sinv[hh];
 
     // ---- weighted sum of the value rows -----------------------------------------------------------
-    float ac[VEC];
+    float ac[GT][VEC];
 #pragma unroll
-    for (int i = 0; i < VEC; i++) ac[i] = 0.0f;
-    for (uint32_t p0 = p_begin + warp; p0 < p_end; p0 += FA_INFLIGHT * FA_WARPS) {
-        Row r[FA_INFLIGHT];
-        float e[FA_INFLIGHT];
+    for (int hh = 0; hh < GT; hh++)
 #pragma unroll
-        for (int u = 0; u < FA_INFLIGHT; u++) {
-            const uint32_t p = p0 + u * FA_WARPS;
-            e[u] = 0.0f;
-            if (p < p_end) {
-                if (p != new_slot) r[u] = *reinterpret_cast<const Row *>(vcb + (size_t)p * kvd);
-                e[u] = sc[p - p_begin];
-            }
+        for (int i = 0; i < VEC; i++) ac[hh][i] = 0.0f;
+    for (uint32_t ps = 0; ps < n_pass; ps++) {
+        const uint32_t r0 = ps * PR, n = min(PR, n_loc - r0);
+        if (n_pass > 1) {                          // with one pass the value tile is still the one staged at the start
+            __syncthreads();
+            stage(r0, n, false);
+            fa_cp_wait_all();
+            __syncthreads();
         }
+#pragma unroll 2
+        for (uint32_t r = warp; r < n; r += FA_WARPS) {
+            const uint32_t p = p_begin + r0 + r;
+            const uint16_t *vrow = (p == new_slot ? newv : vt + r * hd) + lane * VEC;
+            const float *ep = sc + (size_t)(r0 + r) * GT;
+            float vf[VEC];
 #pragma unroll
-        for (int u = 0; u < FA_INFLIGHT; u++) {
-            const uint32_t p = p0 + u * FA_WARPS;
-            if (p < p_end) {
+            for (int i = 0; i < VEC; i++) vf[i] = fa_h2f(vrow[i]);
 #pragma unroll
-                for (int i = 0; i < VEC; i++) {
-                    const float vv = (p == new_slot) ? vn[i] : fa_h2f(r[u].e[i]);
-                    ac[i] += __fmul_rn(__fmul_rn(e[u], vv), inv);
-                }
+            for (int hh = 0; hh < GT; hh++) {
+                const float e = ep[hh];
+#pragma unroll
+                for (int i = 0; i < VEC; i++) ac[hh][i] += __fmul_rn(__fmul_rn(e, vf[i]), inv[hh]);
             }
         }
     }
+    __syncthreads();                               // the tiles are dead: their space takes the partial outputs
 #pragma unroll
-    for (int i = 0; i < VEC; i++) part[warp * hd + lane * VEC + i] = ac[i];
+    for (int hh = 0; hh < GT; hh++)
+#pragma unroll
+        for (int i = 0; i < VEC; i++) part[(size_t)warp * (GT * hd) + hh * hd + lane * VEC + i] = ac[hh][i];
     __syncthreads();
-    if (threadIdx.x < hd) {
-        float t = 0.0f;
+    for (uint32_t t = threadIdx.x; t < GT * hd; t += FA_THREADS) {
+        float v = 0.0f;
 #pragma unroll
-        for (uint32_t w = 0; w < (uint32_t)FA_WARPS; w++) t += part[w * hd + threadIdx.x];
-        part[threadIdx.x] = t;  // row 0: only this thread reads and writes element threadIdx.x of it
+        for (uint32_t w = 0; w < (uint32_t)FA_WARPS; w++) v += part[(size_t)w * (GT * hd) + t];
+        part[t] = v;  // row 0: only this thread reads and writes element t of it
     }
     cluster.sync();
-    if (rank == 0 && threadIdx.x < hd) {
-        float t = 0.0f;
-        for (uint32_t r = 0; r < S; r++) t += *cluster.map_shared_rank(&part[threadIdx.x], r);
-        a.out[(size_t)b * a.nh * hd + (size_t)h * hd + threadIdx.x] = fa_f2h(t);
+    // every CTA of the cluster finishes its own slice of the outputs: the partial sums of all ranks, in rank order
+    {
+        const uint32_t n_out = nhl * hd, per = (n_out + S - 1) / S;
+        const uint32_t t_end = min(n_out, (rank + 1) * per);
+        for (uint32_t t = rank * per + threadIdx.x; t < t_end; t += FA_THREADS) {
+            float v[8];
+            fa_gather(v, cluster, &part[t], S, 0.0f);
+            float o = 0.0f;
+#pragma unroll
+            for (int r = 0; r < 8; r++) o += v[r];
+            a.out[(size_t)b * a.nh * hd + (size_t)h0 * hd + t] = fa_f2h(o);
+        }
     }
-    cluster.sync();  // peers keep their shared memory alive until rank 0 has read it
+    cluster.sync();  // peers keep their shared memory alive until every rank has read it
 }
 
 bool attn_fused_eligible(const AttnArgs &a) {
@@ -236,16 +365,26 @@ bool attn_fused_eligible(const AttnArgs &a) {
            reinterpret_cast<uintptr_t>(a.k) % 16 == 0 && reinterpret_cast<uintptr_t>(a.v) % 16 == 0;
 }
 
-template <int VEC>
-static int launch_attn_fused_v(prism_cuda_ctx *ctx, const FusedAttnArgs &fa, uint32_t S, size_t smem) {
+// shared memory of a launch: the score buffer and the per-warp partial outputs
+static size_t fa_smem_bytes(uint32_t chunk_cap, uint32_t gt, uint32_t hd) {
+    // scores, rotated q, the new token's k and v, and the key/value tiles (48 KB; the per-warp partial
+    // outputs, at most 32 KB, reuse the tiles' space)
+    return (((size_t)chunk_cap * gt + 3) & ~(size_t)3) * 4 + (size_t)gt * hd * 4 + 2 * hd * 2 + 2 * (size_t)fa_tile_rows(hd) * hd * 2;
+}
+
+template <int VEC, int GT>
+static int launch_attn_fused_v(prism_cuda_ctx *ctx, const FusedAttnArgs &fa, uint32_t S) {
+    const uint32_t g = fa.nh / fa.nkv, n_tiles = (g + GT - 1) / GT;
+    const size_t smem = fa_smem_bytes(fa.chunk_cap, GT, 32 * VEC);
+    if (smem > 215 * 1024) return fail(ctx, PRISM_E_ARG, "fused attention: max_seq too large for the score buffer");
     static bool configured[PRISM_MAX_DEVICES] = {false};
     if (smem > 32 * 1024 && !configured[ctx->device]) {
-        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attn_fused_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 160 * 1024));
+        PRISM_CUDA_TRY(ctx, cudaFuncSetAttribute(attn_fused_kernel<VEC, GT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 215 * 1024));
         configured[ctx->device] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(fa.nh * S, fa.batch);
+    cfg.gridDim = dim3(fa.nkv * n_tiles * S, fa.batch);
     cfg.blockDim = dim3(FA_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
@@ -258,8 +397,42 @@ static int launch_attn_fused_v(prism_cuda_ctx *ctx, const FusedAttnArgs &fa, uin
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 2 : 1;
-    (void)cudaLaunchKernelEx(&cfg, attn_fused_kernel<VEC>, fa);
+    (void)cudaLaunchKernelEx(&cfg, attn_fused_kernel<VEC, GT>, fa);
     return after_launch(ctx, "attn_fused_kernel");
+}
+
+template <int VEC>
+static int launch_attn_fused_g(prism_cuda_ctx *ctx, const FusedAttnArgs &fa, uint32_t S) {
+    // query heads served per pass over the cache: the group size rounded up to a power of two, at
+    // most 8 (4 for 256-wide heads: registers)
+    const uint32_t g = fa.nh / fa.nkv, cap = VEC == 8 ? 4 : 8;
+    if (g >= 5 && cap >= 8) return launch_attn_fused_v<VEC, (VEC == 8 ? 4 : 8)>(ctx, fa, S);
+    if (g >= 3) return launch_attn_fused_v<VEC, 4>(ctx, fa, S);
+    if (g == 2) return launch_attn_fused_v<VEC, 2>(ctx, fa, S);
+    return launch_attn_fused_v<VEC, 1>(ctx, fa, S);
+}
+
+// The rotation frequencies base^(-2j/hd), j < hd/2, as the CPU path computes them (powf in fp32,
+// cpu_fallback.rs:137), once per (head size, base) on the host and kept on the device.
+static int rope_table(prism_cuda_ctx *ctx, uint32_t hd, float base, const float **out) {
+    for (auto *t : ctx->rope_tabs) {
+        if (t->hd == hd && t->base == base) {
+            *out = t->dev;
+            return PRISM_OK;
+        }
+    }
+    auto *t = new prism_cuda_ctx::RopeTab{hd, base, nullptr, {0}};
+    cudaError_t e = cudaMalloc((void **)&t->dev, 128 * sizeof(float));
+    if (e != cudaSuccess) {
+        delete t;
+        return cuda_fail(ctx, e, "cudaMalloc(rope table)");
+    }
+    for (uint32_t j = 0; j < hd / 2; j++) t->host[j] = powf(base, -2.0f * (float)j / (float)hd);
+    ctx->rope_tabs.push_back(t);
+    // the host copy lives as long as the context, so the asynchronous copy may read it after this returns
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(t->dev, t->host, (hd / 2) * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    *out = t->dev;
+    return PRISM_OK;
 }
 
 // q_src/k_src/v_src: this step's projection rows (src_stride halfs apart); a.k / a.v: the cache.
@@ -274,19 +447,19 @@ int launch_attn_fused(prism_cuda_ctx *ctx, const AttnArgs &a, const uint16_t *k_
     fa.pos_dev = a.pos_dev; fa.slot_mul = a.slot_mul; fa.slot_add = a.slot_add;
     fa.nh = a.nh; fa.nkv = a.nkv; fa.batch = a.batch;
     fa.seq_stride = a.seq_stride; fa.max_seq = a.max_seq;
-    fa.rope_k = rope_k; fa.rope_base = rope_base;
-    // cluster size: enough CTAs per head to keep every SM loading cache rows at long contexts
-    uint32_t S = a.max_seq >= 512 ? 8 : a.max_seq >= 256 ? 4 : a.max_seq >= 128 ? 2 : 1;
+    fa.rope_k = rope_k;
+    PRISM_TRY(rope_table(ctx, a.hd, rope_base, &fa.inv_freq));
+    // cluster size: a CTA stages up to 96 cached rows of 128-wide heads per pass; more CTAs per group
+    // spread the rows (and the latency of fetching them) over more SMs
+    uint32_t S = a.max_seq > 512 ? 8 : a.max_seq > 256 ? 4 : a.max_seq > 128 ? 2 : 1;
     if (ctx->attn_cluster == 1 || ctx->attn_cluster == 2 || ctx->attn_cluster == 4 || ctx->attn_cluster == 8)
         S = (uint32_t)ctx->attn_cluster;
     fa.chunk_cap = (a.max_seq + S - 1) / S;
-    const size_t smem = (size_t)fa.chunk_cap * sizeof(float);
-    if (smem > 160 * 1024) return fail(ctx, PRISM_E_ARG, "fused attention: max_seq too large for the score buffer");
     switch (a.hd) {
-    case 32: return launch_attn_fused_v<1>(ctx, fa, S, smem);
-    case 64: return launch_attn_fused_v<2>(ctx, fa, S, smem);
-    case 128: return launch_attn_fused_v<4>(ctx, fa, S, smem);
-    default: return launch_attn_fused_v<8>(ctx, fa, S, smem);
+    case 32: return launch_attn_fused_g<1>(ctx, fa, S);
+    case 64: return launch_attn_fused_g<2>(ctx, fa, S);
+    case 128: return launch_attn_fused_g<4>(ctx, fa, S);
+    default: return launch_attn_fused_g<8>(ctx, fa, S);
     }
 }
 

@@ -75,6 +75,7 @@ struct prism_cuda_ctx {
     int fuse = 1;
     int sk_min_chunks = 8;      // stream-K GEMV, small matrices: fewest 1 KB index chunks a CTA is given
     int sk_stream_chunks = 64;  // chunks per CTA from which the balanced contiguous partition is used
+    int cl_max_units = 8192;    // cluster GEMV for matrices of at most this many (64-row block, 1 KB chunk) units; 0: never
     int batch_gemv_max = 8;   // decode batches up to this size use the batched GEMV (groups of 8), larger ones the GEMM
     int attn_cluster = 0;    // CTAs per (head, sequence) of the fused attention kernel; 0: chosen from max_seq
     int gemm_reuse_x = 0;    // set by a caller for the second of two GEMMs over the same activations: skip the re-lay
@@ -115,8 +116,13 @@ struct prism_cuda_ctx {
     void *tp_peer_map[32] = {nullptr};   // what cudaIpcOpenMemHandle returned: [q] receive area, [16+q] flags of peer q
     size_t tp_cap = 0;                 // floats per rank slot; 0: peer path unavailable, NCCL is used
     int tp_peer_ar = 1;                // option "tp_peer_ar": use the peer-memory all-reduce when available
+    int tp_fused_ar = 1;               // option "tp_fused_ar": batch-1 decode does that all-reduce inside the GEMV kernel
     std::string tp_peer_reason;        // why the peer path is unavailable ("" when it is set up)
     bool tp_loopback = false;          // prism_cuda_tp_init_loopback: every "peer" is this GPU's own receive area
+    // rotation frequencies of the fused attention kernel (attn.cu), one table per (head size, base) ever
+    // asked for; tables live until the context is destroyed, so a captured graph's pointer stays valid
+    struct RopeTab { uint32_t hd; float base; float *dev; float host[128]; };
+    std::vector<RopeTab *> rope_tabs;
     // backend-held KV cache of the MetalBackend-style entry points (prism_cuda_kv_init / kv_append / attention_kv)
     uint16_t *kv_k = nullptr, *kv_v = nullptr;
     uint32_t kv_layers = 0, kv_dim = 0, kv_max_seq = 0;
@@ -237,12 +243,16 @@ int launch_embed(prism_cuda_ctx *ctx, const LutTensor &t, const uint32_t *tokens
                  uint16_t *out_dev, uint16_t *out2_dev);
 
 // gemv.cu
-enum GemvMode { GEMV_PLAIN = 0, GEMV_RESID = 1, GEMV_SWIGLU = 2, GEMV_F32 = 3 };
+enum GemvMode { GEMV_PLAIN = 0, GEMV_RESID = 1, GEMV_SWIGLU = 2, GEMV_F32 = 3, GEMV_TP = 4 };
 // y[b] = W x[b] for b < batch; x rows are x_stride halfs apart, y rows y_stride.
 // GEMV_RESID adds resid (same strides as y) after rounding to fp16.
 // GEMV_SWIGLU: t = gate, t2 = up, y = f16(f16(silu(f16(g))) * f16(u)).
 // GEMV_F32: y is float[batch][y_stride], the unrounded sums (partial products of a
 // K-sharded tensor-parallel rank, reduced across ranks before rounding).
+// GEMV_TP (one activation row): the same partial products, all-reduced over the tensor-parallel ranks
+// through peer memory inside the kernel and added to the residual stream y in place:
+// y = f16( f16(sum over ranks) + y )  (tp_push.cuh).  gemv_tp_ok says whether a tensor can take it.
+bool gemv_tp_ok(prism_cuda_ctx *ctx, const LutTensor &t);
 int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2,
                 const uint16_t *x, uint32_t x_stride, uint16_t *y, uint32_t y_stride,
                 const uint16_t *resid, uint32_t batch);
@@ -261,6 +271,14 @@ bool ws_preferred(prism_cuda_ctx *ctx, const LutTensor &t, bool swiglu, uint32_t
 int launch_gemv_ws(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
                    uint32_t x_stride, void *y, uint32_t y_stride, const uint16_t *resid, uint32_t batch,
                    float norm_eps);
+
+// gemv_cl.cu: small matrices -- one cluster of s CTAs per 64-row block, indices prefetched into registers
+// before the dependency wait, sums reduced through distributed shared memory.  cl_cluster_size returns
+// s, or 0 when the matrix is not one for this kernel.
+uint32_t cl_cluster_size(prism_cuda_ctx *ctx, const LutTensor &t, bool swiglu, uint32_t batch);
+int launch_gemv_cl(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const LutTensor *t2, const uint16_t *x,
+                   uint32_t x_stride, void *y, uint32_t y_stride, const uint16_t *resid, uint32_t batch, float norm_eps,
+                   uint32_t s);
 
 // gemv_wsb.cu: the warp-specialised kernel for 2..8 activation rows at once (weights streamed once);
 // the rows must already be normalised

@@ -239,7 +239,10 @@ static int enqueue_step(prism_cuda_engine *e) {
             PRISM_TRY(linear(e, GEMV_PLAIN, tv, nullptr, e->xn, H, e->v, qs, nullptr, B));
         }
         PRISM_TRY(enqueue_attention(e, l, li));
-        if (tp) {
+        if (tp && B == 1 && gemv_tp_ok(ctx, to)) {
+            // partial products, their all-reduce over the ranks and the residual add in one kernel
+            PRISM_TRY(launch_gemv(ctx, GEMV_TP, to, nullptr, e->att, e->qd_l, e->h, H, e->h, B));
+        } else if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, to, nullptr, e->att, e->qd_l, (uint16_t *)e->part, H, nullptr, B));
             PRISM_TRY(tp_reduce_add_resid(e, B * H));
         } else if (fused) {
@@ -258,7 +261,9 @@ static int enqueue_step(prism_cuda_engine *e) {
         }
         if (e->guard_skip) continue;  // DownProj skipped by the dim test (engine_impl.rs:1124-1126)
         const LutTensor &td = ctx->tensors[e->wd[l]];
-        if (tp) {
+        if (tp && B == 1 && gemv_tp_ok(ctx, td)) {
+            PRISM_TRY(launch_gemv(ctx, GEMV_TP, td, nullptr, e->act, e->act_stride, e->h, H, e->h, B));
+        } else if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, td, nullptr, e->act, e->act_stride, (uint16_t *)e->part, H, nullptr, B));
             PRISM_TRY(tp_reduce_add_resid(e, B * H));
         } else if (fused) {

@@ -442,8 +442,12 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
     // 5: stream-K kernel for every shape; 0: plain kernel
     const int v = ctx->gemv_variant;
     // 2..8 activation rows: one pass over the weights for all of them (larger batches in groups of 8)
+    if (mode == GEMV_TP && batch != 1) return fail(ctx, PRISM_E_ARG, "the in-kernel all-reduce takes one activation row");
     const bool use_wsb = (v == 1 || v == 2) && batch >= 2 && wsb_eligible(t, batch < 8 ? batch : 8);
     const bool use_tc5 = !use_wsb && v == 2 && tc5_eligible(ctx, t, batch);
+    const uint32_t cl_s = (!use_wsb && !use_tc5 && v == 1 && batch == 1) ? cl_cluster_size(ctx, t, mode == GEMV_SWIGLU, batch) : 0;
+    if (cl_s && t.k % 8 == 0 && x_stride >= t.k)
+        return launch_gemv_cl(ctx, mode, t, t2, x, x_stride, y, y_stride, resid, batch, norm_eps, cl_s);
     const bool use_ws = !use_wsb && !use_tc5 && ((v == 4 && ws_eligible(t)) ||
                                                  ((v == 1 || v == 2) && ws_preferred(ctx, t, mode == GEMV_SWIGLU, batch)));
     const bool use_sk = !use_wsb && !use_tc5 && !use_ws && (v == 1 || v == 2 || v == 5) && sk_eligible(t);
@@ -468,6 +472,8 @@ int launch_gemv(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const Lu
         }
         return PRISM_OK;
     }
+    if (mode == GEMV_TP && !(use_ws || use_sk) )
+        return fail(ctx, PRISM_E_ARG, "the in-kernel all-reduce needs the pair-table GEMV (4-bit, K % 32 == 0, gemv_variant 1, one row)");
     if (use_tc5) return launch_gemv_tc5(ctx, mode, t, t2, x, y, resid);
     if (use_ws) return launch_gemv_ws(ctx, mode, t, t2, x, x_stride, y, y_stride, resid, batch, norm_eps);
     if (use_sk) return launch_gemv_sk(ctx, mode, t, t2, x, x_stride, y, y_stride, resid, batch, norm_eps);

@@ -24,54 +24,14 @@ namespace prism {
 
 constexpr int SK_WARPS = 8;
 constexpr int SK_CTAS_PER_SM = 3;
-constexpr int SK_NACC = 2;                // independent accumulator sets (2 or 4)
 constexpr int SK_THREADS = SK_WARPS * 32;
-constexpr int SK_TBL_BYTES = 256 * 256;   // 256 entries x (2 half-blocks x 32 lanes x 4 B)
 constexpr int SK_PIECE_BYTES = SK_WARPS * 16 * 64;  // x staged at a time: 4096 halves, 8 KB (128 chunks at 4 bit, 64 at 2 bit)
 constexpr int SK_PF = 2;                 // index chunks in flight per warp (1, 2 or 4)
 constexpr int SK_KNOWN_SBASE = 1024;      // dynamic shared memory starts after the 1 KB the driver reserves
 constexpr size_t SK_SMEM_BYTES = SK_TBL_BYTES + SK_PIECE_BYTES + SK_WARPS * 64 * 4 + 32;
 
 
-// One 32-weight chunk of the two half-blocks: 8 tensor-core steps of 4 k each.  The MMA's 16 x 16
-// A operand is read as "row g = lanes 4g..4g+3, each lane two k-pairs of its own weight row"
-// (rows g: half-block 1, rows g+8: half-block 2), and B carries x[k..k+3] only where its k-rows
-// meet the column of the same lane (lanes 0, 5, 10, 15), so accumulator column n of MMA row g is
-// the dot product of lane (g, n).  x_off is the byte offset of the chunk's 64 bytes of x inside
-// the staged piece.  Lookups of word h+1 are issued before the tensor-core steps of word h; once
-// the last word's lookups are out, w1/w2 are dead and the chunk PF steps ahead is loaded into them.
-template <int SBASE, int NEXT_IMM, typename SRC>
-__device__ __forceinline__ void sk_chunk(float (&acc)[SK_NACC][4], uint4 &w1, uint4 &w2, uint4 (&xb)[2], uint32_t lane_off,
-                                         uint32_t x_off, uint32_t diag, uint32_t base, const SRC &next, bool more) {
-    sk_ldx<SBASE, SK_TBL_BYTES + 0>(xb[0], x_off, base, diag);
-    sk_ldx<SBASE, SK_TBL_BYTES + 16>(xb[1], x_off, base, diag);
-    uint32_t A0[8], A1[8];
-    sk_lookup<SBASE>(A0, w1.x, w2.x, lane_off, base);
-    sk_lookup<SBASE>(A1, w1.y, w2.y, lane_off, base);
-    constexpr int H = SK_NACC == 4 ? 2 : 0;  // second pair of accumulator sets
-    sk_mma(acc[0], A0[0], A0[1], A0[2], A0[3], xb[0].x, xb[0].y);
-    sk_mma(acc[1], A0[4], A0[5], A0[6], A0[7], xb[0].z, xb[0].w);
-    sk_ldx<SBASE, SK_TBL_BYTES + 32>(xb[0], x_off, base, diag);
-    sk_lookup<SBASE>(A0, w1.z, w2.z, lane_off, base);
-    sk_mma(acc[H + 0], A1[0], A1[1], A1[2], A1[3], xb[1].x, xb[1].y);
-    sk_mma(acc[H + 1], A1[4], A1[5], A1[6], A1[7], xb[1].z, xb[1].w);
-    sk_ldx<SBASE, SK_TBL_BYTES + 48>(xb[1], x_off, base, diag);
-    sk_lookup<SBASE>(A1, w1.w, w2.w, lane_off, base);
-    if (more) {
-        w1 = next.template load1<NEXT_IMM>();
-        w2 = next.template load2<NEXT_IMM>();
-    }
-    sk_mma(acc[0], A0[0], A0[1], A0[2], A0[3], xb[0].x, xb[0].y);
-    sk_mma(acc[1], A0[4], A0[5], A0[6], A0[7], xb[0].z, xb[0].w);
-    sk_mma(acc[H + 0], A1[0], A1[1], A1[2], A1[3], xb[1].x, xb[1].y);
-    sk_mma(acc[H + 1], A1[4], A1[5], A1[6], A1[7], xb[1].z, xb[1].w);
-}
-
 // A 2-bit chunk (64 weights per row) as two pseudo 4-bit chunks of 32 weights each.
-struct SkNoNext {
-    template <int OFF> __device__ __forceinline__ uint4 load1() const { return make_uint4(0, 0, 0, 0); }
-    template <int OFF> __device__ __forceinline__ uint4 load2() const { return make_uint4(0, 0, 0, 0); }
-};
 template <int SBASE, int NEXT_IMM, typename SRC>
 __device__ __forceinline__ void sk_chunk2(float (&acc)[SK_NACC][4], uint4 &w1, uint4 &w2, uint4 (&xb)[2], uint32_t lane_off,
                                           uint32_t x_off, uint32_t diag, uint32_t base, const SRC &next, bool more) {
@@ -348,6 +308,8 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
                     a.y[(size_t)bat * a.y_stride + row] = __half_as_ushort(__float2half_rn(s * uu));
                 }
             }
+        } else if (MODE == GEMV_TP) {
+            if (tid < 64) tp_push_reduce_halfblock(a.tp, (tid >> 5) ? hb2 : hb1, tid & 31, sum, a.m, a.y + (size_t)bat * a.y_stride, a.err);
         } else if (tid < 64) {
             const uint32_t row = ((tid >> 5) ? hb2 : hb1) * 32 + (tid & 31);
             if (MODE == GEMV_F32) {
@@ -426,6 +388,9 @@ int launch_gemv_sk(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const
     case GEMV_PLAIN: return launch_sk<GEMV_PLAIN>(ctx, a, grid, t.bits);
     case GEMV_RESID: return launch_sk<GEMV_RESID>(ctx, a, grid, t.bits);
     case GEMV_F32: return launch_sk<GEMV_F32>(ctx, a, grid, t.bits);
+    case GEMV_TP:
+        PRISM_TRY(tp_fill_push(ctx, t, &a.tp));
+        return launch_sk<GEMV_TP>(ctx, a, grid, t.bits);
     default: return launch_sk<GEMV_SWIGLU>(ctx, a, grid, t.bits);
     }
 }

@@ -68,6 +68,30 @@ __device__ __forceinline__ void ws_chunk(float (&acc)[2][4], uint4 &w1, uint4 &w
     sk_mma(acc[1], A1[4], A1[5], A1[6], A1[7], xb[1].z, xb[1].w);
 }
 
+// The pair tables of the CTA's FIRST block, built by all warps together (compute warps would
+// otherwise idle until the builders have made it: at kernel start nothing else can run yet).  Warp
+// gw of the CTA's WS_NC + WS_NB takes the (hi nibble, half-block) combinations gw, gw + 24; lane L
+// writes its own bank.  Entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]}.
+__device__ __forceinline__ void ws_first_table(const SkArgs &a, uint8_t *smem, const WsStage &st, uint32_t gw, uint32_t lane) {
+    const uint32_t hb1 = a.hb_mul * st.blk, hb2 = hb1 + a.hb_add2;
+    uint32_t *tbl = reinterpret_cast<uint32_t *>(smem + (st.seg & 1) * WS_TBL_BYTES);
+    for (uint32_t c = gw; c < 32; c += WS_NC + WS_NB) {
+        const uint32_t hi = c >> 1, h = c & 1;
+        const uint32_t row = (h == 0 ? hb1 : hb2) * 32 + lane;
+        const uint16_t *prow = (h == 0 ? a.pal1 : a.pal2) + (size_t)row * 16;
+        const uint4 p0 = *reinterpret_cast<const uint4 *>(prow);
+        const uint4 pp = *reinterpret_cast<const uint4 *>(prow + 8);
+        const uint32_t cbp[8] = {p0.x, p0.y, p0.z, p0.w, pp.x, pp.y, pp.z, pp.w};
+        const uint32_t hi_pair = reinterpret_cast<const uint32_t *>(prow)[hi >> 1];  // {pal[hi&~1], pal[hi|1]}
+        const uint32_t hsel = (hi & 1) ? 0x7600u : 0x5400u;
+#pragma unroll
+        for (int lo = 0; lo < 16; lo++) {
+            const uint32_t v = __byte_perm(cbp[lo >> 1], hi_pair, hsel | ((lo & 1) ? 0x32u : 0x10u));
+            tbl[((uint32_t)lo + 16u * hi) * 64 + h * 32 + lane] = v;
+        }
+    }
+}
+
 // ---- compute warps --------------------------------------------------------------------------------
 template <int SBASE>
 __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint32_t smem_base, uint32_t u_begin,
@@ -99,6 +123,10 @@ __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint3
         WS_LOAD(0) WS_LOAD(1) WS_LOAD(2) WS_LOAD(3)
 #undef WS_LOAD
         src.advance(WS_PF * WS_NC * 512);  // from here on: the chunk WS_PF steps ahead
+        if (t == 0) {  // with the first index chunks in flight: this warp's share of the first pair table
+            ws_first_table(a, smem, st, cw, lane);
+            __syncthreads();  // every warp of the CTA, once (the builders meet it in their first stage)
+        }
         if (st.first) {
 #pragma unroll
             for (int i = 0; i < 2; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
@@ -210,6 +238,8 @@ __device__ __forceinline__ void ws_finish(const SkArgs &a, uint8_t *smem, const 
             }
         }
         ws_bar_builders();  // fin may be rewritten by the next segment's finish
+    } else if (MODE == GEMV_TP) {
+        if (bt < 64) tp_push_reduce_halfblock(a.tp, (bt >> 5) ? hb2 : hb1, bt & 31, sum, a.m, a.y + (size_t)bat * a.y_stride, a.err);
     } else if (bt < 64) {
         const uint32_t row = ((bt >> 5) ? hb2 : hb1) * 32 + (bt & 31);
         if (MODE == GEMV_F32) {
@@ -251,7 +281,10 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
         }
         hist[xbuf] = st;
         bool staged = false;
-        if (st.first) {
+        if (t == 0) {
+            ws_first_table(a, smem, st, WS_NC + bw, lane);
+            __syncthreads();  // the whole CTA: the first table is complete
+        } else if (st.first) {
             // pair tables: entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]}; builder warp w writes the
             // entries with hi = w, w + WS_NB, ...; lane L writes its own bank.
             const uint32_t hb1 = a.hb_mul * st.blk, hb2 = hb1 + a.hb_add2;
@@ -484,6 +517,9 @@ int launch_gemv_ws(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, const
     case GEMV_PLAIN: return launch_ws<GEMV_PLAIN>(ctx, a, grid);
     case GEMV_RESID: return launch_ws<GEMV_RESID>(ctx, a, grid);
     case GEMV_F32: return launch_ws<GEMV_F32>(ctx, a, grid);
+    case GEMV_TP:
+        PRISM_TRY(tp_fill_push(ctx, t, &a.tp));
+        return launch_ws<GEMV_TP>(ctx, a, grid);
     default: return launch_ws<GEMV_SWIGLU>(ctx, a, grid);
     }
 }

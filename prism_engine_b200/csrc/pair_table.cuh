@@ -3,6 +3,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "tp_push.cuh"
 
 namespace prism {
 
@@ -63,6 +64,7 @@ struct SkArgs {
     unsigned int *err;
     uint32_t norm_n;              // > 0: stage rms_norm(x) (row of norm_n values) instead of x
     float norm_eps;
+    TpPush tp;                    // GEMV_TP only: where the all-reduce of the block sums goes
 };
 
 // Chooses between the two forms for a matrix of n_blocks x n_chunks units and `slots` resident CTA
@@ -177,6 +179,48 @@ __device__ __forceinline__ void sk_lookup(uint32_t (&A)[8], uint32_t w1, uint32_
     A[2] = sk_lds<SBASE, 0>(o11, base);   A[3] = sk_lds<SBASE, 128>(o21, base);
     A[4] = sk_lds<SBASE, 0>(o12, base);   A[5] = sk_lds<SBASE, 128>(o22, base);
     A[6] = sk_lds<SBASE, 0>(o13, base);   A[7] = sk_lds<SBASE, 128>(o23, base);
+}
+
+constexpr int SK_NACC = 2;                // independent accumulator sets of the chunk routine (2 or 4)
+constexpr int SK_TBL_BYTES = 256 * 256;   // one pair table: 256 entries x (2 half-blocks x 32 lanes x 4 B); x is staged right behind it
+
+// Stands for "no further chunk to request" where the chunk routine is used without its prefetch.
+struct SkNoNext {
+    template <int OFF> __device__ __forceinline__ uint4 load1() const { return make_uint4(0, 0, 0, 0); }
+    template <int OFF> __device__ __forceinline__ uint4 load2() const { return make_uint4(0, 0, 0, 0); }
+};
+// One 32-weight chunk of the two half-blocks: 8 tensor-core steps of 4 k each.  The MMA's 16 x 16
+// A operand is read as "row g = lanes 4g..4g+3, each lane two k-pairs of its own weight row"
+// (rows g: half-block 1, rows g+8: half-block 2), and B carries x[k..k+3] only where its k-rows
+// meet the column of the same lane (lanes 0, 5, 10, 15), so accumulator column n of MMA row g is
+// the dot product of lane (g, n).  x_off is the byte offset of the chunk's 64 bytes of x inside
+// the staged piece.  Lookups of word h+1 are issued before the tensor-core steps of word h; once
+// the last word's lookups are out, w1/w2 are dead and the chunk PF steps ahead is loaded into them.
+template <int SBASE, int NEXT_IMM, typename SRC>
+__device__ __forceinline__ void sk_chunk(float (&acc)[SK_NACC][4], uint4 &w1, uint4 &w2, uint4 (&xb)[2], uint32_t lane_off,
+                                         uint32_t x_off, uint32_t diag, uint32_t base, const SRC &next, bool more) {
+    sk_ldx<SBASE, SK_TBL_BYTES + 0>(xb[0], x_off, base, diag);
+    sk_ldx<SBASE, SK_TBL_BYTES + 16>(xb[1], x_off, base, diag);
+    uint32_t A0[8], A1[8];
+    sk_lookup<SBASE>(A0, w1.x, w2.x, lane_off, base);
+    sk_lookup<SBASE>(A1, w1.y, w2.y, lane_off, base);
+    constexpr int H = SK_NACC == 4 ? 2 : 0;  // second pair of accumulator sets
+    sk_mma(acc[0], A0[0], A0[1], A0[2], A0[3], xb[0].x, xb[0].y);
+    sk_mma(acc[1], A0[4], A0[5], A0[6], A0[7], xb[0].z, xb[0].w);
+    sk_ldx<SBASE, SK_TBL_BYTES + 32>(xb[0], x_off, base, diag);
+    sk_lookup<SBASE>(A0, w1.z, w2.z, lane_off, base);
+    sk_mma(acc[H + 0], A1[0], A1[1], A1[2], A1[3], xb[1].x, xb[1].y);
+    sk_mma(acc[H + 1], A1[4], A1[5], A1[6], A1[7], xb[1].z, xb[1].w);
+    sk_ldx<SBASE, SK_TBL_BYTES + 48>(xb[1], x_off, base, diag);
+    sk_lookup<SBASE>(A1, w1.w, w2.w, lane_off, base);
+    if (more) {
+        w1 = next.template load1<NEXT_IMM>();
+        w2 = next.template load2<NEXT_IMM>();
+    }
+    sk_mma(acc[0], A0[0], A0[1], A0[2], A0[3], xb[0].x, xb[0].y);
+    sk_mma(acc[1], A0[4], A0[5], A0[6], A0[7], xb[0].z, xb[0].w);
+    sk_mma(acc[H + 0], A1[0], A1[1], A1[2], A1[3], xb[1].x, xb[1].y);
+    sk_mma(acc[H + 1], A1[4], A1[5], A1[6], A1[7], xb[1].z, xb[1].w);
 }
 
 // ---- 2-bit indices (4-entry palette) through the same lookups ------------------------------------

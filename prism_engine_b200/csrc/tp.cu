@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "tp_push.cuh"
 
 struct prism_nccl_api {
     void *lib = nullptr;
@@ -90,10 +91,8 @@ int tp_all_gather_bytes(prism_cuda_ctx *ctx, const void *send, void *recv, size_
 // peer does only after it finished reading e.  The wait is bounded; when it gives up it sets the
 // context's error word and the step goes on with whatever arrived.
 // ---------------------------------------------------------------------------------------------
-constexpr int TP_AR_MAX_CTAS = 256;
 constexpr int TP_AR_THREADS = 256;
 constexpr size_t TP_AR_CAP_FLOATS = 256 * 1024;    // largest vector the peer path takes (1 MB per slot: batch 32 x 8192)
-constexpr unsigned int TP_AR_SPIN_LIMIT = 1u << 25;  // polls with back-off: about fifteen seconds (ranks may start seconds apart)
 
 __global__ void __launch_bounds__(TP_AR_THREADS) tp_ar_resid_kernel(const float *__restrict__ part, uint16_t *h,
                                                                     uint32_t n, void *const *peer_tab,
@@ -163,6 +162,29 @@ __global__ void __launch_bounds__(TP_AR_THREADS) tp_ar_resid_kernel(const float 
             state[0] = e;
         }
     }
+}
+
+int tp_fill_push(prism_cuda_ctx *ctx, const LutTensor &t, TpPush *out) {
+    if (ctx->tp_world <= 1 || ctx->tp_cap == 0 || !ctx->tp_peer_tab)
+        return fail(ctx, PRISM_E_STATE, "fused all-reduce: the peer-memory path is not set up" +
+                                            (ctx->tp_peer_reason.empty() ? std::string() : ": " + ctx->tp_peer_reason));
+    if (t.n_hb > (uint32_t)TP_AR_MAX_CTAS || t.m_pad > ctx->tp_cap)
+        return fail(ctx, PRISM_E_ARG, "fused all-reduce: output vector too long for the receive area");
+    out->peer_tab = (void *const *)ctx->tp_peer_tab;
+    out->recv = ctx->tp_recv;
+    out->flags = ctx->tp_flags;
+    out->state = ctx->tp_state;
+    out->world = (uint32_t)ctx->tp_world;
+    out->rank = (uint32_t)ctx->tp_rank;
+    out->cap = (uint32_t)ctx->tp_cap;
+    out->spin_limit = wait_limit(ctx, TP_AR_SPIN_LIMIT);
+    out->n_units = t.n_hb;
+    return PRISM_OK;
+}
+
+bool gemv_tp_ok(prism_cuda_ctx *ctx, const LutTensor &t) {
+    return ctx->tp_world > 1 && ctx->tp_peer_ar && ctx->tp_fused_ar && ctx->tp_cap != 0 && ctx->gemv_variant == 1 && t.bits == 4 &&
+           t.k % 32 == 0 && t.k >= 32 && t.n_hb <= (uint32_t)TP_AR_MAX_CTAS && t.m_pad <= ctx->tp_cap;
 }
 
 bool tp_peer_ar_ok(prism_cuda_ctx *ctx, size_t n) {

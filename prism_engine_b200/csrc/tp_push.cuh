@@ -1,0 +1,94 @@
+// All-reduce of a row-parallel matmul's partial sums, done inside the GEMV kernel that produces them
+// (tensor-parallel decode, one sequence).  The reference has no collective; this is the exchange step
+// of a K-sharded linear: h = f16( f16(sum over ranks of partial) + h ).
+//
+// The unit is a half-block: 32 output rows, owned by one warp of the CTA that has just completed the
+// rank's local sums for them.  That warp
+//   1. stores its 32 fp32 sums into slot [epoch & 1][this rank] of EVERY rank's receive area (plain
+//      stores over NVLink into peer memory mapped with cudaIpc*), fences at system scope and writes the
+//      epoch into flag [this rank][half-block] of every rank;
+//   2. waits (bounded) until its own flags [0..world)[half-block] hold the epoch -- the peers run the
+//      same kernel on their own K shard and complete the same rows at about the same time;
+//   3. adds the `world` partial sums in rank order (bit-identical on every rank), rounds to fp16, adds
+//      the residual and stores h.
+// Nothing waits before it has delivered, so no rank can wait for a rank that waits for it.  Two
+// slots are enough: a rank can only start all-reduce e+2 after every peer has delivered e+1, which a
+// peer does after it has finished reading e (its kernel e completes before its kernel e+1 starts).
+// The epoch lives in device memory and is advanced by the warp that finishes the last half-block, so
+// the kernel replays inside a CUDA graph.  No multimem, no TMA, no bulk copies on peer memory.
+#pragma once
+
+#include "common.cuh"
+
+namespace prism {
+
+constexpr int TP_AR_MAX_CTAS = 1024;               // flags per rank: CTAs of the stand-alone kernel, or half-blocks
+constexpr unsigned int TP_AR_SPIN_LIMIT = 1u << 25;  // polls with back-off: about fifteen seconds (ranks may start seconds apart)
+
+struct TpPush {
+    void *const *peer_tab;   // device array: world receive-area pointers, then world flag pointers; nullptr: not in use
+    float *recv;             // this rank's receive area [2][world][cap]
+    unsigned int *flags;     // this rank's flags [world][TP_AR_MAX_CTAS]
+    unsigned int *state;     // {epoch of the last completed all-reduce, half-blocks finished in the current one}
+    uint32_t world, rank, cap, spin_limit;
+    uint32_t n_units;        // half-blocks of the output vector
+};
+
+// Host side (tp.cu): fills the kernel argument from the context's peer set-up; fails when the peer path is
+// not set up or the tensor has more half-blocks than flags.
+int tp_fill_push(prism_cuda_ctx *ctx, const LutTensor &t, TpPush *out);
+
+// Called by one whole warp; lane L holds the local sum of row hb*32 + L (rows >= m carry zeros and are
+// not stored to h).  h is the residual stream, read and written in place.
+#ifdef __CUDACC__
+__device__ __forceinline__ void tp_push_reduce_halfblock(const TpPush &tp, uint32_t hb, uint32_t lane, float sum, uint32_t m,
+                                                         uint16_t *h, unsigned int *err) {
+    const unsigned int e = *reinterpret_cast<volatile unsigned int *>(tp.state) + 1;  // stable while this kernel runs
+    const uint32_t slot = e & 1, row = hb * 32 + lane;
+    // ---- deliver ----
+    for (uint32_t q = 0; q < tp.world; q++) {
+        float *dst = static_cast<float *>(tp.peer_tab[q]) + ((size_t)slot * tp.world + tp.rank) * tp.cap + row;
+        *dst = sum;
+    }
+    __threadfence_system();
+    __syncwarp();
+    if (lane < tp.world) {
+        unsigned int *f = static_cast<unsigned int *>(tp.peer_tab[tp.world + lane]) + (size_t)tp.rank * TP_AR_MAX_CTAS + hb;
+        asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(f), "r"(e) : "memory");
+    }
+    // ---- wait for the same rows of every rank (bounded: spin_limit polls, then error code 3) ----
+    if (lane < tp.world) {
+        const unsigned int *f = tp.flags + (size_t)lane * TP_AR_MAX_CTAS + hb;
+        unsigned int seen = 0, polls = 0;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(f) : "memory");
+            if ((int)(seen - e) >= 0) break;  // a peer that is already one all-reduce ahead has delivered this one too
+            if (++polls > tp.spin_limit) {
+                atomicExch(err, 3u);  // a peer did not deliver: reported by the next synchronising host call
+                break;
+            }
+            if (polls > 64) __nanosleep(polls > 4096 ? 500 : 50);
+        }
+    }
+    __syncwarp();
+    // ---- add in rank order, round, add the residual ----
+    float s = 0.0f;
+    for (uint32_t r = 0; r < tp.world; r++) s += __ldcg(tp.recv + ((size_t)slot * tp.world + r) * tp.cap + row);
+    if (row < m) {
+        const float o = __half2float(__float2half_rn(s)) + __half2float(__ushort_as_half(h[row]));
+        h[row] = __half_as_ushort(__float2half_rn(o));
+    }
+    // ---- the warp that finishes the last half-block advances the epoch ----
+    __syncwarp();
+    if (lane == 0) {
+        __threadfence();
+        if (atomicAdd(&tp.state[1], 1u) == tp.n_units - 1) {
+            tp.state[1] = 0;
+            __threadfence();
+            tp.state[0] = e;
+        }
+    }
+}
+#endif
+
+}  // namespace prism
