@@ -80,6 +80,10 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
  * "wait_limit_polls" (default 0 = built-in, about fifteen seconds: polls after which a kernel stops
  * waiting for a tensor-parallel peer or a grid-wide arrival, records a device error code and goes on;
  * the next synchronising call then returns PRISM_E_TIMEOUT and the context stays usable),
+ * "prefill_chunk" (default 512: prism_cuda_engine_generate puts up to this many prompt tokens of a sequence
+ * through the layers at once -- tensor-core GEMMs, causal attention over the cache, no LM head -- instead of
+ * one step per token as the reference's prefill_cpu does; 0 = one step per token.  Single GPU, fp16 KV),
+ * "tp_fused_ar" (0/1, default 1: batch-1 tensor-parallel decode all-reduces inside the GEMV kernel),
  * "cimage_cache" (0/1, default 0: prism_cuda_engine_load_cimage keeps the re-laid image beside the file).
  * A captured decode graph is rebuilt after any option change. */
 int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value);

@@ -270,6 +270,9 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
         ctx->tp_fused_ar = value ? 1 : 0;
     } else if (!strcmp(key, "pdl")) {
         ctx->pdl = value ? 1 : 0;
+    } else if (!strcmp(key, "prefill_chunk")) {
+        if (value < 0 || value > 65536) return fail(ctx, PRISM_E_ARG, "prefill_chunk must be in 0..65536");
+        ctx->prefill_chunk = (int)value;
     } else if (!strcmp(key, "cimage_cache")) {
         ctx->cimage_cache = value ? 1 : 0;
     } else if (!strcmp(key, "wait_limit_polls")) {

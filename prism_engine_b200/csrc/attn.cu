@@ -43,6 +43,10 @@ struct FusedAttnArgs {
     uint32_t chunk_cap;         // positions of score buffer per CTA
     uint32_t rope_k;
     const float *inv_freq;      // [hd/2] rotation frequencies base^(-2j/hd), computed once on the host
+    // Prefill: the `batch` rows are consecutive tokens of ONE sequence (cache sequence `seq`), row t at
+    // position *pos_dev + t; their keys and values are already in the cache (prefill_kv_kernel), so
+    // nothing is appended and row t attends to positions 0 .. *pos_dev + t.
+    uint32_t prefill, seq;
 };
 
 // cos / sin of the rotation of the VEC elements a lane owns (elements lane*VEC .. +VEC-1 of a head
@@ -146,9 +150,9 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
     const uint32_t h0 = kh * g + tile * GT;        // first query head of this cluster
     const uint32_t nhl = min((uint32_t)GT, g - tile * GT);
 
-    const int32_t pos = *a.pos_dev;
+    const int32_t pos = *a.pos_dev + (a.prefill ? (int32_t)b : 0);
     const int64_t slot64 = (int64_t)pos * a.slot_mul + a.slot_add;
-    const bool have_new = slot64 >= 0 && slot64 < (int64_t)a.max_seq;  // a full cache takes no new row
+    const bool have_new = !a.prefill && slot64 >= 0 && slot64 < (int64_t)a.max_seq;  // a full cache takes no new row
     uint32_t sl = (uint32_t)(slot64 + 1);
     if (slot64 < 0) sl = 0;
     if (sl > a.max_seq) sl = a.max_seq;
@@ -159,8 +163,9 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
     const uint32_t n_loc = p_end - p_begin;
     const uint32_t n_pass = (n_loc + PR - 1) / PR;
 
-    uint16_t *kcb = a.kc + (size_t)b * a.seq_stride + (size_t)kh * hd;
-    uint16_t *vcb = a.vc + (size_t)b * a.seq_stride + (size_t)kh * hd;
+    const uint32_t cseq = a.prefill ? a.seq : b;   // which sequence's cache
+    uint16_t *kcb = a.kc + (size_t)cseq * a.seq_stride + (size_t)kh * hd;
+    uint16_t *vcb = a.vc + (size_t)cseq * a.seq_stride + (size_t)kh * hd;
     constexpr uint32_t PPR = hd / 8;               // 16-byte pieces per row
     // rows [r0, r0 + n) of this CTA's range into the tiles (the new token's row comes from registers instead)
     auto stage = [&](uint32_t r0, uint32_t n, bool with_k) {
@@ -365,6 +370,40 @@ bool attn_fused_eligible(const AttnArgs &a) {
            reinterpret_cast<uintptr_t>(a.k) % 16 == 0 && reinterpret_cast<uintptr_t>(a.v) % 16 == 0;
 }
 
+// Prefill: RoPE of k (when the profile asks for it) and KVCache::append for T consecutive tokens of one
+// sequence at once -- what T decode steps would have left in the cache (rope_inplace,
+// cpu_fallback.rs:131-143; KVCache::append).  One warp per (token, kv head); rows are src_stride apart.
+template <int VEC>
+__global__ void __launch_bounds__(256) prefill_kv_kernel(const uint16_t *__restrict__ k, const uint16_t *__restrict__ v,
+                                                         uint32_t src_stride, uint16_t *kc, uint16_t *vc, uint32_t nkv,
+                                                         uint32_t n_tok, const int32_t *pos_dev, uint32_t max_seq,
+                                                         uint32_t rope_k, const float *__restrict__ inv_freq) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr uint32_t hd = 32 * VEC;
+    const uint32_t lane = threadIdx.x & 31, w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= n_tok * nkv) return;
+    const uint32_t t = w / nkv, kh = w - t * nkv;
+    const int32_t pos = *pos_dev + (int32_t)t;
+    if (pos < 0 || (uint32_t)pos >= max_seq) return;
+    const uint16_t *kr = k + (size_t)t * src_stride + (size_t)kh * hd + lane * VEC;
+    const uint16_t *vr = v + (size_t)t * src_stride + (size_t)kh * hd + lane * VEC;
+    float kn[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; i++) kn[i] = fa_h2f(kr[i]);
+    if (rope_k) {
+        float ca[VEC], sa[VEC];
+        fa_rope_angles<VEC>(ca, sa, lane, (float)pos, inv_freq);
+        fa_rope_apply<VEC>(kn, ca, sa, lane);
+    }
+    const size_t off = (size_t)pos * nkv * hd + (size_t)kh * hd + lane * VEC;
+#pragma unroll
+    for (int i = 0; i < VEC; i++) {
+        kc[off + i] = fa_f2h(kn[i]);
+        vc[off + i] = vr[i];
+    }
+}
+
 // shared memory of a launch: the score buffer and the per-warp partial outputs
 static size_t fa_smem_bytes(uint32_t chunk_cap, uint32_t gt, uint32_t hd) {
     // scores, rotated q, the new token's k and v, and the key/value tiles (48 KB; the per-warp partial
@@ -448,7 +487,24 @@ int launch_attn_fused(prism_cuda_ctx *ctx, const AttnArgs &a, const uint16_t *k_
     fa.nh = a.nh; fa.nkv = a.nkv; fa.batch = a.batch;
     fa.seq_stride = a.seq_stride; fa.max_seq = a.max_seq;
     fa.rope_k = rope_k;
+    fa.prefill = a.prefill; fa.seq = a.prefill_seq;
     PRISM_TRY(rope_table(ctx, a.hd, rope_base, &fa.inv_freq));
+    if (a.prefill) {
+        // the tokens' keys and values go to the cache first; the attention launch then finds them there
+        uint16_t *kc_seq = fa.kc + (size_t)a.prefill_seq * a.seq_stride, *vc_seq = fa.vc + (size_t)a.prefill_seq * a.seq_stride;
+        const unsigned warps = a.batch * a.nkv, blocks = (warps + 7) / 8;
+#define PRISM_PF_KV(V)                                                                                                   \
+    launch_pdl(ctx, "prefill_kv_kernel", prefill_kv_kernel<V>, dim3(blocks), dim3(256), 0, k_src, v_src, a.q_stride, kc_seq, \
+               vc_seq, a.nkv, a.batch, a.pos_dev, a.max_seq, rope_k, fa.inv_freq)
+        switch (a.hd) {
+        case 32: PRISM_PF_KV(1); break;
+        case 64: PRISM_PF_KV(2); break;
+        case 128: PRISM_PF_KV(4); break;
+        default: PRISM_PF_KV(8); break;
+        }
+#undef PRISM_PF_KV
+        PRISM_TRY(after_launch(ctx, "prefill_kv_kernel"));
+    }
     // cluster size: a CTA stages up to 96 cached rows of 128-wide heads per pass; more CTAs per group
     // spread the rows (and the latency of fetching them) over more SMs
     uint32_t S = a.max_seq > 512 ? 8 : a.max_seq > 256 ? 4 : a.max_seq > 128 ? 2 : 1;

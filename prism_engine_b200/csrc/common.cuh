@@ -80,6 +80,7 @@ struct prism_cuda_ctx {
     int attn_cluster = 0;    // CTAs per (head, sequence) of the fused attention kernel; 0: chosen from max_seq
     int gemm_reuse_x = 0;    // set by a caller for the second of two GEMMs over the same activations: skip the re-lay
     int pdl = 1;  // programmatic dependent launch between the kernels of the decode chain
+    int prefill_chunk = 512;  // prompt tokens generate() puts through the layers at once (tensor-core GEMMs); 0: one step per token
     int cimage_cache = 0;  // engine_load_cimage keeps / uses the cache of the re-laid image beside the file
     // Upper bound, in polls, of the device-side waits on something outside the waiting CTA (a peer
     // GPU's flag, a grid-wide arrival); a wait that runs out sets the device error word and the
@@ -318,6 +319,9 @@ struct AttnArgs {
     uint64_t seq_stride;    // elements (fp16) or bytes (int8) between sequences in the cache
     uint32_t int8;          // cache holds [f32 scale][kvd x i8] per position
     uint32_t max_seq;
+    // fused kernel only: the `batch` rows are consecutive prompt tokens of cache sequence prefill_seq,
+    // row t at position pos + t (causal attention over the cache after their keys/values were appended)
+    uint32_t prefill = 0, prefill_seq = 0;
 };
 int launch_attention(prism_cuda_ctx *ctx, const AttnArgs &a);
 struct KvAppendArgs {

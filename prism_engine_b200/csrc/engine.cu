@@ -48,6 +48,11 @@ struct prism_cuda_engine {
     uint32_t kv_slots = 0;       // positions a layer slot can hold
     uint32_t batch = 0, pos = 0;
     bool guard_skip = false;     // down_guard && inter != hidden
+    // batched prefill scratch (one chunk of prompt tokens of one sequence), grown on demand
+    uint16_t *pf_x = nullptr, *pf_xn = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_g = nullptr, *pf_u = nullptr,
+             *pf_act = nullptr;
+    uint32_t *pf_tok = nullptr;
+    uint32_t pf_cap = 0;         // tokens the buffers hold
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_batch = 0;
     uint64_t graph_epoch = ~0ull;  // option epoch of the context when the graph (or its eager warm-up) was made
@@ -394,6 +399,107 @@ static int run_step(prism_cuda_engine *e) {
     return PRISM_OK;
 }
 
+static int set_scalars(prism_cuda_engine *e, int32_t pos, int32_t step, int32_t record);
+
+// ---- batched prefill -------------------------------------------------------------------------------
+// The reference prefills with one step() per prompt token (prefill_cpu, engine_impl.rs:1046-1053) and
+// throws every prefill logit away; all that survives is the KV cache.  Here a chunk of T prompt tokens
+// of one sequence goes through every layer at once: the linears are T-row GEMMs on the tensor cores
+// (each row = the GEMV of that token, up to fp32 summation order), the keys and values of the T tokens
+// are rotated and appended together, token t attends causally to positions 0 .. pos0 + t, and the LM
+// head is skipped.  Rounding points are those of step(): fp16 after every matmul, norm, residual add,
+// SiLU and gate*up product.
+static bool prefill_batched_ok(prism_cuda_engine *e) {
+    prism_cuda_ctx *ctx = e->ctx;
+    const prism_model_config &c = e->cfg;
+    if (ctx->prefill_chunk <= 0 || e->T != 1 || c.kv_int8 || e->guard_skip || !ctx->fuse) return false;
+    if (!(e->hd == 32 || e->hd == 64 || e->hd == 128 || e->hd == 256)) return false;
+    for (uint32_t l = 0; l < c.num_layers; l++)
+        if (e->wqkv[l] < 0 || ctx->tensors[e->wqkv[l]].m % 8) return false;
+    return e->I_l % 8 == 0 && e->H % 8 == 0 && e->qd_l % 8 == 0;
+}
+
+static int ensure_prefill(prism_cuda_engine *e, uint32_t T) {
+    if (T <= e->pf_cap) return PRISM_OK;
+    prism_cuda_ctx *ctx = e->ctx;
+    PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    void **ptrs[] = {(void **)&e->pf_x, (void **)&e->pf_xn, (void **)&e->pf_qkv, (void **)&e->pf_att, (void **)&e->pf_g,
+                     (void **)&e->pf_u, (void **)&e->pf_act, (void **)&e->pf_tok};
+    for (void **p : ptrs) {
+        cudaFree(*p);
+        *p = nullptr;
+    }
+    e->pf_cap = 0;
+    const uint32_t wq = e->qd_l + 2 * e->kvd_l;
+    const size_t wide = std::max<size_t>(e->I_l, e->H);
+    const size_t bytes[] = {(size_t)T * e->H * 2, (size_t)T * e->H * 2, (size_t)T * wq * 2, (size_t)T * e->qd_l * 2,
+                            (size_t)T * wide * 2, (size_t)T * wide * 2, (size_t)T * wide * 2, (size_t)T * 4};
+    for (size_t i = 0; i < sizeof(ptrs) / sizeof(ptrs[0]); i++) {
+        cudaError_t ce = cudaMalloc(ptrs[i], (bytes[i] + 255) / 256 * 256);
+        if (ce != cudaSuccess) return cuda_fail(ctx, ce, "cudaMalloc(prefill scratch)");
+    }
+    e->pf_cap = T;
+    return PRISM_OK;
+}
+
+// Prompt tokens [pos0, pos0 + T) of sequence b (device array `toks`, contiguous) through all layers.
+static int prefill_chunk(prism_cuda_engine *e, uint32_t b, uint32_t pos0, uint32_t T, const uint32_t *toks) {
+    prism_cuda_ctx *ctx = e->ctx;
+    const prism_model_config &c = e->cfg;
+    const uint32_t H = e->H, I = e->I_l, wq = e->qd_l + 2 * e->kvd_l;
+    const float base = c.rope_use_theta ? c.rope_theta : 10000.0f;
+    PRISM_TRY(set_scalars(e, (int32_t)pos0, 0, 0));
+    PRISM_TRY(launch_embed(ctx, ctx->tensors[e->embed], toks, T, e->pf_x, nullptr));
+    for (uint32_t l = 0; l < c.num_layers; l++) {
+        const LutTensor &tqkv = ctx->tensors[e->wqkv[l]], &to = ctx->tensors[e->wo[l]], &tg = ctx->tensors[e->wg[l]],
+                        &tu = ctx->tensors[e->wu[l]], &td = ctx->tensors[e->wd[l]];
+        PRISM_TRY(launch_rms_norm(ctx, e->pf_x, e->pf_xn, H, c.norm_eps, T));
+        PRISM_TRY(launch_gemm(ctx, tqkv, e->pf_xn, T, e->pf_qkv));
+        AttnArgs aa{};
+        aa.q = e->pf_qkv; aa.q_stride = wq;
+        aa.k = (char *)e->kc + (size_t)l * e->kv_layer_bytes;
+        aa.v = (char *)e->vc + (size_t)l * e->kv_layer_bytes;
+        aa.out = e->pf_att;
+        aa.pos_dev = e->scalars; aa.slot_mul = 1; aa.slot_add = 0;
+        aa.nh = e->nh_l; aa.nkv = e->nkv_l; aa.hd = e->hd; aa.batch = T;
+        aa.seq_stride = e->kv_seq_stride; aa.int8 = 0; aa.max_seq = e->kv_slots;
+        aa.prefill = 1; aa.prefill_seq = b;
+        PRISM_TRY(launch_attn_fused(ctx, aa, e->pf_qkv + e->qd_l, e->pf_qkv + e->qd_l + e->kvd_l, c.rope_k, base));
+        PRISM_TRY(launch_gemm(ctx, to, e->pf_att, T, e->pf_g));
+        PRISM_TRY(launch_vec_add(ctx, e->pf_x, e->pf_g, T * H));            // h = f16(o + hr)
+        PRISM_TRY(launch_rms_norm(ctx, e->pf_x, e->pf_xn, H, c.norm_eps, T));
+        PRISM_TRY(launch_gemm(ctx, tg, e->pf_xn, T, e->pf_g));
+        ctx->gemm_reuse_x = 1;  // same activations, same token tile: the re-laid copy is still in scratch
+        const int rc_up = launch_gemm(ctx, tu, e->pf_xn, T, e->pf_u);
+        ctx->gemm_reuse_x = 0;
+        PRISM_TRY(rc_up);
+        PRISM_TRY(launch_silu_mul(ctx, e->pf_act, e->pf_g, e->pf_u, T * I));
+        PRISM_TRY(launch_gemm(ctx, td, e->pf_act, T, e->pf_g));
+        PRISM_TRY(launch_vec_add(ctx, e->pf_x, e->pf_g, T * H));            // h = f16(d + hr)
+    }
+    return PRISM_OK;
+}
+
+// All prompts of a generate call; e->prompts holds them position-major ([position][sequence]).
+static int prefill_batched(prism_cuda_engine *e, uint32_t batch, uint32_t n_prompt) {
+    prism_cuda_ctx *ctx = e->ctx;
+    const uint32_t chunk = std::min<uint32_t>((uint32_t)ctx->prefill_chunk, n_prompt);
+    PRISM_TRY(ensure_prefill(e, chunk));
+    for (uint32_t b = 0; b < batch; b++) {
+        for (uint32_t p0 = 0; p0 < n_prompt; p0 += chunk) {
+            const uint32_t T = std::min(chunk, n_prompt - p0);
+            // this sequence's tokens of the chunk, made contiguous
+            PRISM_CUDA_TRY(ctx, cudaMemcpy2DAsync(e->pf_tok, 4, e->prompts + (size_t)p0 * batch + b, (size_t)batch * 4, 4, T,
+                                                  cudaMemcpyDeviceToDevice, ctx->stream));
+            PRISM_TRY(prefill_chunk(e, b, p0, T, e->pf_tok));
+        }
+    }
+    // the first decode step feeds the last prompt token again, at position n_prompt (engine_impl.rs:1015, 1034)
+    PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->tok, e->prompts + (size_t)(n_prompt - 1) * batch, (size_t)batch * 4,
+                                        cudaMemcpyDeviceToDevice, ctx->stream));
+    return set_scalars(e, (int32_t)n_prompt, 0, 0);
+}
+
 static int set_scalars(prism_cuda_engine *e, int32_t pos, int32_t step, int32_t record) {
     int32_t v[3] = {pos, step, record};
     // pageable source: the copy is complete on return, `v` may go out of scope
@@ -510,7 +616,7 @@ void prism_cuda_engine_destroy(prism_cuda_engine *e) {
     if (e->graph) cudaGraphExecDestroy(e->graph);
     for (int32_t h : e->wqkv)
         if (h >= 0) prism_cuda_free_tensor(e->ctx, h);
-    void *ptrs[] = {e->gu, e->h, e->xn, e->qkv, e->att, e->act, e->logits, e->part, e->tok, e->next,
+    void *ptrs[] = {e->pf_x, e->pf_xn, e->pf_qkv, e->pf_att, e->pf_g, e->pf_u, e->pf_act, e->pf_tok, e->gu, e->h, e->xn, e->qkv, e->att, e->act, e->logits, e->part, e->tok, e->next,
                     e->out_tokens, e->prompts, e->pairs_send, e->pairs_recv, e->scalars, e->kc, e->vc};
     for (void *p : ptrs) cudaFree(p);
     if (e->ev0) cudaEventDestroy(e->ev0);
@@ -707,11 +813,15 @@ int prism_cuda_engine_generate(prism_cuda_engine *e, const uint32_t *prompts, ui
     PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->prompts, tr.data(), need * 4, cudaMemcpyHostToDevice, ctx->stream));
     PRISM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     PRISM_CUDA_TRY(ctx, cudaEventRecord(e->ev0, ctx->stream));
-    // prefill_cpu (engine_impl.rs:1046-1053): one step per prompt token
-    for (uint32_t i = 0; i < n_prompt; i++) {
-        PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->tok, e->prompts + (size_t)i * batch, (size_t)batch * 4,
-                                            cudaMemcpyDeviceToDevice, ctx->stream));
-        PRISM_TRY(run_step(e));
+    if (n_prompt >= 2 && prefill_batched_ok(e)) {
+        PRISM_TRY(prefill_batched(e, batch, n_prompt));
+    } else {
+        // prefill_cpu (engine_impl.rs:1046-1053): one step per prompt token
+        for (uint32_t i = 0; i < n_prompt; i++) {
+            PRISM_CUDA_TRY(ctx, cudaMemcpyAsync(e->tok, e->prompts + (size_t)i * batch, (size_t)batch * 4,
+                                                cudaMemcpyDeviceToDevice, ctx->stream));
+            PRISM_TRY(run_step(e));
+        }
     }
     e->pos = n_prompt;
     // decode: `nt = *prompt.last().unwrap_or(&0)` (engine_impl.rs:1015) is fed first

@@ -176,6 +176,29 @@ def test_batched_decode_matches_the_oracle(oracle, batch_gemv_max, batch):
     eng.close(); twin.close(); be.close()
 
 
+@pytest.mark.parametrize("chunk", [512, 16, 0])
+def test_batched_prefill_matches_the_oracle(oracle, chunk):
+    """generate() puts the prompt through the layers in chunks of `prefill_chunk` tokens (tensor-core GEMMs, causal
+    attention over the cache); 0 is the reference's one step per prompt token.  All must continue with the oracle's tokens."""
+    cfg = dict(num_layers=3, hidden_size=256, num_heads=8, num_kv_heads=2, head_dim=32, intermediate_size=640,
+               vocab_size=2048, norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+    be = p.CudaBackend(device=0)
+    be.set_option("prefill_chunk", chunk)
+    mc = p.model_config(**cfg, max_seq=128, max_batch=3, profile="baseline")
+    eng = p.PrismEngine(be, mc)
+    eng.synth_weights(seed=17)
+    prompts = np.stack([synth.make_prompt(41, cfg["vocab_size"], seed=s) for s in range(3)])
+    l0 = be.launch_count()
+    got = eng.generate(prompts, 33)
+    n_launch = be.launch_count() - l0
+    twin = oracle_twin(oracle, be, cfg, mc)
+    for b in range(3):
+        want, margins = twin.generate(prompts[b], 33)
+        assert np.array_equal(got[b][:32], want[:32]), (chunk, b, float(margins.min()))
+    print("prefill_chunk", chunk, "launches", n_launch)
+    eng.close(); twin.close(); be.close()
+
+
 @pytest.mark.timeout(1500)
 def test_qwen25_0p5b_first_32_tokens(oracle):
     """The 0.5B-architecture model of the benchmark configuration: identical greedy tokens for 32 steps."""

@@ -24,7 +24,7 @@ WIDE = dict(num_layers=2, hidden_size=8192, num_heads=64, num_kv_heads=8, head_d
             vocab_size=152064, norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
 
 
-def _worker(rank, world, port, q, peer_ar, wide=False):
+def _worker(rank, world, port, q, peer_ar, wide=False, batch=2):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -46,7 +46,8 @@ def _worker(rank, world, port, q, peer_ar, wide=False):
         max_seq, n_new = (512, 33) if wide else (64, 33)
         eng = p.PrismEngine(be, p.model_config(**cfg, max_seq=max_seq, max_batch=2, profile="baseline"))
         eng.synth_weights(seed=21)
-        prompts = np.stack([synth.make_prompt(7, cfg["vocab_size"], seed=s) for s in (1, 2)])
+        # one sequence: the row-parallel matmuls all-reduce inside the GEMV kernel; two: through the stand-alone kernel
+        prompts = np.stack([synth.make_prompt(7, cfg["vocab_size"], seed=s) for s in (1, 2)[:batch]])
         got = eng.generate(prompts, n_new)
         eng.close()
         be.close()
@@ -62,7 +63,7 @@ def _worker(rank, world, port, q, peer_ar, wide=False):
             want = ref.generate(prompts, n_new)
             twin = oracle_twin(orc, ref_be, cfg, mc, threads=orc.max_threads())
             msg = "ok" if np.array_equal(got, want) else f"tokens differ from one GPU: {got.tolist()} vs {want.tolist()}"
-            for b in (0, 1):
+            for b in range(batch):
                 w, margins = twin.generate(prompts[b], n_new)
                 if not np.array_equal(got[b][:32], w[:32]):
                     msg = f"sequence {b} differs from the oracle: {got[b].tolist()} vs {w.tolist()} (min margin {float(margins.min()):.5f})"
@@ -79,8 +80,8 @@ def _worker(rank, world, port, q, peer_ar, wide=False):
 
 
 @pytest.mark.timeout(1500)
-@pytest.mark.parametrize("peer_ar,wide", [(1, False), (0, False), (1, True)])
-def test_tp2_matches_single_gpu_and_oracle(peer_ar, wide):
+@pytest.mark.parametrize("peer_ar,wide,batch", [(1, False, 2), (0, False, 2), (1, False, 1), (0, False, 1), (1, True, 1)])
+def test_tp2_matches_single_gpu_and_oracle(peer_ar, wide, batch):
     import torch
 
     if torch.cuda.device_count() < 2:
@@ -89,8 +90,8 @@ def test_tp2_matches_single_gpu_and_oracle(peer_ar, wide):
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + os.getpid() % 1000 + peer_ar + 2 * int(wide)
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peer_ar, wide)) for r in range(2)]
+    port = 29700 + os.getpid() % 1000 + peer_ar + 2 * int(wide) + 4 * batch
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peer_ar, wide, batch)) for r in range(2)]
     for pr in procs:
         pr.start()
     res = [q.get(timeout=1200) for _ in procs]
