@@ -282,6 +282,12 @@ typedef struct prism_model_config {
     uint32_t kv_int8;        /* 1: int8 + f32 scale per token (engine_impl.rs:516-567) */
     uint32_t down_guard;     /* 1: keep the dim test at engine_impl.rs:1124-1126 that skips
                                 DownProj when intermediate_size != hidden_size */
+    /* Paged KV cache (not in the reference, whose KVCache is one Vec per layer, engine_impl.rs:514-530):
+     * kv_page_size > 0 (a power of two >= 16) keeps the fp16 cache of every layer as a pool of pages of
+     * that many positions, handed to sequences as they grow; kv_pool_pages sizes the pool (0 = enough for
+     * max_batch sequences of max_seq positions).  A pool smaller than that serves more or longer
+     * sequences than a slab per sequence could, until it runs out (PRISM_E_STATE).  fp16 cache only. */
+    uint32_t kv_page_size, kv_pool_pages;
 } prism_model_config;
 
 /* Tensor roles of TensorRole (src/lut/graph.rs) as used by step(). */

@@ -32,7 +32,7 @@ class ModelConfig(C.Structure):
         ("vocab_size", C.c_uint32), ("norm_eps", C.c_float), ("rope_theta", C.c_float),
         ("tie_word_embeddings", C.c_uint32), ("bits", C.c_uint32), ("max_seq", C.c_uint32),
         ("max_batch", C.c_uint32), ("rope_use_theta", C.c_uint32), ("rope_k", C.c_uint32),
-        ("kv_int8", C.c_uint32), ("down_guard", C.c_uint32),
+        ("kv_int8", C.c_uint32), ("down_guard", C.c_uint32), ("kv_page_size", C.c_uint32), ("kv_pool_pages", C.c_uint32),
     ]
 
 

@@ -357,7 +357,7 @@ class CudaBackend:
 
 def model_config(num_layers, hidden_size, num_heads, num_kv_heads, head_dim, intermediate_size, vocab_size,
                  norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True, bits=4, max_seq=4096, max_batch=1,
-                 profile="baseline") -> ModelConfig:
+                 profile="baseline", kv_page_size=0, kv_pool_pages=0) -> ModelConfig:
     """``profile``: "reference_cpu" keeps every behaviour of the reference's CPU path (RoPE base
     10000 on q only, int8 KV, the DownProj dim test); "baseline" is the configuration the
     benchmarks name (rope_theta from the config on q and k, fp16 KV, DownProj runs)."""
@@ -366,7 +366,7 @@ def model_config(num_layers, hidden_size, num_heads, num_kv_heads, head_dim, int
         raise ValueError(profile)
     return ModelConfig(num_layers, hidden_size, num_heads, num_kv_heads, head_dim, intermediate_size, vocab_size,
                        norm_eps, rope_theta, int(tie_word_embeddings), bits, max_seq, max_batch,
-                       0 if ref else 1, 0 if ref else 1, 1 if ref else 0, 1 if ref else 0)
+                       0 if ref else 1, 0 if ref else 1, 1 if ref else 0, 1 if ref else 0, kv_page_size, kv_pool_pages)
 
 
 QWEN25_0P5B = dict(num_layers=24, hidden_size=896, num_heads=14, num_kv_heads=2, head_dim=64,

@@ -47,7 +47,19 @@ struct FusedAttnArgs {
     // position *pos_dev + t; their keys and values are already in the cache (prefill_kv_kernel), so
     // nothing is appended and row t attends to positions 0 .. *pos_dev + t.
     uint32_t prefill, seq;
+    // Paged cache: position p of cache sequence c lives in row (page_tbl[c*tbl_stride + (p >> page_shift)]
+    // << page_shift) + (p & (page - 1)) of the layer's page pool; nullptr: one contiguous slab per sequence.
+    const int32_t *page_tbl;
+    uint32_t page_shift, tbl_stride;
 };
+
+// Row (in units of cached rows of the layer) of position p of cache sequence c.
+__device__ __forceinline__ size_t fa_row(const int32_t *__restrict__ tbl, uint32_t shift, uint32_t tbl_stride, uint64_t seq_rows,
+                                         uint32_t c, uint32_t p) {
+    if (tbl == nullptr) return (size_t)c * seq_rows + p;
+    const uint32_t page = (uint32_t)__ldg(tbl + (size_t)c * tbl_stride + (p >> shift));
+    return ((size_t)page << shift) + (p & ((1u << shift) - 1u));
+}
 
 // cos / sin of the rotation of the VEC elements a lane owns (elements lane*VEC .. +VEC-1 of a head
 // of 32*VEC): the angle depends on the position and the pair index only, so it is computed once
@@ -164,16 +176,19 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
     const uint32_t n_pass = (n_loc + PR - 1) / PR;
 
     const uint32_t cseq = a.prefill ? a.seq : b;   // which sequence's cache
-    uint16_t *kcb = a.kc + (size_t)cseq * a.seq_stride + (size_t)kh * hd;
-    uint16_t *vcb = a.vc + (size_t)cseq * a.seq_stride + (size_t)kh * hd;
+    uint16_t *kcb = a.kc + (size_t)kh * hd;
+    uint16_t *vcb = a.vc + (size_t)kh * hd;
+    const uint64_t seq_rows = a.seq_stride / kvd;  // rows of a sequence's slab (contiguous cache)
+    auto row_of = [&](uint32_t p) { return fa_row(a.page_tbl, a.page_shift, a.tbl_stride, seq_rows, cseq, p) * kvd; };
     constexpr uint32_t PPR = hd / 8;               // 16-byte pieces per row
     // rows [r0, r0 + n) of this CTA's range into the tiles (the new token's row comes from registers instead)
     auto stage = [&](uint32_t r0, uint32_t n, bool with_k) {
         for (uint32_t i = threadIdx.x; i < n * PPR; i += FA_THREADS) {
             const uint32_t r = i / PPR, c = i - r * PPR, p = p_begin + r0 + r;
             if (p == new_slot) continue;
-            if (with_k) fa_cp16(kt + r * hd + c * 8, kcb + (size_t)p * kvd + c * 8);
-            fa_cp16(vt + r * hd + c * 8, vcb + (size_t)p * kvd + c * 8);
+            const size_t ro = row_of(p);
+            if (with_k) fa_cp16(kt + r * hd + c * 8, kcb + ro + c * 8);
+            fa_cp16(vt + r * hd + c * 8, vcb + ro + c * 8);
         }
     };
     stage(0, min(n_loc, PR), true);                // requested before anything else is computed
@@ -199,6 +214,7 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
             for (int i = 0; i < VEC; i++) kn[i] = fa_h2f(k[i]);
             if (a.rope_k) fa_rope_apply<VEC>(kn, ca, sa, lane);
             const bool own_new = have_new && new_slot >= p_begin && new_slot < p_end;
+            const size_t new_off = (own_new && tile == 0) ? row_of(new_slot) : 0;
 #pragma unroll
             for (int i = 0; i < VEC; i++) {
                 const uint16_t kb = fa_f2h(kn[i]), vb = v[i];
@@ -206,8 +222,8 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
                 newv[lane * VEC + i] = vb;
                 // KVCache::append: the first head tile of a group stores the row for all later steps
                 if (own_new && tile == 0) {
-                    kcb[(size_t)new_slot * kvd + lane * VEC + i] = kb;
-                    vcb[(size_t)new_slot * kvd + lane * VEC + i] = vb;
+                    kcb[new_off + lane * VEC + i] = kb;
+                    vcb[new_off + lane * VEC + i] = vb;
                 }
             }
         }
@@ -377,7 +393,9 @@ template <int VEC>
 __global__ void __launch_bounds__(256) prefill_kv_kernel(const uint16_t *__restrict__ k, const uint16_t *__restrict__ v,
                                                          uint32_t src_stride, uint16_t *kc, uint16_t *vc, uint32_t nkv,
                                                          uint32_t n_tok, const int32_t *pos_dev, uint32_t max_seq,
-                                                         uint32_t rope_k, const float *__restrict__ inv_freq) {
+                                                         uint32_t rope_k, const float *__restrict__ inv_freq,
+                                                         const int32_t *__restrict__ page_tbl, uint32_t page_shift,
+                                                         uint32_t tbl_stride, uint64_t seq_rows, uint32_t seq) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr uint32_t hd = 32 * VEC;
@@ -396,7 +414,7 @@ __global__ void __launch_bounds__(256) prefill_kv_kernel(const uint16_t *__restr
         fa_rope_angles<VEC>(ca, sa, lane, (float)pos, inv_freq);
         fa_rope_apply<VEC>(kn, ca, sa, lane);
     }
-    const size_t off = (size_t)pos * nkv * hd + (size_t)kh * hd + lane * VEC;
+    const size_t off = fa_row(page_tbl, page_shift, tbl_stride, seq_rows, seq, (uint32_t)pos) * nkv * hd + (size_t)kh * hd + lane * VEC;
 #pragma unroll
     for (int i = 0; i < VEC; i++) {
         kc[off + i] = fa_f2h(kn[i]);
@@ -488,14 +506,16 @@ int launch_attn_fused(prism_cuda_ctx *ctx, const AttnArgs &a, const uint16_t *k_
     fa.seq_stride = a.seq_stride; fa.max_seq = a.max_seq;
     fa.rope_k = rope_k;
     fa.prefill = a.prefill; fa.seq = a.prefill_seq;
+    fa.page_tbl = a.page_tbl; fa.page_shift = a.page_shift; fa.tbl_stride = a.tbl_stride;
     PRISM_TRY(rope_table(ctx, a.hd, rope_base, &fa.inv_freq));
     if (a.prefill) {
         // the tokens' keys and values go to the cache first; the attention launch then finds them there
-        uint16_t *kc_seq = fa.kc + (size_t)a.prefill_seq * a.seq_stride, *vc_seq = fa.vc + (size_t)a.prefill_seq * a.seq_stride;
         const unsigned warps = a.batch * a.nkv, blocks = (warps + 7) / 8;
-#define PRISM_PF_KV(V)                                                                                                   \
-    launch_pdl(ctx, "prefill_kv_kernel", prefill_kv_kernel<V>, dim3(blocks), dim3(256), 0, k_src, v_src, a.q_stride, kc_seq, \
-               vc_seq, a.nkv, a.batch, a.pos_dev, a.max_seq, rope_k, fa.inv_freq)
+        const uint64_t seq_rows = a.seq_stride / (a.nkv * a.hd);
+#define PRISM_PF_KV(V)                                                                                                  \
+    launch_pdl(ctx, "prefill_kv_kernel", prefill_kv_kernel<V>, dim3(blocks), dim3(256), 0, k_src, v_src, a.q_stride, fa.kc, \
+               fa.vc, a.nkv, a.batch, a.pos_dev, a.max_seq, rope_k, fa.inv_freq, a.page_tbl, a.page_shift, a.tbl_stride,  \
+               seq_rows, a.prefill_seq)
         switch (a.hd) {
         case 32: PRISM_PF_KV(1); break;
         case 64: PRISM_PF_KV(2); break;

@@ -117,7 +117,10 @@ struct prism_cuda_ctx {
     void *tp_peer_map[32] = {nullptr};   // what cudaIpcOpenMemHandle returned: [q] receive area, [16+q] flags of peer q
     size_t tp_cap = 0;                 // floats per rank slot; 0: peer path unavailable, NCCL is used
     int tp_peer_ar = 1;                // option "tp_peer_ar": use the peer-memory all-reduce when available
-    int tp_fused_ar = 1;               // option "tp_fused_ar": batch-1 decode does that all-reduce inside the GEMV kernel
+    // option "tp_fused_ar" (batch-1 decode): 0 = GEMV writes fp32 partial sums, a separate kernel pushes and reduces them;
+    // 1 = the GEMV epilogue stores its sums straight into every rank's receive area, a small kernel publishes flags and
+    // reduces; 2 = flags, wait and reduction inside the GEMV kernel too
+    int tp_fused_ar = 1;
     std::string tp_peer_reason;        // why the peer path is unavailable ("" when it is set up)
     bool tp_loopback = false;          // prism_cuda_tp_init_loopback: every "peer" is this GPU's own receive area
     // rotation frequencies of the fused attention kernel (attn.cu), one table per (head size, base) ever
@@ -217,6 +220,8 @@ int tp_all_gather_bytes(prism_cuda_ctx *ctx, const void *send, void *recv, size_
 // matmul's fp32 partial sums fused with the residual add, through peer memory (one kernel, no NCCL).
 bool tp_peer_ar_ok(prism_cuda_ctx *ctx, size_t n);
 int tp_all_reduce_resid_peer(prism_cuda_ctx *ctx, const float *part, uint16_t *h, size_t n);
+// the same after a GEMV_TP kernel that only delivered (option tp_fused_ar = 1): flags, wait, reduction, residual
+int tp_all_reduce_flags_resid(prism_cuda_ctx *ctx, uint16_t *h, size_t n);
 // Synchronises the stream and reads the device error word.  Codes kernels leave there:
 //   1  a kernel found its shared-memory layout assumption broken and refused to run  -> PRISM_E_STATE
 //   2  an mbarrier hand-over inside a warp-specialised GEMV gave up                    -> PRISM_E_TIMEOUT
@@ -322,6 +327,9 @@ struct AttnArgs {
     // fused kernel only: the `batch` rows are consecutive prompt tokens of cache sequence prefill_seq,
     // row t at position pos + t (causal attention over the cache after their keys/values were appended)
     uint32_t prefill = 0, prefill_seq = 0;
+    // fused kernel only: paged cache (page table on the device, [sequence][tbl_stride] page numbers of 2^page_shift rows)
+    const int32_t *page_tbl = nullptr;
+    uint32_t page_shift = 0, tbl_stride = 0;
 };
 int launch_attention(prism_cuda_ctx *ctx, const AttnArgs &a);
 struct KvAppendArgs {

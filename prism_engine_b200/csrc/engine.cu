@@ -48,6 +48,11 @@ struct prism_cuda_engine {
     uint32_t kv_slots = 0;       // positions a layer slot can hold
     uint32_t batch = 0, pos = 0;
     bool guard_skip = false;     // down_guard && inter != hidden
+    // paged KV cache (cfg.kv_page_size > 0): page table on the device and its host mirror, free pages
+    int32_t *page_tbl = nullptr;             // [max_batch][pages_per_seq]
+    std::vector<int32_t> page_tbl_host, free_pages;
+    std::vector<uint32_t> seq_pages;         // pages each sequence holds
+    uint32_t page_shift = 0, pages_per_seq = 0, pool_pages = 0;
     // batched prefill scratch (one chunk of prompt tokens of one sequence), grown on demand
     uint16_t *pf_x = nullptr, *pf_xn = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_g = nullptr, *pf_u = nullptr,
              *pf_act = nullptr;
@@ -209,7 +214,9 @@ static int enqueue_attention(prism_cuda_engine *e, uint32_t l, uint32_t li) {
     aa.pos_dev = pos_dev; aa.slot_mul = slot_mul; aa.slot_add = slot_add;
     aa.nh = e->nh_l; aa.nkv = e->nkv_l; aa.hd = e->hd; aa.batch = B;
     aa.seq_stride = e->kv_seq_stride; aa.int8 = c.kv_int8; aa.max_seq = e->kv_slots;
+    aa.page_tbl = e->page_tbl; aa.page_shift = e->page_shift; aa.tbl_stride = e->pages_per_seq;
     if (ctx->fuse != 0 && attn_fused_eligible(aa)) return launch_attn_fused(ctx, aa, e->k, e->v, c.rope_k, base);
+    if (e->page_tbl) return fail(ctx, PRISM_E_STATE, "the paged KV cache needs the fused attention kernel (option fuse = 1)");
     if (c.rope_k) PRISM_TRY(launch_rope(ctx, e->k, e->kvd_l, pos_dev, 0, e->hd, base, B, qs));
     PRISM_TRY(launch_kv_append(ctx, ka));
     PRISM_TRY(launch_rope(ctx, e->q, e->qd_l, pos_dev, 0, e->hd, base, B, qs));
@@ -247,6 +254,7 @@ static int enqueue_step(prism_cuda_engine *e) {
         if (tp && B == 1 && gemv_tp_ok(ctx, to)) {
             // partial products, their all-reduce over the ranks and the residual add in one kernel
             PRISM_TRY(launch_gemv(ctx, GEMV_TP, to, nullptr, e->att, e->qd_l, e->h, H, e->h, B));
+            if (ctx->tp_fused_ar == 1) PRISM_TRY(tp_all_reduce_flags_resid(ctx, e->h, H));
         } else if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, to, nullptr, e->att, e->qd_l, (uint16_t *)e->part, H, nullptr, B));
             PRISM_TRY(tp_reduce_add_resid(e, B * H));
@@ -268,6 +276,7 @@ static int enqueue_step(prism_cuda_engine *e) {
         const LutTensor &td = ctx->tensors[e->wd[l]];
         if (tp && B == 1 && gemv_tp_ok(ctx, td)) {
             PRISM_TRY(launch_gemv(ctx, GEMV_TP, td, nullptr, e->act, e->act_stride, e->h, H, e->h, B));
+            if (ctx->tp_fused_ar == 1) PRISM_TRY(tp_all_reduce_flags_resid(ctx, e->h, H));
         } else if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, td, nullptr, e->act, e->act_stride, (uint16_t *)e->part, H, nullptr, B));
             PRISM_TRY(tp_reduce_add_resid(e, B * H));
@@ -345,11 +354,42 @@ static int check_bound(prism_cuda_engine *e) {
     return PRISM_OK;
 }
 
+// Paged cache: every sequence of the current batch gets the pages its first `upto` positions need.
+static int ensure_pages(prism_cuda_engine *e, uint32_t upto) {
+    if (!e->page_tbl) return PRISM_OK;
+    const uint32_t P = 1u << e->page_shift, need = (upto + P - 1) / P;
+    bool changed = false;
+    for (uint32_t b = 0; b < e->batch; b++) {
+        while (e->seq_pages[b] < need) {
+            if (e->free_pages.empty())
+                return fail(e->ctx, PRISM_E_STATE, "KV page pool exhausted: " + std::to_string(e->pool_pages) + " pages of " +
+                                                       std::to_string(P) + " positions are all in use");
+            e->page_tbl_host[(size_t)b * e->pages_per_seq + e->seq_pages[b]] = e->free_pages.back();
+            e->free_pages.pop_back();
+            e->seq_pages[b] += 1;
+            changed = true;
+        }
+    }
+    if (changed) {
+        // the mirror outlives the copy (it belongs to the engine), so the asynchronous copy may read it later
+        PRISM_CUDA_TRY(e->ctx, cudaMemcpyAsync(e->page_tbl, e->page_tbl_host.data(), e->page_tbl_host.size() * sizeof(int32_t),
+                                               cudaMemcpyHostToDevice, e->ctx->stream));
+        PRISM_CUDA_TRY(e->ctx, cudaStreamSynchronize(e->ctx->stream));
+    }
+    return PRISM_OK;
+}
+static void release_pages(prism_cuda_engine *e) {
+    if (!e->page_tbl) return;
+    e->free_pages.clear();
+    for (uint32_t p = e->pool_pages; p > 0; p--) e->free_pages.push_back((int32_t)(p - 1));
+    std::fill(e->seq_pages.begin(), e->seq_pages.end(), 0u);
+}
+
 static int capacity_ok(prism_cuda_engine *e, uint32_t steps) {
     const uint64_t need = e->guard_skip ? (uint64_t)(e->pos + steps) * e->cfg.num_layers : (uint64_t)e->pos + steps;
     if (need > e->kv_slots)
         return fail(e->ctx, PRISM_E_STATE, "KV cache full: " + std::to_string(need) + " > " + std::to_string(e->kv_slots));
-    return PRISM_OK;
+    return ensure_pages(e, (uint32_t)need);
 }
 
 // Runs one step: the first call per (batch, options) runs eagerly (this sizes
@@ -464,6 +504,7 @@ static int prefill_chunk(prism_cuda_engine *e, uint32_t b, uint32_t pos0, uint32
         aa.nh = e->nh_l; aa.nkv = e->nkv_l; aa.hd = e->hd; aa.batch = T;
         aa.seq_stride = e->kv_seq_stride; aa.int8 = 0; aa.max_seq = e->kv_slots;
         aa.prefill = 1; aa.prefill_seq = b;
+        aa.page_tbl = e->page_tbl; aa.page_shift = e->page_shift; aa.tbl_stride = e->pages_per_seq;
         PRISM_TRY(launch_attn_fused(ctx, aa, e->pf_qkv + e->qd_l, e->pf_qkv + e->qd_l + e->kvd_l, c.rope_k, base));
         PRISM_TRY(launch_gemm(ctx, to, e->pf_att, T, e->pf_g));
         PRISM_TRY(launch_vec_add(ctx, e->pf_x, e->pf_g, T * H));            // h = f16(o + hr)
@@ -524,6 +565,12 @@ int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg,
     if (c.num_heads % c.num_kv_heads) return fail(ctx, PRISM_E_ARG, "num_heads must be a multiple of num_kv_heads");
     if (c.bits != 2 && c.bits != 4) return fail(ctx, PRISM_E_ARG, "bits must be 2 or 4");
     if (c.head_dim & 1) return fail(ctx, PRISM_E_ARG, "head_dim must be even");
+    if (c.kv_page_size) {
+        if (c.kv_page_size < 16 || (c.kv_page_size & (c.kv_page_size - 1))) return fail(ctx, PRISM_E_ARG, "kv_page_size must be a power of two >= 16");
+        if (c.kv_int8 || (c.down_guard && c.intermediate_size != c.hidden_size) ||
+            !(c.head_dim == 32 || c.head_dim == 64 || c.head_dim == 128 || c.head_dim == 256))
+            return fail(ctx, PRISM_E_ARG, "the paged KV cache is fp16 only, head_dim 32/64/128/256, without the reference's DownProj guard");
+    }
     const int T = ctx->tp_world, r = ctx->tp_rank;
     if (ctx->tp_loopback) return fail(ctx, PRISM_E_STATE, "a loopback tensor-parallel context has no peers: it cannot run a model");
     if (T > 1) {
@@ -564,7 +611,16 @@ int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg,
     e->act_stride = round_up_u32(round_up_u32(e->I_l, 64), 8);
     e->out_cap = c.max_seq;
     const uint32_t kv_layers = e->guard_skip ? 1 : L;
-    if (c.kv_int8) {
+    if (c.kv_page_size) {
+        e->page_shift = 0;
+        while ((1u << e->page_shift) < c.kv_page_size) e->page_shift++;
+        e->pages_per_seq = (c.max_seq + c.kv_page_size - 1) / c.kv_page_size;
+        e->pool_pages = c.kv_pool_pages ? c.kv_pool_pages : B * e->pages_per_seq;
+        e->kv_seq_stride = (uint64_t)e->kv_slots * e->kvd_l;   // not used for addressing: rows come from the page table
+        e->kv_layer_bytes = (size_t)e->pool_pages * c.kv_page_size * e->kvd_l * 2;
+        e->page_tbl_host.assign((size_t)B * e->pages_per_seq, 0);
+        e->seq_pages.assign(B, 0);
+    } else if (c.kv_int8) {
         e->kv_seq_stride = (uint64_t)e->kv_slots * (e->kvd_l + 4);
         e->kv_layer_bytes = (size_t)B * e->kv_seq_stride;
     } else {
@@ -588,6 +644,7 @@ int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg,
     ALLOC(e->pairs_send, (size_t)B * 8);
     ALLOC(e->pairs_recv, (size_t)B * 8 * T);
     ALLOC(e->scalars, 64);
+    if (c.kv_page_size) ALLOC(e->page_tbl, (size_t)B * e->pages_per_seq * sizeof(int32_t));
     ALLOC(e->kc, e->kv_layer_bytes * kv_layers);
     ALLOC(e->vc, e->kv_layer_bytes * kv_layers);
 #undef ALLOC
@@ -605,6 +662,10 @@ int prism_cuda_engine_create(prism_cuda_ctx *ctx, const prism_model_config *cfg,
         return cuda_fail(ctx, ce, "engine allocation");
     }
     e->batch = 1;
+    if (e->page_tbl) {
+        cudaMemsetAsync(e->page_tbl, 0, (size_t)B * e->pages_per_seq * sizeof(int32_t), ctx->stream);
+        release_pages(e);
+    }
     *out = e;
     return PRISM_OK;
 }
@@ -616,7 +677,7 @@ void prism_cuda_engine_destroy(prism_cuda_engine *e) {
     if (e->graph) cudaGraphExecDestroy(e->graph);
     for (int32_t h : e->wqkv)
         if (h >= 0) prism_cuda_free_tensor(e->ctx, h);
-    void *ptrs[] = {e->pf_x, e->pf_xn, e->pf_qkv, e->pf_att, e->pf_g, e->pf_u, e->pf_act, e->pf_tok, e->gu, e->h, e->xn, e->qkv, e->att, e->act, e->logits, e->part, e->tok, e->next,
+    void *ptrs[] = {e->page_tbl, e->pf_x, e->pf_xn, e->pf_qkv, e->pf_att, e->pf_g, e->pf_u, e->pf_act, e->pf_tok, e->gu, e->h, e->xn, e->qkv, e->att, e->act, e->logits, e->part, e->tok, e->next,
                     e->out_tokens, e->prompts, e->pairs_send, e->pairs_recv, e->scalars, e->kc, e->vc};
     for (void *p : ptrs) cudaFree(p);
     if (e->ev0) cudaEventDestroy(e->ev0);
@@ -732,6 +793,7 @@ int prism_cuda_engine_reset(prism_cuda_engine *e, uint32_t batch) {
     PRISM_CUDA_TRY(e->ctx, cudaSetDevice(e->ctx->device));
     e->batch = batch;
     e->pos = 0;
+    release_pages(e);  // a reset returns every page to the pool
     return set_scalars(e, 0, 0, 0);
 }
 

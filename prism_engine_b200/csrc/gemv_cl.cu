@@ -211,7 +211,15 @@ __global__ void __launch_bounds__(CL_THREADS) lut_gemv_cl_kernel(const ClArgs a)
                 }
             }
         } else if (MODE == GEMV_TP) {
-            if (tid < 64) tp_push_reduce_halfblock(a.tp, (tid >> 5) ? hb2 : hb1, tid & 31, sum, a.m, a.y + (size_t)bat * a.y_stride, a.err);
+            if (tid < 64) {  // this CTA has only this block: deliver and finish at once
+                const unsigned int e = tp_epoch(a.tp);
+                const uint32_t hb = (tid >> 5) ? hb2 : hb1;
+                uint16_t *lst = reinterpret_cast<uint16_t *>(csum) + (tid >> 5) * 2;  // rank 0's own sums are not needed any more
+                tp_deliver(a.tp, e, hb, lane, sum);
+                if (lane == 0 && !a.tp.deliver_only) lst[0] = (uint16_t)hb;
+                __syncwarp();
+                tp_finish(a.tp, e, lst, 1, lane, a.m, a.y + (size_t)bat * a.y_stride, a.err);
+            }
         } else if (tid < 64) {
             const uint32_t row = ((tid >> 5) ? hb2 : hb1) * 32 + (tid & 31);
             if (MODE == GEMV_F32) {

@@ -28,7 +28,7 @@ constexpr int SK_THREADS = SK_WARPS * 32;
 constexpr int SK_PIECE_BYTES = SK_WARPS * 16 * 64;  // x staged at a time: 4096 halves, 8 KB (128 chunks at 4 bit, 64 at 2 bit)
 constexpr int SK_PF = 2;                 // index chunks in flight per warp (1, 2 or 4)
 constexpr int SK_KNOWN_SBASE = 1024;      // dynamic shared memory starts after the 1 KB the driver reserves
-constexpr size_t SK_SMEM_BYTES = SK_TBL_BYTES + SK_PIECE_BYTES + SK_WARPS * 64 * 4 + 32;
+constexpr size_t SK_SMEM_BYTES = SK_TBL_BYTES + SK_PIECE_BYTES + SK_WARPS * 64 * 4 + 32 + 2 * TP_LIST_MAX * 2;
 
 
 // A 2-bit chunk (64 weights per row) as two pseudo 4-bit chunks of 32 weights each.
@@ -77,6 +77,8 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
 
     float inv = 1.0f;
     bool waited = false;
+    // GEMV_TP: what warps 0 and 1 have delivered to the peers, finished when the CTA has nothing left to stream
+    TpWarpList wl{reinterpret_cast<uint16_t *>(red + SK_WARPS * 64 + 8) + (warp & 1) * TP_LIST_MAX, 0};
 
     for (uint32_t u = u_begin; u < u_end;) {
         const uint32_t blk = u / nc;
@@ -309,7 +311,7 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
                 }
             }
         } else if (MODE == GEMV_TP) {
-            if (tid < 64) tp_push_reduce_halfblock(a.tp, (tid >> 5) ? hb2 : hb1, tid & 31, sum, a.m, a.y + (size_t)bat * a.y_stride, a.err);
+            if (tid < 64) tp_deliver_listed(a.tp, wl, (tid >> 5) ? hb2 : hb1, lane, sum, a.m, a.y + (size_t)bat * a.y_stride, a.err);
         } else if (tid < 64) {
             const uint32_t row = ((tid >> 5) ? hb2 : hb1) * 32 + (tid & 31);
             if (MODE == GEMV_F32) {
@@ -324,6 +326,7 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) lut_gemv_sk_kernel
             }
         }
     }
+    if (MODE == GEMV_TP && tid < 64) tp_finish(a.tp, tp_epoch(a.tp), wl.list, wl.n, lane, a.m, a.y + (size_t)bat * a.y_stride, a.err);
 }
 
 template <int MODE, int SBASE, int BITS>

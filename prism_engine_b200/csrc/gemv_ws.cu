@@ -36,7 +36,8 @@ constexpr int WS_X_BYTES = WS_STAGE_CHUNKS * 64;
 constexpr int WS_RED_OFF = WS_X_OFF + 2 * WS_X_BYTES;       // [2][WS_NC][64] floats
 constexpr int WS_FIN_OFF = WS_RED_OFF + 2 * WS_NC * 64 * 4; // builder scratch: 256 words
 constexpr int WS_BAR_OFF = WS_FIN_OFF + 256 * 4;            // full[2], empty[2], flags
-constexpr size_t WS_SMEM_BYTES = WS_BAR_OFF + 64;
+constexpr int WS_TPL_OFF = WS_BAR_OFF + 64;                 // GEMV_TP: two lists of delivered half-blocks
+constexpr size_t WS_SMEM_BYTES = WS_TPL_OFF + 2 * TP_LIST_MAX * 2;
 constexpr int WS_KNOWN_SBASE = 1024;
 
 
@@ -166,7 +167,7 @@ __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint3
 // partial sums and, when this CTA completes the block, adds every contributor's in range order.
 template <int MODE>
 __device__ __forceinline__ void ws_finish(const SkArgs &a, uint8_t *smem, const WsStage &st, uint32_t bt, uint32_t cta,
-                                          uint32_t G, uint32_t bat) {
+                                          uint32_t G, uint32_t bat, TpWarpList &wl) {
     const uint32_t nc = a.n_chunks, blk = st.blk, tb = st.seg & 1;
     const uint32_t hb1 = a.hb_mul * blk, hb2 = hb1 + a.hb_add2;
     const float *red = reinterpret_cast<const float *>(smem + WS_RED_OFF) + tb * WS_NC * 64;
@@ -239,7 +240,7 @@ __device__ __forceinline__ void ws_finish(const SkArgs &a, uint8_t *smem, const 
         }
         ws_bar_builders();  // fin may be rewritten by the next segment's finish
     } else if (MODE == GEMV_TP) {
-        if (bt < 64) tp_push_reduce_halfblock(a.tp, (bt >> 5) ? hb2 : hb1, bt & 31, sum, a.m, a.y + (size_t)bat * a.y_stride, a.err);
+        if (bt < 64) tp_deliver_listed(a.tp, wl, (bt >> 5) ? hb2 : hb1, bt & 31, sum, a.m, a.y + (size_t)bat * a.y_stride, a.err);
     } else if (bt < 64) {
         const uint32_t row = ((bt >> 5) ? hb2 : hb1) * 32 + (bt & 31);
         if (MODE == GEMV_F32) {
@@ -267,6 +268,8 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
     float inv = 1.0f;
     bool waited = false;
     WsStage hist[2];  // the two stages in flight, by buffer
+    // GEMV_TP: what builder warps 0 and 1 have delivered to the peers, finished after the CTA's last stage
+    TpWarpList wl{reinterpret_cast<uint16_t *>(smem + WS_TPL_OFF) + (bw & 1) * TP_LIST_MAX, 0};
     WsWalk walk;
     walk.init(u_begin, u_end, nc, WS_STAGE_CHUNKS);
     uint32_t t = 0;
@@ -277,7 +280,7 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
             // the compute warps are done with stage t-2: its buffers are free, its sums (if it
             // closed a segment) are in place
             ws_wait(bar_empty + 8 * xbuf, ((t - 2) >> 1) & 1, err_flag);
-            if (hist[xbuf].last) ws_finish<MODE>(a, smem, hist[xbuf], bt, cta, G, bat);
+            if (hist[xbuf].last) ws_finish<MODE>(a, smem, hist[xbuf], bt, cta, G, bat, wl);
         }
         hist[xbuf] = st;
         bool staged = false;
@@ -416,8 +419,9 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
     for (uint32_t r = (n_stages >= 2 ? n_stages - 2 : 0); r < n_stages; r++) {
         const uint32_t xbuf = r & 1;
         ws_wait(bar_empty + 8 * xbuf, (r >> 1) & 1, err_flag);
-        if (hist[xbuf].last) ws_finish<MODE>(a, smem, hist[xbuf], bt, cta, G, bat);
+        if (hist[xbuf].last) ws_finish<MODE>(a, smem, hist[xbuf], bt, cta, G, bat, wl);
     }
+    if (MODE == GEMV_TP && bt < 64) tp_finish(a.tp, tp_epoch(a.tp), wl.list, wl.n, bt & 31, a.m, a.y + (size_t)bat * a.y_stride, a.err);
 }
 
 template <int MODE, int SBASE>

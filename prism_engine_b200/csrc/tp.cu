@@ -179,12 +179,79 @@ int tp_fill_push(prism_cuda_ctx *ctx, const LutTensor &t, TpPush *out) {
     out->cap = (uint32_t)ctx->tp_cap;
     out->spin_limit = wait_limit(ctx, TP_AR_SPIN_LIMIT);
     out->n_units = t.n_hb;
+    out->deliver_only = ctx->tp_fused_ar == 1 ? 1u : 0u;
     return PRISM_OK;
 }
 
 bool gemv_tp_ok(prism_cuda_ctx *ctx, const LutTensor &t) {
     return ctx->tp_world > 1 && ctx->tp_peer_ar && ctx->tp_fused_ar && ctx->tp_cap != 0 && ctx->gemv_variant == 1 && t.bits == 4 &&
            t.k % 32 == 0 && t.k >= 32 && t.n_hb <= (uint32_t)TP_AR_MAX_CTAS && t.m_pad <= ctx->tp_cap;
+}
+
+// The second half of the all-reduce when the GEMV kernel has already delivered this rank's partial sums into
+// every rank's receive area (GEMV_TP with deliver_only): that kernel has completed, so its stores to peer
+// memory are performed; CTA c publishes flag [rank][c], waits for the same flag of every rank (bounded), adds
+// the slices in rank order, rounds, adds the residual.  No data crosses NVLink here, only the flags.
+__global__ void __launch_bounds__(TP_AR_THREADS) tp_ar_flags_resid_kernel(uint16_t *h, uint32_t n, void *const *peer_tab,
+                                                                          const float *recv, unsigned int *flags,
+                                                                          unsigned int *state, uint32_t world, uint32_t rank,
+                                                                          uint32_t cap, unsigned int *err, uint32_t spin_limit) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t cta = blockIdx.x, tid = threadIdx.x;
+    const unsigned int e = state[0] + 1;
+    const uint32_t slot = e & 1;
+    const uint32_t i = (cta * TP_AR_THREADS + tid) * 4;
+    if (tid < world) {
+        unsigned int *f = static_cast<unsigned int *>(peer_tab[world + tid]) + rank * TP_AR_MAX_CTAS + cta;
+        asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(f), "r"(e) : "memory");
+        const unsigned int *fw = flags + tid * TP_AR_MAX_CTAS + cta;
+        unsigned int seen = 0, polls = 0;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(fw) : "memory");
+            if ((int)(seen - e) >= 0) break;
+            if (++polls > spin_limit) {
+                atomicExch(err, 3u);
+                break;
+            }
+            if (polls > 64) __nanosleep(polls > 4096 ? 500 : 50);
+        }
+    }
+    __syncthreads();
+    if (i < n) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t r = 0; r < world; r++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(recv + ((size_t)slot * world + r) * cap + i));
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        uint2 hv = *reinterpret_cast<const uint2 *>(h + i);
+        const __half2 h01 = *reinterpret_cast<const __half2 *>(&hv.x), h23 = *reinterpret_cast<const __half2 *>(&hv.y);
+        const float o0 = __half2float(__float2half_rn(s.x)) + __low2float(h01);
+        const float o1 = __half2float(__float2half_rn(s.y)) + __high2float(h01);
+        const float o2 = __half2float(__float2half_rn(s.z)) + __low2float(h23);
+        const float o3 = __half2float(__float2half_rn(s.w)) + __high2float(h23);
+        const __half2 r01 = __floats2half2_rn(o0, o1), r23 = __floats2half2_rn(o2, o3);
+        hv.x = *reinterpret_cast<const unsigned int *>(&r01);
+        hv.y = *reinterpret_cast<const unsigned int *>(&r23);
+        *reinterpret_cast<uint2 *>(h + i) = hv;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&state[1], 1u) == gridDim.x - 1) {
+            state[1] = 0;
+            state[0] = e;
+        }
+    }
+}
+
+int tp_all_reduce_flags_resid(prism_cuda_ctx *ctx, uint16_t *h, size_t n) {
+    if (!tp_peer_ar_ok(ctx, n)) return fail(ctx, PRISM_E_STATE, "peer-memory all-reduce not available for this size");
+    const unsigned ctas = (unsigned)((n + TP_AR_THREADS * 4 - 1) / (TP_AR_THREADS * 4));
+    launch_pdl(ctx, "tp_ar_flags_resid_kernel", tp_ar_flags_resid_kernel, dim3(ctas), dim3(TP_AR_THREADS), 0, h, (uint32_t)n,
+               (void *const *)ctx->tp_peer_tab, (const float *)ctx->tp_recv, ctx->tp_flags, ctx->tp_state, (uint32_t)ctx->tp_world,
+               (uint32_t)ctx->tp_rank, (uint32_t)ctx->tp_cap, ctx->dev_err, wait_limit(ctx, TP_AR_SPIN_LIMIT));
+    return after_launch(ctx, "tp_ar_flags_resid_kernel");
 }
 
 bool tp_peer_ar_ok(prism_cuda_ctx *ctx, size_t n) {

@@ -5,10 +5,12 @@
 // The unit is a half-block: 32 output rows, owned by one warp of the CTA that has just completed the
 // rank's local sums for them.  That warp
 //   1. stores its 32 fp32 sums into slot [epoch & 1][this rank] of EVERY rank's receive area (plain
-//      stores over NVLink into peer memory mapped with cudaIpc*), fences at system scope and writes the
-//      epoch into flag [this rank][half-block] of every rank;
-//   2. waits (bounded) until its own flags [0..world)[half-block] hold the epoch -- the peers run the
-//      same kernel on their own K shard and complete the same rows at about the same time;
+//      stores over NVLink into peer memory mapped with cudaIpc*) as soon as they are complete, while the
+//      CTA goes on streaming;
+// and, when the CTA has nothing left to stream, for all the half-blocks it delivered:
+//   2. fences at system scope, writes the epoch into flag [this rank][half-block] of every rank, and
+//      waits (bounded) until its own flags [0..world)[half-block] hold the epoch -- the peers run the
+//      same kernel on their own K shard;
 //   3. adds the `world` partial sums in rank order (bit-identical on every rank), rounds to fp16, adds
 //      the residual and stores h.
 // Nothing waits before it has delivered, so no rank can wait for a rank that waits for it.  Two
@@ -32,62 +34,100 @@ struct TpPush {
     unsigned int *state;     // {epoch of the last completed all-reduce, half-blocks finished in the current one}
     uint32_t world, rank, cap, spin_limit;
     uint32_t n_units;        // half-blocks of the output vector
+    uint32_t deliver_only;   // 1: the kernel only delivers; flags, wait and reduction are a following tp_ar_flags_resid_kernel
 };
 
 // Host side (tp.cu): fills the kernel argument from the context's peer set-up; fails when the peer path is
 // not set up or the tensor has more half-blocks than flags.
 int tp_fill_push(prism_cuda_ctx *ctx, const LutTensor &t, TpPush *out);
 
-// Called by one whole warp; lane L holds the local sum of row hb*32 + L (rows >= m carry zeros and are
-// not stored to h).  h is the residual stream, read and written in place.
 #ifdef __CUDACC__
-__device__ __forceinline__ void tp_push_reduce_halfblock(const TpPush &tp, uint32_t hb, uint32_t lane, float sum, uint32_t m,
-                                                         uint16_t *h, unsigned int *err) {
-    const unsigned int e = *reinterpret_cast<volatile unsigned int *>(tp.state) + 1;  // stable while this kernel runs
+constexpr int TP_LIST_MAX = 32;  // half-blocks a warp may have delivered before it must stop and finish them
+
+__device__ __forceinline__ unsigned int tp_epoch(const TpPush &tp) {
+    return *reinterpret_cast<volatile unsigned int *>(tp.state) + 1;  // stable while this kernel runs
+}
+
+// Step 1 for one half-block, called by one whole warp as soon as the rank's local sums of the 32 rows are
+// complete: lane L holds the sum of row hb*32 + L (rows past the tensor carry zeros).  Only stores: a warp
+// never waits in the middle of the kernel, where a late peer would stall the CTA's pipeline.
+__device__ __forceinline__ void tp_deliver(const TpPush &tp, unsigned int e, uint32_t hb, uint32_t lane, float sum) {
     const uint32_t slot = e & 1, row = hb * 32 + lane;
-    // ---- deliver ----
     for (uint32_t q = 0; q < tp.world; q++) {
         float *dst = static_cast<float *>(tp.peer_tab[q]) + ((size_t)slot * tp.world + tp.rank) * tp.cap + row;
         *dst = sum;
     }
+}
+
+// Steps 2 and 3 for the `n` half-blocks list[0..n) this warp has delivered (the same warp, so one fence at
+// system scope covers all its stores): publish the flags, then for each half-block wait for every rank's
+// flag (bounded: spin_limit polls, then error code 3), add in rank order, round, add the residual into h,
+// and count the half-block as finished.  Called at the end of the CTA's work.
+__device__ __forceinline__ void tp_finish(const TpPush &tp, unsigned int e, const uint16_t *list, uint32_t n, uint32_t lane,
+                                          uint32_t m, uint16_t *h, unsigned int *err) {
+    if (n == 0 || tp.deliver_only) return;
+    const uint32_t slot = e & 1;
     __threadfence_system();
     __syncwarp();
     if (lane < tp.world) {
-        unsigned int *f = static_cast<unsigned int *>(tp.peer_tab[tp.world + lane]) + (size_t)tp.rank * TP_AR_MAX_CTAS + hb;
-        asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(f), "r"(e) : "memory");
+        unsigned int *fb = static_cast<unsigned int *>(tp.peer_tab[tp.world + lane]) + (size_t)tp.rank * TP_AR_MAX_CTAS;
+        for (uint32_t i = 0; i < n; i++) asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(fb + list[i]), "r"(e) : "memory");
     }
-    // ---- wait for the same rows of every rank (bounded: spin_limit polls, then error code 3) ----
-    if (lane < tp.world) {
-        const unsigned int *f = tp.flags + (size_t)lane * TP_AR_MAX_CTAS + hb;
-        unsigned int seen = 0, polls = 0;
-        for (;;) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(f) : "memory");
-            if ((int)(seen - e) >= 0) break;  // a peer that is already one all-reduce ahead has delivered this one too
-            if (++polls > tp.spin_limit) {
-                atomicExch(err, 3u);  // a peer did not deliver: reported by the next synchronising host call
-                break;
+    for (uint32_t i = 0; i < n; i++) {
+        const uint32_t hb = list[i], row = hb * 32 + lane;
+        if (lane < tp.world) {
+            const unsigned int *f = tp.flags + (size_t)lane * TP_AR_MAX_CTAS + hb;
+            unsigned int seen = 0, polls = 0;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(f) : "memory");
+                if ((int)(seen - e) >= 0) break;  // a peer that is already one all-reduce ahead has delivered this one too
+                if (++polls > tp.spin_limit) {
+                    atomicExch(err, 3u);  // a peer did not deliver: reported by the next synchronising host call
+                    break;
+                }
+                if (polls > 64) __nanosleep(polls > 4096 ? 500 : 50);
             }
-            if (polls > 64) __nanosleep(polls > 4096 ? 500 : 50);
         }
-    }
-    __syncwarp();
-    // ---- add in rank order, round, add the residual ----
-    float s = 0.0f;
-    for (uint32_t r = 0; r < tp.world; r++) s += __ldcg(tp.recv + ((size_t)slot * tp.world + r) * tp.cap + row);
-    if (row < m) {
-        const float o = __half2float(__float2half_rn(s)) + __half2float(__ushort_as_half(h[row]));
-        h[row] = __half_as_ushort(__float2half_rn(o));
+        __syncwarp();
+        float s = 0.0f;
+        for (uint32_t r = 0; r < tp.world; r++) s += __ldcg(tp.recv + ((size_t)slot * tp.world + r) * tp.cap + row);
+        if (row < m) {
+            const float o = __half2float(__float2half_rn(s)) + __half2float(__ushort_as_half(h[row]));
+            h[row] = __half_as_ushort(__float2half_rn(o));
+        }
     }
     // ---- the warp that finishes the last half-block advances the epoch ----
     __syncwarp();
     if (lane == 0) {
         __threadfence();
-        if (atomicAdd(&tp.state[1], 1u) == tp.n_units - 1) {
+        if (atomicAdd(&tp.state[1], n) + n == tp.n_units) {
             tp.state[1] = 0;
             __threadfence();
             tp.state[0] = e;
         }
     }
+}
+
+// A warp's bookkeeping of what it has delivered: deliver, remember, and finish early only when the list is full.
+struct TpWarpList {
+    uint16_t *list;   // TP_LIST_MAX entries of shared memory owned by this warp
+    uint32_t n;
+};
+__device__ __forceinline__ void tp_deliver_listed(const TpPush &tp, TpWarpList &wl, uint32_t hb, uint32_t lane, float sum,
+                                                  uint32_t m, uint16_t *h, unsigned int *err) {
+    const unsigned int e = tp_epoch(tp);
+    if (tp.deliver_only) {
+        tp_deliver(tp, e, hb, lane, sum);
+        return;
+    }
+    if (wl.n == (uint32_t)TP_LIST_MAX) {
+        tp_finish(tp, e, wl.list, wl.n, lane, m, h, err);
+        wl.n = 0;
+    }
+    tp_deliver(tp, e, hb, lane, sum);
+    if (lane == 0) wl.list[wl.n] = (uint16_t)hb;
+    __syncwarp();
+    wl.n += 1;
 }
 #endif
 

@@ -199,6 +199,69 @@ def test_batched_prefill_matches_the_oracle(oracle, chunk):
     eng.close(); twin.close(); be.close()
 
 
+@pytest.mark.timeout(900)
+def test_context_beyond_the_reference_limit(oracle):
+    """A 5000-token prompt (the reference stops at MAX_SEQ = 4096, engine_impl.rs:30): batched prefill in chunks,
+    then decode with every cluster rank of the attention kernel walking several tiles of cached rows."""
+    cfg = dict(num_layers=2, hidden_size=128, num_heads=4, num_kv_heads=2, head_dim=32, intermediate_size=256,
+               vocab_size=1024, norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True)
+    be = p.CudaBackend(device=0)
+    mc = p.model_config(**cfg, max_seq=6000, max_batch=1, profile="baseline")
+    eng = p.PrismEngine(be, mc)
+    eng.synth_weights(seed=23)
+    prompt = synth.make_prompt(5000, cfg["vocab_size"], seed=4)
+    got = eng.generate(prompt, 33)
+    assert eng.position() == 5033
+    twin = oracle_twin(oracle, be, cfg, mc)
+    want, margins = twin.generate(prompt, 33)
+    assert np.array_equal(got[:32], want[:32]), float(margins.min())
+    eng.close(); twin.close(); be.close()
+
+
+def test_paged_kv_cache(oracle):
+    """The fp16 cache as a pool of 16-position pages shared by the sequences: same tokens as the oracle, pages
+    returned on reset, and a clear error when the pool runs out."""
+    cfg = dict(TINY, hidden_size=128, intermediate_size=256, head_dim=32, vocab_size=1024)
+    be = p.CudaBackend(device=0)
+    # 3 sequences x 64 positions would be 12 pages of 16; the pool has 9: enough for 3 x 45 positions, not for 3 x 64
+    mc = p.model_config(**cfg, max_seq=64, max_batch=3, profile="baseline", kv_page_size=16, kv_pool_pages=9)
+    eng = p.PrismEngine(be, mc)
+    eng.synth_weights(seed=31)
+    prompts = np.stack([synth.make_prompt(11, cfg["vocab_size"], seed=s) for s in range(3)])
+    got = eng.generate(prompts, 33)                       # 44 positions per sequence: 3 pages each
+    twin = oracle_twin(oracle, be, cfg, mc)
+    for b in range(3):
+        want, margins = twin.generate(prompts[b], 33)
+        assert np.array_equal(got[b][:32], want[:32]), (b, float(margins.min()))
+    with pytest.raises(p.PrismCudaError) as e:
+        eng.generate(prompts, 50)                         # 61 positions: 4 pages each = 12 > 9
+    assert e.value.code == -5 and "page pool exhausted" in e.value.msg
+    one = eng.generate(prompts[1], 50)                    # a single sequence may use what three could not
+    want, _ = twin.generate(prompts[1], 50)
+    assert np.array_equal(one[:32], want[:32])
+    # token-serial prefill and stepwise decode go through the same page table
+    be.set_option("prefill_chunk", 0)
+    again = eng.generate(prompts, 33)
+    assert np.array_equal(again, got)
+    eng.close(); twin.close(); be.close()
+
+
+def test_more_than_32_sequences(oracle):
+    """40 concurrent sequences (the reference decodes one): every linear is one tensor-core GEMM over the batch."""
+    cfg = dict(TINY, hidden_size=128, intermediate_size=256, head_dim=32, vocab_size=1024)
+    be = p.CudaBackend(device=0)
+    mc = p.model_config(**cfg, max_seq=64, max_batch=40, profile="baseline")
+    eng = p.PrismEngine(be, mc)
+    eng.synth_weights(seed=29)
+    prompts = np.stack([synth.make_prompt(9, cfg["vocab_size"], seed=s) for s in range(40)])
+    got = eng.generate(prompts, 33)
+    twin = oracle_twin(oracle, be, cfg, mc)
+    for b in (0, 17, 39):
+        want, margins = twin.generate(prompts[b], 33)
+        assert np.array_equal(got[b][:32], want[:32]), (b, float(margins.min()))
+    eng.close(); twin.close(); be.close()
+
+
 @pytest.mark.timeout(1500)
 def test_qwen25_0p5b_first_32_tokens(oracle):
     """The 0.5B-architecture model of the benchmark configuration: identical greedy tokens for 32 steps."""

@@ -24,7 +24,7 @@ WIDE = dict(num_layers=2, hidden_size=8192, num_heads=64, num_kv_heads=8, head_d
             vocab_size=152064, norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
 
 
-def _worker(rank, world, port, q, peer_ar, wide=False, batch=2):
+def _worker(rank, world, port, q, peer_ar, wide=False, batch=2, fused=1):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -41,6 +41,7 @@ def _worker(rank, world, port, q, peer_ar, wide=False, batch=2):
         be = p.CudaBackend(device=rank)
         be.tp_init(world, rank, tp.exchange_unique_id(p.CudaBackend.tp_unique_id))
         be.set_option("tp_peer_ar", peer_ar)
+        be.set_option("tp_fused_ar", fused)
         peer = be.tp_peer_ready()
         cfg = WIDE if wide else CFG
         max_seq, n_new = (512, 33) if wide else (64, 33)
@@ -80,8 +81,11 @@ def _worker(rank, world, port, q, peer_ar, wide=False, batch=2):
 
 
 @pytest.mark.timeout(1500)
-@pytest.mark.parametrize("peer_ar,wide,batch", [(1, False, 2), (0, False, 2), (1, False, 1), (0, False, 1), (1, True, 1)])
-def test_tp2_matches_single_gpu_and_oracle(peer_ar, wide, batch):
+# fused (one sequence only): 0 = GEMV leaves fp32 partial sums, a kernel pushes and reduces them; 1 = the GEMV delivers
+# into the peers' receive areas, a kernel publishes flags and reduces; 2 = everything inside the GEMV kernel
+@pytest.mark.parametrize("peer_ar,fused,wide,batch", [(1, 1, False, 2), (0, 1, False, 2), (1, 0, False, 1), (1, 1, False, 1),
+                                                       (1, 2, False, 1), (0, 1, False, 1), (1, 1, True, 1), (1, 2, True, 1)])
+def test_tp2_matches_single_gpu_and_oracle(peer_ar, fused, wide, batch):
     import torch
 
     if torch.cuda.device_count() < 2:
@@ -90,8 +94,8 @@ def test_tp2_matches_single_gpu_and_oracle(peer_ar, wide, batch):
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + os.getpid() % 1000 + peer_ar + 2 * int(wide) + 4 * batch
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peer_ar, wide, batch)) for r in range(2)]
+    port = 29700 + os.getpid() % 1000 + peer_ar + 2 * int(wide) + 4 * batch + 16 * fused
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peer_ar, wide, batch, fused)) for r in range(2)]
     for pr in procs:
         pr.start()
     res = [q.get(timeout=1200) for _ in procs]
