@@ -39,6 +39,30 @@ def test_gemv_matches_oracle(backend, oracle, variant, m, k):
     backend.set_option("gemv_variant", 1)
 
 
+@pytest.mark.parametrize("m,k", [(8192, 8192), (8256, 8192), (4160, 29568), (10240, 8192)])
+def test_gemv_large_shapes(backend, oracle, m, k):
+    """The persistent warp-specialised kernel at 72B-sized shapes (8256 rows = 129 blocks: an odd count)."""
+    h = backend.synth("big", m, k, seed=m + k)
+    pay = backend.download_payload(h)
+    x = synth.make_activation(k, seed=7)
+    y = backend.gemv(h, x)
+    want = oracle.lut_gemv(x, pay, m, k, threads=oracle.max_threads())
+    assert rel_l2(y, want) <= TOL
+    assert np.mean(y == want) > 0.9
+    backend.free(h)
+
+
+def test_fused_gate_up_large(backend, oracle):
+    hidden, inter = 8192, 9248           # 289 gate/up half-blocks: an odd number of blocks
+    hg, hu = backend.synth("bg", inter, hidden, seed=1), backend.synth("bu", inter, hidden, seed=2)
+    x = synth.make_activation(hidden, seed=3)
+    act = backend.fused_gate_up(hg, hu, x)
+    _, want = oracle.mlp(backend.download_payload(hg), backend.download_payload(hu), None, x, hidden, inter,
+                         threads=oracle.max_threads())
+    assert rel_l2(act, want) <= TOL and np.mean(act == want) > 0.9
+    backend.free(hg); backend.free(hu)
+
+
 @pytest.mark.parametrize("variant", [0, 1])
 @pytest.mark.parametrize("m,k", [(65, 64), (512, 3584), (96, 128), (100, 48), (3584, 18944), (18944, 3584), (4864, 896)])
 def test_gemv_2bit(backend, oracle, variant, m, k):
