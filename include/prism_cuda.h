@@ -74,7 +74,7 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
  * "sk_min_chunks" (default 8: fewest 1 KB index chunks the GEMV gives one CTA of a small matrix),
  * "sk_stream_chunks" (default 64: chunks per CTA from which the GEMV deals contiguous, balanced
  * ranges to a persistent grid instead of cutting every 64-row block into equal parts),
- * "cl_max_units" (default 8192: matrices of at most this many (64-row block x 1 KB index chunk) units go to
+ * "cl_max_units" (default 16384: matrices of at most this many (64-row block x 1 KB index chunk) units go to
  * the cluster GEMV, whose CTAs hold all their indices in registers before the previous kernel has
  * finished and reduce through distributed shared memory; 0 = never),
  * "wait_limit_polls" (default 0 = built-in, about fifteen seconds: polls after which a kernel stops
@@ -83,7 +83,12 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
  * "prefill_chunk" (default 512: prism_cuda_engine_generate puts up to this many prompt tokens of a sequence
  * through the layers at once -- tensor-core GEMMs, causal attention over the cache, no LM head -- instead of
  * one step per token as the reference's prefill_cpu does; 0 = one step per token.  Single GPU, fp16 KV),
- * "tp_fused_ar" (0/1, default 1: batch-1 tensor-parallel decode all-reduces inside the GEMV kernel),
+ * "tp_fused_ar" (batch-1 tensor-parallel decode, how the partial sums of a row-parallel matmul are reduced:
+ * 0 = the GEMV leaves fp32 partial sums, one kernel pushes them to the peers and reduces; 1 = the GEMV's epilogue
+ * stores its sums into every rank's receive area, a small kernel publishes flags, waits and reduces; 2 = flags,
+ * wait and reduction inside the GEMV kernel too; 3 (default) = the GEMV's epilogue stores 8-byte words that carry
+ * their epoch, a small kernel polls the words and reduces -- no flags and no system-scope fence.  Set it
+ * identically on every rank),
  * "cimage_cache" (0/1, default 0: prism_cuda_engine_load_cimage keeps the re-laid image beside the file).
  * A captured decode graph is rebuilt after any option change. */
 int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value);

@@ -264,10 +264,14 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
         if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8)
             return fail(ctx, PRISM_E_ARG, "attn_cluster must be 0, 1, 2, 4 or 8");
         ctx->attn_cluster = (int)value;
+    } else if (!strcmp(key, "attn_group")) {
+        if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8)
+            return fail(ctx, PRISM_E_ARG, "attn_group must be 0, 1, 2, 4 or 8");
+        ctx->attn_group = (int)value;
     } else if (!strcmp(key, "tp_peer_ar")) {
         ctx->tp_peer_ar = value ? 1 : 0;
     } else if (!strcmp(key, "tp_fused_ar")) {
-        if (value < 0 || value > 2) return fail(ctx, PRISM_E_ARG, "tp_fused_ar must be 0, 1 or 2");
+        if (value < 0 || value > 3) return fail(ctx, PRISM_E_ARG, "tp_fused_ar must be 0, 1, 2 or 3");
         ctx->tp_fused_ar = (int)value;
     } else if (!strcmp(key, "pdl")) {
         ctx->pdl = value ? 1 : 0;

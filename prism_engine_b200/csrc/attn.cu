@@ -462,10 +462,15 @@ template <int VEC>
 static int launch_attn_fused_g(prism_cuda_ctx *ctx, const FusedAttnArgs &fa, uint32_t S) {
     // query heads served per pass over the cache: the group size rounded up to a power of two, at
     // most 8 (4 for 256-wide heads: registers)
-    const uint32_t g = fa.nh / fa.nkv, cap = VEC == 8 ? 4 : 8;
+    const uint32_t g = fa.nh / fa.nkv;
+    uint32_t cap = VEC == 8 ? 4 : 8;
+    // A small model with few KV heads would leave most of the GPU idle (0.5B: 2 KV heads x 2 CTAs): serve fewer
+    // heads per cluster until about two dozen CTAs run; the cached rows are then read once per cluster, from L2.
+    while (cap > 1 && fa.nkv * ((g + cap - 1) / cap) * S * fa.batch < 24 && g > cap / 2) cap /= 2;
+    if (ctx->attn_group > 0) cap = min(cap, (uint32_t)ctx->attn_group);
     if (g >= 5 && cap >= 8) return launch_attn_fused_v<VEC, (VEC == 8 ? 4 : 8)>(ctx, fa, S);
-    if (g >= 3) return launch_attn_fused_v<VEC, 4>(ctx, fa, S);
-    if (g == 2) return launch_attn_fused_v<VEC, 2>(ctx, fa, S);
+    if (g >= 3 && cap >= 4) return launch_attn_fused_v<VEC, 4>(ctx, fa, S);
+    if (g >= 2 && cap >= 2) return launch_attn_fused_v<VEC, 2>(ctx, fa, S);
     return launch_attn_fused_v<VEC, 1>(ctx, fa, S);
 }
 

@@ -75,9 +75,10 @@ struct prism_cuda_ctx {
     int fuse = 1;
     int sk_min_chunks = 8;      // stream-K GEMV, small matrices: fewest 1 KB index chunks a CTA is given
     int sk_stream_chunks = 64;  // chunks per CTA from which the balanced contiguous partition is used
-    int cl_max_units = 8192;    // cluster GEMV for matrices of at most this many (64-row block, 1 KB chunk) units; 0: never
+    int cl_max_units = 16384;    // cluster GEMV for matrices of at most this many (64-row block, 1 KB chunk) units; 0: never
     int batch_gemv_max = 8;   // decode batches up to this size use the batched GEMV (groups of 8), larger ones the GEMM
     int attn_cluster = 0;    // CTAs per (head, sequence) of the fused attention kernel; 0: chosen from max_seq
+    int attn_group = 0;      // most query heads of a KV group one cluster of the fused attention serves (1/2/4/8); 0: chosen from the shape
     int gemm_reuse_x = 0;    // set by a caller for the second of two GEMMs over the same activations: skip the re-lay
     int pdl = 1;  // programmatic dependent launch between the kernels of the decode chain
     int prefill_chunk = 512;  // prompt tokens generate() puts through the layers at once (tensor-core GEMMs); 0: one step per token
@@ -119,8 +120,9 @@ struct prism_cuda_ctx {
     int tp_peer_ar = 1;                // option "tp_peer_ar": use the peer-memory all-reduce when available
     // option "tp_fused_ar" (batch-1 decode): 0 = GEMV writes fp32 partial sums, a separate kernel pushes and reduces them;
     // 1 = the GEMV epilogue stores its sums straight into every rank's receive area, a small kernel publishes flags and
-    // reduces; 2 = flags, wait and reduction inside the GEMV kernel too
-    int tp_fused_ar = 1;
+    // reduces; 2 = flags, wait and reduction inside the GEMV kernel too; 3 = the GEMV epilogue stores 8-byte words
+    // {sum, epoch} into every rank's flagged-word area, a small kernel polls the words themselves and reduces
+    int tp_fused_ar = 3;
     std::string tp_peer_reason;        // why the peer path is unavailable ("" when it is set up)
     bool tp_loopback = false;          // prism_cuda_tp_init_loopback: every "peer" is this GPU's own receive area
     // rotation frequencies of the fused attention kernel (attn.cu), one table per (head size, base) ever
@@ -222,6 +224,8 @@ bool tp_peer_ar_ok(prism_cuda_ctx *ctx, size_t n);
 int tp_all_reduce_resid_peer(prism_cuda_ctx *ctx, const float *part, uint16_t *h, size_t n);
 // the same after a GEMV_TP kernel that only delivered (option tp_fused_ar = 1): flags, wait, reduction, residual
 int tp_all_reduce_flags_resid(prism_cuda_ctx *ctx, uint16_t *h, size_t n);
+// after a GEMV_TP kernel that delivered flagged words (tp_fused_ar = 3): poll the words, reduction, residual
+int tp_all_reduce_ll_resid(prism_cuda_ctx *ctx, uint16_t *h, size_t n);
 // Synchronises the stream and reads the device error word.  Codes kernels leave there:
 //   1  a kernel found its shared-memory layout assumption broken and refused to run  -> PRISM_E_STATE
 //   2  an mbarrier hand-over inside a warp-specialised GEMV gave up                    -> PRISM_E_TIMEOUT

@@ -255,6 +255,7 @@ static int enqueue_step(prism_cuda_engine *e) {
             // partial products, their all-reduce over the ranks and the residual add in one kernel
             PRISM_TRY(launch_gemv(ctx, GEMV_TP, to, nullptr, e->att, e->qd_l, e->h, H, e->h, B));
             if (ctx->tp_fused_ar == 1) PRISM_TRY(tp_all_reduce_flags_resid(ctx, e->h, H));
+            if (ctx->tp_fused_ar == 3) PRISM_TRY(tp_all_reduce_ll_resid(ctx, e->h, H));
         } else if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, to, nullptr, e->att, e->qd_l, (uint16_t *)e->part, H, nullptr, B));
             PRISM_TRY(tp_reduce_add_resid(e, B * H));
@@ -277,6 +278,7 @@ static int enqueue_step(prism_cuda_engine *e) {
         if (tp && B == 1 && gemv_tp_ok(ctx, td)) {
             PRISM_TRY(launch_gemv(ctx, GEMV_TP, td, nullptr, e->act, e->act_stride, e->h, H, e->h, B));
             if (ctx->tp_fused_ar == 1) PRISM_TRY(tp_all_reduce_flags_resid(ctx, e->h, H));
+            if (ctx->tp_fused_ar == 3) PRISM_TRY(tp_all_reduce_ll_resid(ctx, e->h, H));
         } else if (tp) {
             PRISM_TRY(launch_gemv(ctx, GEMV_F32, td, nullptr, e->act, e->act_stride, (uint16_t *)e->part, H, nullptr, B));
             PRISM_TRY(tp_reduce_add_resid(e, B * H));

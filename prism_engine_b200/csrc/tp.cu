@@ -164,6 +164,9 @@ __global__ void __launch_bounds__(TP_AR_THREADS) tp_ar_resid_kernel(const float 
     }
 }
 
+// The flagged-word area follows the float slots inside the same allocation (one IPC handle covers both).
+static size_t tp_ll_offset(int world) { return 2ull * world * TP_AR_CAP_FLOATS * sizeof(float); }
+
 int tp_fill_push(prism_cuda_ctx *ctx, const LutTensor &t, TpPush *out) {
     if (ctx->tp_world <= 1 || ctx->tp_cap == 0 || !ctx->tp_peer_tab)
         return fail(ctx, PRISM_E_STATE, "fused all-reduce: the peer-memory path is not set up" +
@@ -179,11 +182,14 @@ int tp_fill_push(prism_cuda_ctx *ctx, const LutTensor &t, TpPush *out) {
     out->cap = (uint32_t)ctx->tp_cap;
     out->spin_limit = wait_limit(ctx, TP_AR_SPIN_LIMIT);
     out->n_units = t.n_hb;
-    out->deliver_only = ctx->tp_fused_ar == 1 ? 1u : 0u;
+    out->deliver_only = (ctx->tp_fused_ar == 1 || ctx->tp_fused_ar == 3) ? 1u : 0u;
+    out->ll_off = ctx->tp_fused_ar == 3 ? (uint32_t)tp_ll_offset(ctx->tp_world) : 0u;
+    if (out->ll_off && t.m_pad > TP_LL_CAP) return fail(ctx, PRISM_E_ARG, "fused all-reduce: output vector too long for the flagged-word area");
     return PRISM_OK;
 }
 
 bool gemv_tp_ok(prism_cuda_ctx *ctx, const LutTensor &t) {
+    if (ctx->tp_fused_ar == 3 && t.m_pad > TP_LL_CAP) return false;
     return ctx->tp_world > 1 && ctx->tp_peer_ar && ctx->tp_fused_ar && ctx->tp_cap != 0 && ctx->gemv_variant == 1 && t.bits == 4 &&
            t.k % 32 == 0 && t.k >= 32 && t.n_hb <= (uint32_t)TP_AR_MAX_CTAS && t.m_pad <= ctx->tp_cap;
 }
@@ -254,6 +260,74 @@ int tp_all_reduce_flags_resid(prism_cuda_ctx *ctx, uint16_t *h, size_t n) {
     return after_launch(ctx, "tp_ar_flags_resid_kernel");
 }
 
+// The reduction when the GEMV kernel has delivered flagged words (GEMV_TP, ll_off != 0): every word carries the
+// epoch it belongs to, so nothing but the data crosses NVLink -- no fence at system scope, no flag stores, no
+// second trip.  One thread per output row loads the `world` words of its row, re-polls (bounded) the ones that
+// have not arrived, adds them in rank order, rounds and adds the residual.  64-thread CTAs with few registers:
+// they fit beside a GEMV CTA that owns the rest of an SM, so the grid is resident before the GEMV ends.
+constexpr int TP_LL_THREADS = 64;
+__device__ __forceinline__ unsigned long long tp_ll_load(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];\n" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__global__ void __launch_bounds__(TP_LL_THREADS) tp_ar_ll_resid_kernel(uint16_t *h, uint32_t n, const unsigned long long *ll,
+                                                                       unsigned int *state, uint32_t world, unsigned int *err,
+                                                                       uint32_t spin_limit) {
+    pdl_launch_dependents();
+    pdl_wait();  // the delivering GEMV and everything before it (the previous reduction, which advanced the epoch) are complete
+    const uint32_t row = blockIdx.x * TP_LL_THREADS + threadIdx.x;
+    const unsigned int e = *reinterpret_cast<volatile unsigned int *>(state) + 1;
+    if (row < n) {
+        const unsigned long long *p = ll + (size_t)(e & 1) * world * TP_LL_CAP + row;
+        unsigned long long v[16];
+#pragma unroll
+        for (uint32_t r = 0; r < 16; r++) v[r] = r < world ? tp_ll_load(p + (size_t)r * TP_LL_CAP) : 0ull;
+        unsigned int polls = 0;
+        for (;;) {
+            bool all = true;
+#pragma unroll
+            for (uint32_t r = 0; r < 16; r++) {
+                if (r < world && (unsigned int)(v[r] >> 32) != e) {
+                    all = false;
+                    v[r] = tp_ll_load(p + (size_t)r * TP_LL_CAP);
+                }
+            }
+            if (all) break;
+            if (++polls > spin_limit) {
+                atomicExch(err, 3u);  // a peer did not deliver: reported by the next synchronising host call
+                break;
+            }
+            if (polls > 64) __nanosleep(polls > 4096 ? 500 : 50);
+        }
+        float s = 0.0f;
+#pragma unroll
+        for (uint32_t r = 0; r < 16; r++)
+            if (r < world) s += __uint_as_float((unsigned int)v[r]);
+        const float o = __half2float(__float2half_rn(s)) + __half2float(__ushort_as_half(h[row]));
+        h[row] = __half_as_ushort(__float2half_rn(o));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&state[1], 1u) == gridDim.x - 1) {
+            state[1] = 0;
+            state[0] = e;
+        }
+    }
+}
+
+int tp_all_reduce_ll_resid(prism_cuda_ctx *ctx, uint16_t *h, size_t n) {
+    if (ctx->tp_world <= 1 || ctx->tp_cap == 0 || n > TP_LL_CAP || ctx->tp_world > 16)
+        return fail(ctx, PRISM_E_STATE, "flagged-word all-reduce not available for this size");
+    const unsigned ctas = (unsigned)((n + TP_LL_THREADS - 1) / TP_LL_THREADS);
+    const unsigned long long *ll =
+        reinterpret_cast<const unsigned long long *>(reinterpret_cast<const char *>(ctx->tp_recv) + tp_ll_offset(ctx->tp_world));
+    launch_pdl(ctx, "tp_ar_ll_resid_kernel", tp_ar_ll_resid_kernel, dim3(ctas), dim3(TP_LL_THREADS), 0, h, (uint32_t)n, ll,
+               ctx->tp_state, (uint32_t)ctx->tp_world, ctx->dev_err, wait_limit(ctx, TP_AR_SPIN_LIMIT));
+    return after_launch(ctx, "tp_ar_ll_resid_kernel");
+}
+
 bool tp_peer_ar_ok(prism_cuda_ctx *ctx, size_t n) {
     return ctx->tp_world > 1 && ctx->tp_peer_ar && ctx->tp_cap != 0 && n <= ctx->tp_cap && n % 4 == 0 &&
            (n + TP_AR_THREADS * 4 - 1) / (TP_AR_THREADS * 4) <= (size_t)TP_AR_MAX_CTAS;
@@ -287,7 +361,8 @@ static void tp_peer_release(prism_cuda_ctx *ctx) {
 
 // This rank's receive area, flags, epoch state and the (still empty) pointer table.
 static bool tp_peer_alloc(prism_cuda_ctx *ctx, int T, std::string &why) {
-    const size_t recv_bytes = 2ull * T * TP_AR_CAP_FLOATS * sizeof(float);
+    const size_t ll_bytes = 2ull * T * TP_LL_CAP * sizeof(unsigned long long);  // epoch 0 in every word: nothing delivered
+    const size_t recv_bytes = tp_ll_offset(T) + ll_bytes;
     const size_t flag_bytes = (size_t)T * TP_AR_MAX_CTAS * sizeof(unsigned int);
     cudaError_t e;
     if ((e = cudaMalloc((void **)&ctx->tp_recv, recv_bytes)) != cudaSuccess ||
@@ -295,6 +370,7 @@ static bool tp_peer_alloc(prism_cuda_ctx *ctx, int T, std::string &why) {
         (e = cudaMalloc((void **)&ctx->tp_state, 2 * sizeof(unsigned int))) != cudaSuccess ||
         (e = cudaMalloc((void **)&ctx->tp_peer_tab, 2 * T * sizeof(void *))) != cudaSuccess ||
         (e = cudaMemsetAsync(ctx->tp_flags, 0, flag_bytes, ctx->stream)) != cudaSuccess ||
+        (e = cudaMemsetAsync(reinterpret_cast<char *>(ctx->tp_recv) + tp_ll_offset(T), 0, ll_bytes, ctx->stream)) != cudaSuccess ||
         (e = cudaMemsetAsync(ctx->tp_state, 0, 2 * sizeof(unsigned int), ctx->stream)) != cudaSuccess) {
         why = std::string("receive area allocation: ") + cudaGetErrorString(e);
         (void)cudaGetLastError();

@@ -26,6 +26,7 @@ namespace prism {
 
 constexpr int TP_AR_MAX_CTAS = 1024;               // flags per rank: CTAs of the stand-alone kernel, or half-blocks
 constexpr unsigned int TP_AR_SPIN_LIMIT = 1u << 25;  // polls with back-off: about fifteen seconds (ranks may start seconds apart)
+constexpr uint32_t TP_LL_CAP = 65536;              // rows per rank slot of the flagged-word area (longest output vector it takes)
 
 struct TpPush {
     void *const *peer_tab;   // device array: world receive-area pointers, then world flag pointers; nullptr: not in use
@@ -34,7 +35,9 @@ struct TpPush {
     unsigned int *state;     // {epoch of the last completed all-reduce, half-blocks finished in the current one}
     uint32_t world, rank, cap, spin_limit;
     uint32_t n_units;        // half-blocks of the output vector
-    uint32_t deliver_only;   // 1: the kernel only delivers; flags, wait and reduction are a following tp_ar_flags_resid_kernel
+    uint32_t deliver_only;   // 1: the kernel only delivers; wait and reduction are a following kernel
+    uint32_t ll_off;         // != 0: deliver 8-byte words {sum, epoch} into the flagged-word area, this many bytes into
+                             // every rank's receive area ([2][world][TP_LL_CAP] words); the reader polls the words themselves
 };
 
 // Host side (tp.cu): fills the kernel argument from the context's peer set-up; fails when the peer path is
@@ -53,6 +56,17 @@ __device__ __forceinline__ unsigned int tp_epoch(const TpPush &tp) {
 // never waits in the middle of the kernel, where a late peer would stall the CTA's pipeline.
 __device__ __forceinline__ void tp_deliver(const TpPush &tp, unsigned int e, uint32_t hb, uint32_t lane, float sum) {
     const uint32_t slot = e & 1, row = hb * 32 + lane;
+    if (tp.ll_off) {
+        // One 8-byte store carries value and epoch: a reader that sees the epoch sees the value (a scalar 64-bit
+        // access is single-copy atomic), so neither a fence nor a separate flag crosses the link.
+        const unsigned long long word = ((unsigned long long)e << 32) | (unsigned long long)__float_as_uint(sum);
+        for (uint32_t q = 0; q < tp.world; q++) {
+            unsigned long long *dst = reinterpret_cast<unsigned long long *>(static_cast<char *>(tp.peer_tab[q]) + tp.ll_off) +
+                                      ((size_t)slot * tp.world + tp.rank) * TP_LL_CAP + row;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;\n" ::"l"(dst), "l"(word) : "memory");
+        }
+        return;
+    }
     for (uint32_t q = 0; q < tp.world; q++) {
         float *dst = static_cast<float *>(tp.peer_tab[q]) + ((size_t)slot * tp.world + tp.rank) * tp.cap + row;
         *dst = sum;
