@@ -21,6 +21,7 @@ clocks:
   config3           N = 1: Qwen2.5-0.5B decode, 128-token prompt, 256 generated tokens
   config4           N = 1: the six prefill GEMMs of a Qwen2.5-7B layer, M = 2048, N(0,1) activations
   lut_gemv_0p5b_shapes   N = 1: GEMV / fused gate-up / MLP at the 4864x896 shapes, working set > L2
+  lut_gemv_decode_shapes N = 1: the five GEMV launch shapes of the workload's decode step, each timed alone
   cpu_baseline      N = 1: the CPU restatement of the reference's path on the host cores (a sample)
 
 `--impl reference` times the CPU restatement of the reference's own path (the
@@ -420,6 +421,7 @@ def run_ours(args):
             line["config4"] = config4_gemm(env, be)
         if not args.no_gemv_shapes:
             line["lut_gemv_0p5b_shapes"] = small_shape_bandwidth(env, be, peak)
+            line["lut_gemv_decode_shapes"] = decode_shape_bandwidth(env, be, arch, peak)
         if not args.no_cpu_baseline:
             from oracle import oracle as orc
 
@@ -575,6 +577,41 @@ def small_shape_bandwidth(env, be, peak):
                      "us_per_call": ms * 1e3 / (n_sets * reps), "algorithmic_bytes": nbytes}
     for h in gate + up + down:
         be.free(h)
+    return out
+
+
+def decode_shape_bandwidth(env, be, arch, peak):
+    """The five GEMV launch shapes of the decode step (stacked q+k+v, o, fused gate+up, down, LM head), each
+    timed alone: more than 1 GB of distinct weight sets of the shape cycle inside one CUDA graph, so every
+    launch streams from HBM and follows a launch of its own kind."""
+    torch = env.torch
+    from prism_engine_b200 import synth
+
+    H, I, V = arch["hidden_size"], arch["intermediate_size"], arch["vocab_size"]
+    qkv_rows = (arch["num_heads"] + 2 * arch["num_kv_heads"]) * arch["head_dim"]
+    shapes = (("qkv", qkv_rows, H, 0), ("o", H, arch["num_heads"] * arch["head_dim"], 0), ("gate_up_swiglu", I, H, 1),
+              ("down", H, I, 0), ("lm_head", V, H, 0))
+    out = {}
+    for name, m, k, kind in shapes:
+        nbytes = synth.gemv_algorithmic_bytes(m, k)
+        n_sets = min(64, max(2, int(1.2e9 // nbytes)))
+        if kind == 1:
+            n_sets = max(2, n_sets // 2 * 2)
+        hs = [be.synth(f"shape.{name}{i}", m, k, seed=5000 + i) for i in range(n_sets)]
+        x = torch.from_numpy(synth.make_activation(k, seed=9).view(np.int16)).cuda()
+        torch.cuda.synchronize()
+        calls = n_sets // 2 if kind == 1 else n_sets
+        per_call = 2 * nbytes - 2 * k if kind == 1 else nbytes
+        arr = np.array(list(zip(hs[0::2], hs[1::2])) if kind == 1 else hs, np.int32)
+        reps = 6
+        be.bench_cycle(kind, arr, 2, x.data_ptr())
+        ms = be.bench_cycle(kind, arr, reps, x.data_ptr())
+        us = ms * 1e3 / (calls * reps)
+        gbs = per_call / us / 1e3
+        out[name] = {"rows": m * (2 if kind == 1 else 1), "k": k, "us_per_call": us, "gbs": gbs, "frac_of_measured_peak": gbs / peak,
+                     "algorithmic_bytes": per_call}
+        for h in hs:
+            be.free(h)
     return out
 
 

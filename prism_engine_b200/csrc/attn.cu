@@ -51,6 +51,7 @@ struct FusedAttnArgs {
     // << page_shift) + (p & (page - 1)) of the layer's page pool; nullptr: one contiguous slab per sequence.
     const int32_t *page_tbl;
     uint32_t page_shift, tbl_stride;
+    uint32_t early_cache;       // 1: the kernel before this one in the stream does not write the cache (see the kernel)
 };
 
 // Row (in units of cached rows of the layer) of position p of cache sequence c.
@@ -77,12 +78,12 @@ __device__ __forceinline__ void fa_rope_angles(float (&ca)[VEC], float (&sa)[VEC
     }
 }
 
-// Values of the same shared-memory word in every CTA of the cluster (at most 8), requested together:
-// a loop with a run-time trip count would issue the remote loads one after the other.
+// Stores a value into the same shared-memory word of every CTA of the cluster (at most 8), its own included.
 template <typename G>
-__device__ __forceinline__ void fa_gather(float (&v)[8], G &cluster, float *word, uint32_t S, float neutral) {
+__device__ __forceinline__ void fa_scatter(G &cluster, float *word, uint32_t S, float value) {
 #pragma unroll
-    for (uint32_t r = 0; r < 8; r++) v[r] = r < S ? *cluster.map_shared_rank(word, r) : neutral;
+    for (uint32_t r = 0; r < 8; r++)
+        if (r < S) *cluster.map_shared_rank(word, r) = value;
 }
 // Rotates a lane's elements; the partner element j +- hd/2 lives in lane ^ 16.
 template <int VEC>
@@ -139,7 +140,9 @@ __host__ __device__ constexpr uint32_t fa_tile_rows(uint32_t hd) { return 24576u
 template <int VEC, int GT>
 __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnArgs a) {
     pdl_launch_dependents();
-    pdl_wait();
+    // first half of a cluster barrier that only says "this CTA has started": its second half stands before the
+    // first store into a peer's shared memory and has long completed by then
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory");
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t S = cluster.dim_blocks().x, rank = cluster.block_rank();
     constexpr uint32_t hd = 32 * VEC;
@@ -153,8 +156,9 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
     uint16_t *kt = newv + hd;                                      // [PR][hd] key tile
     uint16_t *vt = kt + PR * hd;                                   // [PR][hd] value tile
     float *part = reinterpret_cast<float *>(kt);                   // after the last tile: [FA_WARPS][GT*hd] partial outputs
+    float *recv = reinterpret_cast<float *>(vt + PR * hd);         // [S][slice]: every rank's partial sums of the outputs this CTA finishes
     __shared__ float sh[FA_WARPS][GT];
-    __shared__ float xch[2][GT];                   // this CTA's maxima and sums, read by its peers
+    __shared__ float xall[2][8][GT];               // maxima and sums of every CTA of the cluster, stored here by their owners
     __shared__ float sinv[GT];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, b = blockIdx.y;
     const uint32_t g = a.nh / a.nkv, n_tiles = (g + GT - 1) / GT, kvd = a.nkv * hd;
@@ -162,25 +166,32 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
     const uint32_t h0 = kh * g + tile * GT;        // first query head of this cluster
     const uint32_t nhl = min((uint32_t)GT, g - tile * GT);
 
-    const int32_t pos = *a.pos_dev + (a.prefill ? (int32_t)b : 0);
-    const int64_t slot64 = (int64_t)pos * a.slot_mul + a.slot_add;
-    const bool have_new = !a.prefill && slot64 >= 0 && slot64 < (int64_t)a.max_seq;  // a full cache takes no new row
-    uint32_t sl = (uint32_t)(slot64 + 1);
-    if (slot64 < 0) sl = 0;
-    if (sl > a.max_seq) sl = a.max_seq;
-    const uint32_t new_slot = have_new ? (uint32_t)slot64 : 0xFFFFFFFFu;
-    uint32_t chunk = (sl + S - 1) / S;
-    if (chunk > a.chunk_cap) chunk = a.chunk_cap;  // cannot happen with chunk_cap = ceil(max_seq / S)
-    const uint32_t p_begin = min(sl, rank * chunk), p_end = min(sl, p_begin + chunk);
-    const uint32_t n_loc = p_end - p_begin;
-    const uint32_t n_pass = (n_loc + PR - 1) / PR;
-
     const uint32_t cseq = a.prefill ? a.seq : b;   // which sequence's cache
     uint16_t *kcb = a.kc + (size_t)kh * hd;
     uint16_t *vcb = a.vc + (size_t)kh * hd;
     const uint64_t seq_rows = a.seq_stride / kvd;  // rows of a sequence's slab (contiguous cache)
     auto row_of = [&](uint32_t p) { return fa_row(a.page_tbl, a.page_shift, a.tbl_stride, seq_rows, cseq, p) * kvd; };
     constexpr uint32_t PPR = hd / 8;               // 16-byte pieces per row
+
+    // Everything that follows from the token position: which cache rows this CTA covers, where the new row goes.
+    int32_t pos;
+    bool have_new;
+    uint32_t sl, new_slot, p_begin, p_end, n_loc, n_pass;
+    auto place = [&](int32_t pos_now) {
+        pos = pos_now + (a.prefill ? (int32_t)b : 0);
+        const int64_t slot64 = (int64_t)pos * a.slot_mul + a.slot_add;
+        have_new = !a.prefill && slot64 >= 0 && slot64 < (int64_t)a.max_seq;  // a full cache takes no new row
+        sl = (uint32_t)(slot64 + 1);
+        if (slot64 < 0) sl = 0;
+        if (sl > a.max_seq) sl = a.max_seq;
+        new_slot = have_new ? (uint32_t)slot64 : 0xFFFFFFFFu;
+        uint32_t chunk = (sl + S - 1) / S;
+        if (chunk > a.chunk_cap) chunk = a.chunk_cap;  // cannot happen with chunk_cap = ceil(max_seq / S)
+        p_begin = min(sl, rank * chunk);
+        p_end = min(sl, p_begin + chunk);
+        n_loc = p_end - p_begin;
+        n_pass = (n_loc + PR - 1) / PR;
+    };
     // rows [r0, r0 + n) of this CTA's range into the tiles (the new token's row comes from registers instead)
     auto stage = [&](uint32_t r0, uint32_t n, bool with_k) {
         for (uint32_t i = threadIdx.x; i < n * PPR; i += FA_THREADS) {
@@ -191,12 +202,34 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
             fa_cp16(vt + r * hd + c * 8, vcb + ro + c * 8);
         }
     };
+    // A decode step's predecessor in the stream (the q/k/v projection) does not touch the cache, and the rows
+    // below the new token's were written steps ago: with `early_cache` the first tiles are requested and the
+    // rotation angles computed BEFORE the dependency wait, on the position as it reads now.  The position is
+    // read again after the wait; should it have changed (the kernel that advances it had not finished yet),
+    // the speculative tiles are dropped and everything is placed again.  Prefill rows are written by the
+    // kernel right before this one, so prefill waits first.
+    const volatile int32_t *pos_ptr = a.pos_dev;
+    const bool early = a.early_cache && !a.prefill;
+    if (!early) pdl_wait();
+    const int32_t pos_seen = *pos_ptr;
+    place(pos_seen);
     stage(0, min(n_loc, PR), true);                // requested before anything else is computed
+    float ca[VEC], sa[VEC];
+    fa_rope_angles<VEC>(ca, sa, lane, (float)pos, a.inv_freq);
+    if (early) {
+        pdl_wait();
+        const int32_t pos_now = *pos_ptr;
+        if (pos_now != pos_seen) {                 // the same value in every thread of the cluster
+            fa_cp_wait_all();
+            __syncthreads();
+            place(pos_now);
+            stage(0, min(n_loc, PR), true);
+            fa_rope_angles<VEC>(ca, sa, lane, (float)pos, a.inv_freq);
+        }
+    }
 
     // ---- rotation: warp w prepares query head w of the group, warp 0 also the new token's k and v ----
     {
-        float ca[VEC], sa[VEC];
-        fa_rope_angles<VEC>(ca, sa, lane, (float)pos, a.inv_freq);
         for (uint32_t hh = warp; hh < (uint32_t)GT; hh += FA_WARPS) {
             float x[VEC];
             const uint16_t *q = a.q + (size_t)b * a.src_stride + (size_t)(h0 + hh) * hd + lane * VEC;
@@ -277,19 +310,15 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
     for (int o = 16; o >= GT; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
     if (lane < GT) sh[warp][lane] = mx;
     __syncthreads();
+    asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory");
     if (threadIdx.x < GT) {
         float m = -INFINITY;
         for (int w = 0; w < FA_WARPS; w++) m = fmaxf(m, sh[w][threadIdx.x]);
-        xch[0][threadIdx.x] = m;
+        fa_scatter(cluster, &xall[0][rank][threadIdx.x], S, m);
     }
     cluster.sync();
-    {
-        float v[8];
-        fa_gather(v, cluster, &xch[0][hm], S, -INFINITY);
-        mx = -INFINITY;
-#pragma unroll
-        for (int r = 0; r < 8; r++) mx = fmaxf(mx, v[r]);
-    }
+    mx = -INFINITY;
+    for (uint32_t r = 0; r < S; r++) mx = fmaxf(mx, xall[0][r][hm]);
 
     // ---- exp and its sum: local in warp order, then across the cluster in rank order -------------
     float es = 0.0f;
@@ -305,15 +334,12 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
     if (threadIdx.x < GT) {
         float t = 0.0f;
         for (int w = 0; w < FA_WARPS; w++) t += sh[w][threadIdx.x];
-        xch[1][threadIdx.x] = t;
+        fa_scatter(cluster, &xall[1][rank][threadIdx.x], S, t);
     }
     cluster.sync();
     if (threadIdx.x < GT) {
-        float v[8];
-        fa_gather(v, cluster, &xch[1][threadIdx.x], S, 0.0f);
         float t = 0.0f;
-#pragma unroll
-        for (int r = 0; r < 8; r++) t += v[r];  // rank order
+        for (uint32_t r = 0; r < S; r++) t += xall[1][r][threadIdx.x];  // rank order
         sinv[threadIdx.x] = 1.0f / (t + 1e-10f);
     }
     __syncthreads();
@@ -357,27 +383,26 @@ __global__ void __launch_bounds__(FA_THREADS) attn_fused_kernel(const FusedAttnA
 #pragma unroll
         for (int i = 0; i < VEC; i++) part[(size_t)warp * (GT * hd) + hh * hd + lane * VEC + i] = ac[hh][i];
     __syncthreads();
-    for (uint32_t t = threadIdx.x; t < GT * hd; t += FA_THREADS) {
+    // Output element t is finished by rank t / per: every CTA adds its warps' partial sums and stores the result
+    // into slot [its rank] of the finishing CTA's receive buffer; after one cluster barrier the finisher adds the
+    // slots in rank order from its own shared memory.  Nobody touches a peer's memory after that barrier.
+    const uint32_t n_out = nhl * hd, per = (n_out + S - 1) / S;
+    for (uint32_t t = threadIdx.x; t < n_out; t += FA_THREADS) {
         float v = 0.0f;
 #pragma unroll
         for (uint32_t w = 0; w < (uint32_t)FA_WARPS; w++) v += part[(size_t)w * (GT * hd) + t];
-        part[t] = v;  // row 0: only this thread reads and writes element t of it
+        const uint32_t owner = t / per;
+        *cluster.map_shared_rank(recv + rank * per + (t - owner * per), owner) = v;
     }
     cluster.sync();
-    // every CTA of the cluster finishes its own slice of the outputs: the partial sums of all ranks, in rank order
     {
-        const uint32_t n_out = nhl * hd, per = (n_out + S - 1) / S;
         const uint32_t t_end = min(n_out, (rank + 1) * per);
         for (uint32_t t = rank * per + threadIdx.x; t < t_end; t += FA_THREADS) {
-            float v[8];
-            fa_gather(v, cluster, &part[t], S, 0.0f);
             float o = 0.0f;
-#pragma unroll
-            for (int r = 0; r < 8; r++) o += v[r];
+            for (uint32_t r = 0; r < S; r++) o += recv[r * per + (t - rank * per)];  // rank order
             a.out[(size_t)b * a.nh * hd + (size_t)h0 * hd + t] = fa_f2h(o);
         }
     }
-    cluster.sync();  // peers keep their shared memory alive until every rank has read it
 }
 
 bool attn_fused_eligible(const AttnArgs &a) {
@@ -426,7 +451,9 @@ __global__ void __launch_bounds__(256) prefill_kv_kernel(const uint16_t *__restr
 static size_t fa_smem_bytes(uint32_t chunk_cap, uint32_t gt, uint32_t hd) {
     // scores, rotated q, the new token's k and v, and the key/value tiles (48 KB; the per-warp partial
     // outputs, at most 32 KB, reuse the tiles' space)
-    return (((size_t)chunk_cap * gt + 3) & ~(size_t)3) * 4 + (size_t)gt * hd * 4 + 2 * hd * 2 + 2 * (size_t)fa_tile_rows(hd) * hd * 2;
+    // and the receive buffer of the final reduction (one slice per rank, together at most gt*hd + 8 floats)
+    return (((size_t)chunk_cap * gt + 3) & ~(size_t)3) * 4 + (size_t)gt * hd * 4 + 2 * hd * 2 + 2 * (size_t)fa_tile_rows(hd) * hd * 2 +
+           ((size_t)gt * hd + 8) * 4;
 }
 
 template <int VEC, int GT>
@@ -512,6 +539,7 @@ int launch_attn_fused(prism_cuda_ctx *ctx, const AttnArgs &a, const uint16_t *k_
     fa.rope_k = rope_k;
     fa.prefill = a.prefill; fa.seq = a.prefill_seq;
     fa.page_tbl = a.page_tbl; fa.page_shift = a.page_shift; fa.tbl_stride = a.tbl_stride;
+    fa.early_cache = a.early_cache;
     PRISM_TRY(rope_table(ctx, a.hd, rope_base, &fa.inv_freq));
     if (a.prefill) {
         // the tokens' keys and values go to the cache first; the attention launch then finds them there

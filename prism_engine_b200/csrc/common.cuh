@@ -334,6 +334,9 @@ struct AttnArgs {
     // fused kernel only: paged cache (page table on the device, [sequence][tbl_stride] page numbers of 2^page_shift rows)
     const int32_t *page_tbl = nullptr;
     uint32_t page_shift = 0, tbl_stride = 0;
+    // fused kernel only: the caller guarantees that the kernel enqueued right before this one does not write the
+    // cache (a decode step: the q/k/v projection), so cached rows may be requested before the dependency wait
+    uint32_t early_cache = 0;
 };
 int launch_attention(prism_cuda_ctx *ctx, const AttnArgs &a);
 struct KvAppendArgs {

@@ -215,6 +215,7 @@ static int enqueue_attention(prism_cuda_engine *e, uint32_t l, uint32_t li) {
     aa.nh = e->nh_l; aa.nkv = e->nkv_l; aa.hd = e->hd; aa.batch = B;
     aa.seq_stride = e->kv_seq_stride; aa.int8 = c.kv_int8; aa.max_seq = e->kv_slots;
     aa.page_tbl = e->page_tbl; aa.page_shift = e->page_shift; aa.tbl_stride = e->pages_per_seq;
+    aa.early_cache = 1;  // what precedes this launch in a step is the q/k/v projection, which leaves the cache alone
     if (ctx->fuse != 0 && attn_fused_eligible(aa)) return launch_attn_fused(ctx, aa, e->k, e->v, c.rope_k, base);
     if (e->page_tbl) return fail(ctx, PRISM_E_STATE, "the paged KV cache needs the fused attention kernel (option fuse = 1)");
     if (c.rope_k) PRISM_TRY(launch_rope(ctx, e->k, e->kvd_l, pos_dev, 0, e->hd, base, B, qs));

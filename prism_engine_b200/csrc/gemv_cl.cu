@@ -28,7 +28,8 @@ constexpr int CL_THREADS = CL_WARPS * 32;
 constexpr int CL_PF = 8;                              // index chunks a warp holds in registers
 constexpr int CL_MAX_CHUNKS = CL_WARPS * CL_PF;       // chunks of one CTA's K part (2048 weights per row)
 constexpr int CL_X_BYTES = CL_MAX_CHUNKS * 64;
-constexpr size_t CL_SMEM_BYTES = SK_TBL_BYTES + CL_X_BYTES + CL_WARPS * 64 * 4 + 64 * 4 + 32;
+constexpr int CL_MAX_S = 8;                           // largest cluster
+constexpr size_t CL_SMEM_BYTES = SK_TBL_BYTES + CL_X_BYTES + CL_WARPS * 64 * 4 + CL_MAX_S * 64 * 4 + 32;
 
 struct ClArgs {
     const uint8_t *idx1, *idx2;   // index arrays the two half-blocks of a block come from
@@ -63,8 +64,12 @@ __global__ void __launch_bounds__(CL_THREADS) lut_gemv_cl_kernel(const ClArgs a)
     uint32_t *tbl = reinterpret_cast<uint32_t *>(smem);
     uint16_t *xs = reinterpret_cast<uint16_t *>(smem + SK_TBL_BYTES);
     float *red = reinterpret_cast<float *>(smem + SK_TBL_BYTES + CL_X_BYTES);  // [CL_WARPS][64]
-    float *csum = red + CL_WARPS * 64;                                          // [64]: this CTA's sums, read by rank 0
-    float &s_inv = *(csum + 64);
+    float *cpush = red + CL_WARPS * 64;   // [CL_MAX_S][64]: on rank 0 the sums of every CTA of the cluster, stored there by their owners
+    float &s_inv = *(cpush + CL_MAX_S * 64);
+    // First half of a cluster barrier whose only purpose is that every CTA of the cluster has started before
+    // anyone stores into rank 0's shared memory; its second half sits right before those stores and has long
+    // completed by then.
+    if (a.s > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory");
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t s = a.s, rank = blockIdx.x % s, blk = blockIdx.x / s, bat = blockIdx.y;
@@ -188,11 +193,14 @@ __global__ void __launch_bounds__(CL_THREADS) lut_gemv_cl_kernel(const ClArgs a)
         for (int w = 0; w < CL_WARPS; w++) sum += red[w * 64 + tid];
     }
     if (s > 1) {
-        if (tid < 64) csum[tid] = sum;
+        // every CTA stores its 64 sums into slot [rank] of rank 0's shared memory; after one cluster barrier
+        // rank 0 adds the slots in rank order from its own memory, and nobody reads a peer's memory after it
+        asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory");
+        if (tid < 64) *cluster.map_shared_rank(cpush + rank * 64 + tid, 0) = sum;
         cluster.sync();
         if (rank == 0 && tid < 64) {
             sum = 0.0f;
-            for (uint32_t r = 0; r < s; r++) sum += *cluster.map_shared_rank(&csum[tid], r);  // rank order
+            for (uint32_t r = 0; r < s; r++) sum += cpush[r * 64 + tid];  // rank order
         }
     }
     if (rank == 0) {
@@ -214,7 +222,7 @@ __global__ void __launch_bounds__(CL_THREADS) lut_gemv_cl_kernel(const ClArgs a)
             if (tid < 64) {  // this CTA has only this block: deliver and finish at once
                 const unsigned int e = tp_epoch(a.tp);
                 const uint32_t hb = (tid >> 5) ? hb2 : hb1;
-                uint16_t *lst = reinterpret_cast<uint16_t *>(csum) + (tid >> 5) * 2;  // rank 0's own sums are not needed any more
+                uint16_t *lst = reinterpret_cast<uint16_t *>(&s_inv + 1) + (tid >> 5) * 2;  // spare words behind the norm factor
                 tp_deliver(a.tp, e, hb, lane, sum);
                 if (lane == 0 && !a.tp.deliver_only) lst[0] = (uint16_t)hb;
                 __syncwarp();
@@ -234,7 +242,6 @@ __global__ void __launch_bounds__(CL_THREADS) lut_gemv_cl_kernel(const ClArgs a)
             }
         }
     }
-    if (s > 1) cluster.sync();  // peers keep their shared memory alive until rank 0 has read it
 }
 
 template <int MODE>
