@@ -163,7 +163,6 @@ class CpuSample:
         self.xs = {k: synth.make_activation(k, seed=k) for _, k in self.shapes}
         self.vrows = max(64, V // head_frac // 64 * 64)
         self.head = synth.make_payload(self.vrows, H, 4, seed=99)
-        self.fraction = (n_sets * 1.0 / arch["num_layers"] + self.vrows / V) / 2  # rough share of a step actually run
         self.sample = (f"SAMPLE, extrapolated: 7 palettized GEMVs of {n_sets} distinct layers (mean x {arch['num_layers']} layers) + "
                        f"{self.vrows}/{V} LM-head rows (scaled), lut_gemv restatement over {threads} threads")
 
@@ -393,7 +392,7 @@ def run_ours(args):
         "config": workload_config(args, arch),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_8tbs_nominal": achieved / 8000.0,
-                     "kernel": "lut_gemv_ws_kernel (lut_gemv_sk_kernel for small matrices)", "launches_timed": gemv_launches,
+                     "kernel": "lut_gemv_ws_kernel (lut_gemv_cl_kernel / lut_gemv_sk_kernel for small matrices)", "launches_timed": gemv_launches,
                      "avg_launch_us": gemv_ms * 1e3 / max(gemv_launches, 1),
                      "algorithmic_bytes_per_launch": gemv_bytes / max(gemv_launches, 1),
                      "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE and TRAFFIC_PER_ALGORITHMIC_BYTE * gemv_bytes / max(gemv_launches, 1)},

@@ -67,8 +67,10 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
  * the kernels of a decode step, so a kernel's weight-only prologue overlaps its predecessor),
  * "batch_gemv_max" (default 8: decode batches up to this many sequences stream the weights once
  * through the batched GEMV, in groups of 8; larger batches use the tcgen05 GEMM),
- * "attn_cluster" (0 = from max_seq, default; 1/2/4/8 CTAs per head and sequence in the fused
+ * "attn_cluster" (0 = from max_seq, default; 1/2/4/8 CTAs per KV head and sequence in the fused
  * attention kernel),
+ * "attn_group" (0 = from the shape, default; 1/2/4/8 = most query heads of a KV group one cluster of the
+ * fused attention kernel serves),
  * "tp_peer_ar" (0/1, default 1: tensor-parallel partial sums are reduced by one kernel through
  * peer memory instead of ncclAllReduce + add; set it identically on every rank),
  * "sk_min_chunks" (default 8: fewest 1 KB index chunks the GEMV gives one CTA of a small matrix),

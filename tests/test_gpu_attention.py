@@ -66,6 +66,18 @@ def test_fused_attention_72b_head_layout(backend, oracle):
     _case(backend, oracle, 128, nh=64, nkv=8, cluster=0, ctx_len=515, rope_k=True, base=1e6, seed=9)
 
 
+@pytest.mark.parametrize("group", [1, 2, 4])
+def test_fused_attention_fewer_heads_per_cluster(backend, oracle, group):
+    # the head group split over several clusters: 7 query heads per KV head (the 0.5B layout, which the launcher
+    # splits by itself) and 8, with the last cluster of a group only partly filled when 7 is not a multiple
+    backend.set_option("attn_group", group)
+    try:
+        _case(backend, oracle, 64, nh=14, nkv=2, cluster=2, ctx_len=141, rope_k=True, base=1e6, seed=11)
+        _case(backend, oracle, 128, nh=16, nkv=2, cluster=4, ctx_len=300, rope_k=True, base=1e6, seed=12)
+    finally:
+        backend.set_option("attn_group", 0)
+
+
 def test_kv_entry_points_mirror_the_backend_cache(backend, oracle):
     """append_kv ignores rows outside the cache (as MetalBackend::append_kv does); the C call reports them."""
     import prism_engine_b200 as p
