@@ -542,7 +542,9 @@ def config4_gemm(env, be, bits=4):
         "roofline": {"bound": "tensor", "achieved": big, "peak": sustained, "unit": "TFLOP/s", "frac": big / sustained,
                      "frac_of_burst": big / burst, "layer_frac": value / sustained, "layer_frac_of_burst": value / burst,
                      "peak_kind": f"of {kind} sustained bf16 cuBLAS {sustained} (burst {burst}); each shape ran >= 0.3 s back to back",
-                     "kernel": "lut_gemm_tc5_kernel", "launch": "gate 18944x3584, M=2048", "traffic": None},
+                     "kernel": "lut_gemm_tc5_kernel", "launch": "gate 18944x3584, M=2048",
+                     # DRAM read + write bytes of one gate launch in the ncu capture summarised under profiles/
+                     "traffic": 164.3e6 if bits == 4 else None, "traffic_unit": "bytes per gate launch (algorithmic 126.8e6)"},
         "per_gemm": per,
         "e2e": {"value": 2.0 * m_tok * I * H / e2e_s / 1e12, "unit": "TFLOP/s (gate GEMM through prism_cuda_gemm, host buffers)",
                 "h2d_bytes_per_step": int(Xh.nbytes), "d2h_bytes_per_step": m_tok * I * 2},
