@@ -89,7 +89,8 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
  * 0 = the GEMV leaves fp32 partial sums, one kernel pushes them to the peers and reduces; 1 = the GEMV's epilogue
  * stores its sums into every rank's receive area, a small kernel publishes flags, waits and reduces; 2 = flags,
  * wait and reduction inside the GEMV kernel too; 3 (default) = the GEMV's epilogue stores 8-byte words that carry
- * their epoch, a small kernel polls the words and reduces -- no flags and no system-scope fence.  Set it
+ * their epoch, a small kernel polls the words and reduces -- no flags and no system-scope fence; 4 = flagged
+ * words polled and reduced at the end of the GEMV kernel itself (matmul and all-reduce in one kernel).  Set it
  * identically on every rank),
  * "cimage_cache" (0/1, default 0: prism_cuda_engine_load_cimage keeps the re-laid image beside the file).
  * A captured decode graph is rebuilt after any option change. */

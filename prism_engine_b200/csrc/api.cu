@@ -271,7 +271,7 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
     } else if (!strcmp(key, "tp_peer_ar")) {
         ctx->tp_peer_ar = value ? 1 : 0;
     } else if (!strcmp(key, "tp_fused_ar")) {
-        if (value < 0 || value > 3) return fail(ctx, PRISM_E_ARG, "tp_fused_ar must be 0, 1, 2 or 3");
+        if (value < 0 || value > 4) return fail(ctx, PRISM_E_ARG, "tp_fused_ar must be 0, 1, 2, 3 or 4");
         ctx->tp_fused_ar = (int)value;
     } else if (!strcmp(key, "pdl")) {
         ctx->pdl = value ? 1 : 0;

@@ -121,7 +121,8 @@ struct prism_cuda_ctx {
     // option "tp_fused_ar" (batch-1 decode): 0 = GEMV writes fp32 partial sums, a separate kernel pushes and reduces them;
     // 1 = the GEMV epilogue stores its sums straight into every rank's receive area, a small kernel publishes flags and
     // reduces; 2 = flags, wait and reduction inside the GEMV kernel too; 3 = the GEMV epilogue stores 8-byte words
-    // {sum, epoch} into every rank's flagged-word area, a small kernel polls the words themselves and reduces
+    // {sum, epoch} into every rank's flagged-word area, a small kernel polls the words themselves and reduces; 4 = the
+    // flagged words are polled and reduced at the end of the GEMV kernel itself
     int tp_fused_ar = 3;
     std::string tp_peer_reason;        // why the peer path is unavailable ("" when it is set up)
     bool tp_loopback = false;          // prism_cuda_tp_init_loopback: every "peer" is this GPU's own receive area

@@ -183,13 +183,13 @@ int tp_fill_push(prism_cuda_ctx *ctx, const LutTensor &t, TpPush *out) {
     out->spin_limit = wait_limit(ctx, TP_AR_SPIN_LIMIT);
     out->n_units = t.n_hb;
     out->deliver_only = (ctx->tp_fused_ar == 1 || ctx->tp_fused_ar == 3) ? 1u : 0u;
-    out->ll_off = ctx->tp_fused_ar == 3 ? (uint32_t)tp_ll_offset(ctx->tp_world) : 0u;
+    out->ll_off = ctx->tp_fused_ar >= 3 ? (uint32_t)tp_ll_offset(ctx->tp_world) : 0u;
     if (out->ll_off && t.m_pad > TP_LL_CAP) return fail(ctx, PRISM_E_ARG, "fused all-reduce: output vector too long for the flagged-word area");
     return PRISM_OK;
 }
 
 bool gemv_tp_ok(prism_cuda_ctx *ctx, const LutTensor &t) {
-    if (ctx->tp_fused_ar == 3 && t.m_pad > TP_LL_CAP) return false;
+    if (ctx->tp_fused_ar >= 3 && t.m_pad > TP_LL_CAP) return false;
     return ctx->tp_world > 1 && ctx->tp_peer_ar && ctx->tp_fused_ar && ctx->tp_cap != 0 && ctx->gemv_variant == 1 && t.bits == 4 &&
            t.k % 32 == 0 && t.k >= 32 && t.n_hb <= (uint32_t)TP_AR_MAX_CTAS && t.m_pad <= ctx->tp_cap;
 }

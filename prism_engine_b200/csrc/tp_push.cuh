@@ -81,6 +81,34 @@ __device__ __forceinline__ void tp_finish(const TpPush &tp, unsigned int e, cons
                                           uint32_t m, uint16_t *h, unsigned int *err) {
     if (n == 0 || tp.deliver_only) return;
     const uint32_t slot = e & 1;
+    if (tp.ll_off) {
+        // flagged words: nothing to publish; poll the `world` words of each row (bounded), add in rank order
+        const unsigned long long *ll = reinterpret_cast<const unsigned long long *>(reinterpret_cast<const char *>(tp.recv) + tp.ll_off) +
+                                       (size_t)slot * tp.world * TP_LL_CAP;
+        for (uint32_t i = 0; i < n; i++) {
+            const uint32_t row = list[i] * 32 + lane;
+            float s = 0.0f;
+            for (uint32_t r = 0; r < tp.world; r++) {
+                const unsigned long long *p = ll + (size_t)r * TP_LL_CAP + row;
+                unsigned long long v;
+                unsigned int polls = 0;
+                for (;;) {
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];\n" : "=l"(v) : "l"(p) : "memory");
+                    if ((unsigned int)(v >> 32) == e) break;
+                    if (++polls > tp.spin_limit) {
+                        atomicExch(err, 3u);
+                        break;
+                    }
+                    if (polls > 64) __nanosleep(polls > 4096 ? 500 : 50);
+                }
+                s += __uint_as_float((unsigned int)v);
+            }
+            if (row < m) {
+                const float o = __half2float(__float2half_rn(s)) + __half2float(__ushort_as_half(h[row]));
+                h[row] = __half_as_ushort(__float2half_rn(o));
+            }
+        }
+    } else {
     __threadfence_system();
     __syncwarp();
     if (lane < tp.world) {
@@ -109,6 +137,7 @@ __device__ __forceinline__ void tp_finish(const TpPush &tp, unsigned int e, cons
             const float o = __half2float(__float2half_rn(s)) + __half2float(__ushort_as_half(h[row]));
             h[row] = __half_as_ushort(__float2half_rn(o));
         }
+    }
     }
     // ---- the warp that finishes the last half-block advances the epoch ----
     __syncwarp();

@@ -83,10 +83,11 @@ def _worker(rank, world, port, q, peer_ar, wide=False, batch=2, fused=1):
 @pytest.mark.timeout(1500)
 # fused (one sequence only): 0 = GEMV leaves fp32 partial sums, a kernel pushes and reduces them; 1 = the GEMV delivers
 # into the peers' receive areas, a kernel publishes flags and reduces; 2 = everything inside the GEMV kernel; 3 = the GEMV delivers 8-byte words
-# that carry their epoch, a kernel polls the words and reduces (no flags, no fence)
+# that carry their epoch, a kernel polls the words and reduces (no flags, no fence); 4 = flagged words polled and reduced
+# at the end of the GEMV kernel itself
 @pytest.mark.parametrize("peer_ar,fused,wide,batch", [(1, 1, False, 2), (0, 1, False, 2), (1, 0, False, 1), (1, 1, False, 1),
                                                        (1, 2, False, 1), (0, 1, False, 1), (1, 1, True, 1), (1, 2, True, 1),
-                                                       (1, 3, False, 1), (1, 3, True, 1), (1, 3, False, 2)])
+                                                       (1, 3, False, 1), (1, 3, True, 1), (1, 3, False, 2), (1, 4, False, 1), (1, 4, True, 1)])
 def test_tp2_matches_single_gpu_and_oracle(peer_ar, fused, wide, batch):
     import torch
 
