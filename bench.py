@@ -20,6 +20,7 @@ clocks:
   token_checksum    CRC of the first 32 greedy tokens of the timed model (compare across N)
   config3           N = 1: Qwen2.5-0.5B decode, 128-token prompt, 256 generated tokens
   config4           N = 1: the six prefill GEMMs of a Qwen2.5-7B layer, M = 2048, N(0,1) activations
+  config4_2bit      N = 1: the same six GEMMs with 2-bit indices and a 4-entry palette per row
   lut_gemv_0p5b_shapes   N = 1: GEMV / fused gate-up / MLP at the 4864x896 shapes, working set > L2
   lut_gemv_decode_shapes N = 1: the five GEMV launch shapes of the workload's decode step, each timed alone
   cpu_baseline      N = 1: the CPU restatement of the reference's path on the host cores (a sample)
@@ -418,6 +419,7 @@ def run_ours(args):
         if not args.no_configs:
             line["config3"] = config3_decode(env, be)
             line["config4"] = config4_gemm(env, be)
+            line["config4_2bit"] = config4_gemm(env, be, bits=2)
         if not args.no_gemv_shapes:
             line["lut_gemv_0p5b_shapes"] = small_shape_bandwidth(env, be, peak)
             line["lut_gemv_decode_shapes"] = decode_shape_bandwidth(env, be, arch, peak)

@@ -488,7 +488,11 @@ bool ws_preferred(prism_cuda_ctx *ctx, const LutTensor &t, bool swiglu, uint32_t
 
 // Chooses the partition (see SkPart) for one activation vector of a batch: one CTA per SM.
 SkPart ws_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch) {
-    const uint32_t slots = (uint32_t)ctx->sm_count / (batch ? batch : 1);
+    uint32_t slots = (uint32_t)ctx->sm_count / (batch ? batch : 1);
+    // Almost as many blocks as CTAs, rows short enough that a block is a few microseconds of streaming: one
+    // whole block per CTA on n_blocks CTAs.  The idle SMs cost less than what every CTA otherwise pays for
+    // covering parts of two blocks (a second table, partial sums, the arrival and the fix-up at the end).
+    if (ctx->ws_whole_blocks && n_blocks < slots && n_blocks * 100 >= slots * 85 && n_chunks <= (uint32_t)ctx->ws_whole_blocks) slots = n_blocks;
     return sk_choose_partition(n_blocks, n_chunks, slots, (uint32_t)ctx->sk_stream_chunks, (uint32_t)ctx->sk_min_chunks, 96);
 }
 
