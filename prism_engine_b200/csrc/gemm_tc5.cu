@@ -208,6 +208,10 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
                 }
                 asm volatile("bar.sync %0, 256;\n" ::"r"(1 + pair) : "memory");
             }
+            // Everything so far read weights only.  The waits below depend on the activations, which come after the
+            // loader's dependency wait: wait for the same dependency first, so that no bounded wait runs while the
+            // kernel before this one (under tensor parallelism: a late peer) is still at work.
+            if (w == blockIdx.x) pdl_wait();
             // ---- K loop: lookups -> TMEM stage -> signal the MMA thread ----
             // a stage is CPS consecutive chunks; warp slot j takes the stages j, j+4, ...
             const uint32_t nst = nch / CPS;
@@ -273,6 +277,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) lut_gemm_tc5_kernel(const GemmA
         const uint32_t idesc = t5::idesc_f16(128, NT);
         const uint32_t x_addr = smem_base + GM_X_OFF;
         uint32_t n = 0, nx = 0, ti = 0;
+        pdl_wait();  // see the dequantising warps: no bounded wait before the dependency is met
         for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x, ti++) {
             t5::mbar_wait_bounded(b_dempty, (ti & 1) ^ 1, err_flag);  // epilogue of the previous tile has read D
             t5::fence_after();

@@ -158,6 +158,10 @@ __device__ __forceinline__ void wb_compute(const SkArgs &a, uint8_t *smem, uint3
 #pragma unroll
                 for (int i = 0; i < 2; i++) acc[p][i][0] = acc[p][i][1] = acc[p][i][2] = acc[p][i][3] = 0.f;
         }
+        // The first stage's x comes after the builders' dependency wait, which lasts as long as the kernel before
+        // this one -- under tensor parallelism as long as a late peer.  The bounded hand-over wait must not run
+        // during that time: wait for the same dependency first.
+        if (t == 0) pdl_wait();
         ws_wait(bar_full + 8 * xbuf, par, err_flag);
         const uint32_t lane_off = lane * 4 | (tb << 16);
         uint32_t x_off = xbuf * WB_X_BYTES + (lane >> 4) * Geo::ROW_BYTES + cw * 64;
