@@ -69,14 +69,15 @@ __device__ __forceinline__ void ws_chunk(float (&acc)[2][4], uint4 &w1, uint4 &w
     sk_mma(acc[1], A1[4], A1[5], A1[6], A1[7], xb[1].z, xb[1].w);
 }
 
-// The pair tables of the CTA's FIRST block, built by all warps together (compute warps would
-// otherwise idle until the builders have made it: at kernel start nothing else can run yet).  Warp
-// gw of the CTA's WS_NC + WS_NB takes the (hi nibble, half-block) combinations gw, gw + 24; lane L
-// writes its own bank.  Entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]}.
+// The pair tables of the CTA's FIRST block, built by the compute warps (they would otherwise idle until the
+// builders have made it) while the builders wait for the stream dependency and stage the first slice of x:
+// the two halves of the prologue run side by side.  Compute warp gw takes the (hi nibble, half-block)
+// combinations gw, gw + WS_NC of the 32 (at most two per warp); lane L writes its own bank.
+// Entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]}.
 __device__ __forceinline__ void ws_first_table(const SkArgs &a, uint8_t *smem, const WsStage &st, uint32_t gw, uint32_t lane) {
     const uint32_t hb1 = a.hb_mul * st.blk, hb2 = hb1 + a.hb_add2;
     uint32_t *tbl = reinterpret_cast<uint32_t *>(smem + (st.seg & 1) * WS_TBL_BYTES);
-    for (uint32_t c = gw; c < 32; c += WS_NC + WS_NB) {
+    for (uint32_t c = gw; c < 32; c += WS_NC) {
         const uint32_t hi = c >> 1, h = c & 1;
         const uint32_t row = (h == 0 ? hb1 : hb2) * 32 + lane;
         const uint16_t *prow = (h == 0 ? a.pal1 : a.pal2) + (size_t)row * 16;
@@ -126,7 +127,7 @@ __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint3
         src.advance(WS_PF * WS_NC * 512);  // from here on: the chunk WS_PF steps ahead
         if (t == 0) {  // with the first index chunks in flight: this warp's share of the first pair table
             ws_first_table(a, smem, st, cw, lane);
-            __syncthreads();  // every warp of the CTA, once (the builders meet it in their first stage)
+            asm volatile("bar.sync 2, %0;\n" ::"n"(WS_NC * 32) : "memory");  // the compute warps only: they are the table's readers
         }
         if (st.first) {
 #pragma unroll
@@ -289,8 +290,7 @@ __device__ __forceinline__ void ws_build(const SkArgs &a, uint8_t *smem, uint32_
         hist[xbuf] = st;
         bool staged = false;
         if (t == 0) {
-            ws_first_table(a, smem, st, WS_NC + bw, lane);
-            __syncthreads();  // the whole CTA: the first table is complete
+            // the first block's table is the compute warps' job (ws_first_table)
         } else if (st.first) {
             // pair tables: entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]}; builder warp w writes the
             // entries with hi = w, w + WS_NB, ...; lane L writes its own bank.
