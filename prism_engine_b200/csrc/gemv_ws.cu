@@ -69,31 +69,6 @@ __device__ __forceinline__ void ws_chunk(float (&acc)[2][4], uint4 &w1, uint4 &w
     sk_mma(acc[1], A1[4], A1[5], A1[6], A1[7], xb[1].z, xb[1].w);
 }
 
-// The pair tables of the CTA's FIRST block, built by the compute warps (they would otherwise idle until the
-// builders have made it) while the builders wait for the stream dependency and stage the first slice of x:
-// the two halves of the prologue run side by side.  Compute warp gw takes the (hi nibble, half-block)
-// combinations gw, gw + WS_NC of the 32 (at most two per warp); lane L writes its own bank.
-// Entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]}.
-__device__ __forceinline__ void ws_first_table(const SkArgs &a, uint8_t *smem, const WsStage &st, uint32_t gw, uint32_t lane) {
-    const uint32_t hb1 = a.hb_mul * st.blk, hb2 = hb1 + a.hb_add2;
-    uint32_t *tbl = reinterpret_cast<uint32_t *>(smem + (st.seg & 1) * WS_TBL_BYTES);
-    for (uint32_t c = gw; c < 32; c += WS_NC) {
-        const uint32_t hi = c >> 1, h = c & 1;
-        const uint32_t row = (h == 0 ? hb1 : hb2) * 32 + lane;
-        const uint16_t *prow = (h == 0 ? a.pal1 : a.pal2) + (size_t)row * 16;
-        const uint4 p0 = *reinterpret_cast<const uint4 *>(prow);
-        const uint4 pp = *reinterpret_cast<const uint4 *>(prow + 8);
-        const uint32_t cbp[8] = {p0.x, p0.y, p0.z, p0.w, pp.x, pp.y, pp.z, pp.w};
-        const uint32_t hi_pair = reinterpret_cast<const uint32_t *>(prow)[hi >> 1];  // {pal[hi&~1], pal[hi|1]}
-        const uint32_t hsel = (hi & 1) ? 0x7600u : 0x5400u;
-#pragma unroll
-        for (int lo = 0; lo < 16; lo++) {
-            const uint32_t v = __byte_perm(cbp[lo >> 1], hi_pair, hsel | ((lo & 1) ? 0x32u : 0x10u));
-            tbl[((uint32_t)lo + 16u * hi) * 64 + h * 32 + lane] = v;
-        }
-    }
-}
-
 // ---- compute warps --------------------------------------------------------------------------------
 template <int SBASE>
 __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint32_t smem_base, uint32_t u_begin,
@@ -126,7 +101,7 @@ __device__ __forceinline__ void ws_compute(const SkArgs &a, uint8_t *smem, uint3
 #undef WS_LOAD
         src.advance(WS_PF * WS_NC * 512);  // from here on: the chunk WS_PF steps ahead
         if (t == 0) {  // with the first index chunks in flight: this warp's share of the first pair table
-            ws_first_table(a, smem, st, cw, lane);
+            ws_first_table(a, reinterpret_cast<uint32_t *>(smem + (st.seg & 1) * WS_TBL_BYTES), st.blk, cw, WS_NC, lane);
             asm volatile("bar.sync 2, %0;\n" ::"n"(WS_NC * 32) : "memory");  // the compute warps only: they are the table's readers
         }
         if (st.first) {

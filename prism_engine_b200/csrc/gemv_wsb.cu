@@ -152,6 +152,10 @@ __device__ __forceinline__ void wb_compute(const SkArgs &a, uint8_t *smem, uint3
             if (1 < nj) { q1[1] = src.load1<Geo::NC * 512>(); q2[1] = src.load2<Geo::NC * 512>(); }
             src.advance(2 * Geo::NC * 512);  // from here on: the chunk two steps ahead
         }
+        if (t == 0) {  // with the first index chunks in flight: the first block's pair table (see ws_first_table)
+            ws_first_table(a, reinterpret_cast<uint32_t *>(smem + tb * WB_TBL_BYTES), st.blk, cw, Geo::NC, lane);
+            asm volatile("bar.sync 2, %0;\n" ::"n"(Geo::NC * 32) : "memory");
+        }
         if (st.first) {
 #pragma unroll
             for (int p = 0; p < NBP; p++)
@@ -335,7 +339,7 @@ __device__ __forceinline__ void wb_build(const WbArgs &wa, uint8_t *smem, uint32
             if (hist[xbuf].last) wb_finish<MODE, NBP>(wa, smem, smem_base, hist[xbuf], bt, cta, G);
         }
         hist[xbuf] = st;
-        if (st.first) {
+        if (st.first && t != 0) {  // the first block's table is the compute warps' job
             // pair tables: entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]}; builder warp w writes the
             // entries with hi = w, w + WB_NB, ...; lane L writes its own bank.
             const uint32_t hb1 = a.hb_mul * st.blk, hb2 = hb1 + a.hb_add2;

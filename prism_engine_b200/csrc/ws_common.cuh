@@ -112,6 +112,31 @@ struct WsPrefetch {
     }
 };
 
+// The pair tables of the CTA's FIRST block, built by the compute warps (they would otherwise idle until the
+// builders have made it) while the builders wait for the stream dependency and stage the first slice of x:
+// the two halves of the prologue run side by side.  Compute warp gw of n_warps takes the (hi nibble,
+// half-block) combinations gw, gw + n_warps, ... of the 32; lane L writes its own bank.
+// Entry e = lo | hi<<4 -> half2{pal[lo], pal[hi]}.  The callers close it with a barrier of the compute warps.
+__device__ __forceinline__ void ws_first_table(const SkArgs &a, uint32_t *tbl, uint32_t blk, uint32_t gw, uint32_t n_warps,
+                                               uint32_t lane) {
+    const uint32_t hb1 = a.hb_mul * blk, hb2 = hb1 + a.hb_add2;
+    for (uint32_t c = gw; c < 32; c += n_warps) {
+        const uint32_t hi = c >> 1, h = c & 1;
+        const uint32_t row = (h == 0 ? hb1 : hb2) * 32 + lane;
+        const uint16_t *prow = (h == 0 ? a.pal1 : a.pal2) + (size_t)row * 16;
+        const uint4 p0 = *reinterpret_cast<const uint4 *>(prow);
+        const uint4 pp = *reinterpret_cast<const uint4 *>(prow + 8);
+        const uint32_t cbp[8] = {p0.x, p0.y, p0.z, p0.w, pp.x, pp.y, pp.z, pp.w};
+        const uint32_t hi_pair = reinterpret_cast<const uint32_t *>(prow)[hi >> 1];  // {pal[hi&~1], pal[hi|1]}
+        const uint32_t hsel = (hi & 1) ? 0x7600u : 0x5400u;
+#pragma unroll
+        for (int lo = 0; lo < 16; lo++) {
+            const uint32_t v = __byte_perm(cbp[lo >> 1], hi_pair, hsel | ((lo & 1) ? 0x32u : 0x10u));
+            tbl[((uint32_t)lo + 16u * hi) * 64 + h * 32 + lane] = v;
+        }
+    }
+}
+
 __device__ __forceinline__ void ws_wait(uint32_t bar, uint32_t parity, volatile uint32_t *err_flag) {
     for (uint32_t i = 0; i < WS_WAIT_LIMIT; i++) {
         if (t5::mbar_test(bar, parity)) return;
