@@ -79,9 +79,10 @@ int prism_cuda_synchronize(prism_cuda_ctx *ctx);
  * "cl_max_units" (default 16384: matrices of at most this many (64-row block x 1 KB index chunk) units go to
  * the cluster GEMV, whose CTAs hold all their indices in registers before the previous kernel has
  * finished and reduce through distributed shared memory; 0 = never),
- * "ws_whole_blocks" (default 1024: when a matrix has almost as many 64-row blocks as the GPU has SMs -- at least
- * 85 % -- and rows of at most this many 1 KB chunks, the warp-specialised GEMV gives every CTA one whole block
- * and leaves the other SMs idle, instead of cutting blocks between CTAs; 0 = never),
+ * "ws_whole_blocks" (default 1024: when a matrix has fewer 64-row blocks than the GPU has SMs, but at least
+ * "ws_whole_fill" per 100 (default 50; 85 for batches), and rows of at most this many 1 KB chunks, the
+ * warp-specialised GEMV gives every CTA one whole block and leaves the other SMs idle, instead of cutting
+ * blocks between CTAs; 0 = never),
  * "wait_limit_polls" (default 0 = built-in, about fifteen seconds: polls after which a kernel stops
  * waiting for a tensor-parallel peer or a grid-wide arrival, records a device error code and goes on;
  * the next synchronising call then returns PRISM_E_TIMEOUT and the context stays usable),

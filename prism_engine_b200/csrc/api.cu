@@ -267,6 +267,9 @@ int prism_cuda_set_option(prism_cuda_ctx *ctx, const char *key, int64_t value) {
     } else if (!strcmp(key, "ws_whole_blocks")) {
         if (value < 0 || value > 65536) return fail(ctx, PRISM_E_ARG, "ws_whole_blocks must be in 0..65536");
         ctx->ws_whole_blocks = (int)value;
+    } else if (!strcmp(key, "ws_whole_fill")) {
+        if (value < 1 || value > 100) return fail(ctx, PRISM_E_ARG, "ws_whole_fill must be in 1..100");
+        ctx->ws_whole_fill = (int)value;
     } else if (!strcmp(key, "attn_group")) {
         if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8)
             return fail(ctx, PRISM_E_ARG, "attn_group must be 0, 1, 2, 4 or 8");

@@ -79,6 +79,7 @@ struct prism_cuda_ctx {
     int batch_gemv_max = 8;   // decode batches up to this size use the batched GEMV (groups of 8), larger ones the GEMM
     int attn_cluster = 0;    // CTAs per (head, sequence) of the fused attention kernel; 0: chosen from max_seq
     int ws_whole_blocks = 1024;  // warp-specialised GEMV: one whole block per CTA when there are almost as many blocks as SMs and rows have at most this many chunks; 0: never
+    int ws_whole_fill = 50;  // ... for one activation row, when the matrix has at least this many blocks per 100 SMs
     int attn_group = 0;      // most query heads of a KV group one cluster of the fused attention serves (1/2/4/8); 0: chosen from the shape
     int gemm_reuse_x = 0;    // set by a caller for the second of two GEMMs over the same activations: skip the re-lay
     int pdl = 1;  // programmatic dependent launch between the kernels of the decode chain

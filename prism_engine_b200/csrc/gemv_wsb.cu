@@ -494,7 +494,7 @@ int launch_gemv_wsb(prism_cuda_ctx *ctx, GemvMode mode, const LutTensor &t, cons
         a.hb_mul = 2; a.hb_add2 = 1;
         a.n_blocks = t.n_hb / 2;
     }
-    a.part = ws_partition(ctx, a.n_blocks, a.n_chunks, 1);
+    a.part = ws_partition(ctx, a.n_blocks, a.n_chunks, 1, 85);  // a batch streams longer per block: idle SMs cost more
     const uint32_t G = a.part.G;
     const uint32_t nbp = (batch + 1) / 2;
     PRISM_TRY(ensure_splitk(ctx, (size_t)G * 2 * (2 * nbp) * 64, (size_t)a.n_blocks));

@@ -97,7 +97,7 @@ inline SkPart sk_choose_partition(uint32_t n_blocks, uint32_t n_chunks, uint32_t
 }
 
 // gemv_ws.cu: the partition of the warp-specialised kernels (one CTA per SM)
-SkPart ws_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch);
+SkPart ws_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch, uint32_t fill_pct);
 
 // Arrival on a block's counter: an acq_rel add at gpu scope.  Called by one thread after a CTA-level
 // barrier that follows the CTA's stores of partial sums (the release then covers those stores) and
