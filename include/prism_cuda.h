@@ -108,6 +108,11 @@ uint64_t prism_cuda_launch_count(prism_cuda_ctx *ctx);
  * checked without a device. */
 int prism_cuda_gemv_partition(uint32_t n_blocks, uint32_t n_chunks, uint32_t slots, uint32_t stream_chunks,
                               uint32_t min_chunks, uint32_t *n_ctas, uint32_t *bounds, uint32_t cap);
+/* Host arithmetic only: the `slots` value the warp-specialised GEMV hands to the partition above -- all the
+ * resident CTA slots, or one per block when the matrix has fewer blocks than slots but at least fill_pct per
+ * 100 and rows of at most whole_max_chunks chunks (options "ws_whole_fill", "ws_whole_blocks"). */
+uint32_t prism_cuda_gemv_partition_ctas(uint32_t n_blocks, uint32_t n_chunks, uint32_t slots, uint32_t whole_max_chunks,
+                                        uint32_t fill_pct);
 
 /* ---- weights: the upload loop of MetalBackend::new (engine_impl.rs:123-133)
  *      and PrismEngine::load (engine_impl.rs:597-676) ---------------------- */

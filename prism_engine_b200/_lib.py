@@ -113,6 +113,7 @@ SIGNATURES = {
     "prism_cuda_palettize_dev": (C.c_int, [_vp, _vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _vp]),
     "prism_cuda_gemv_partition": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                             C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.c_uint32]),
+    "prism_cuda_gemv_partition_ctas": (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
     "prism_cuda_tp_all_reduce_dev": (C.c_int, [_vp, _vp, _sz]),
     "prism_cuda_tp_peer_reason": (_cp, [_vp]),
     "prism_cuda_tp_all_reduce_resid_dev": (C.c_int, [_vp, _vp, _vp, _sz]),

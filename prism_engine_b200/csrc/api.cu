@@ -311,6 +311,11 @@ int prism_cuda_gemv_partition(uint32_t n_blocks, uint32_t n_chunks, uint32_t slo
     return PRISM_OK;
 }
 
+uint32_t prism_cuda_gemv_partition_ctas(uint32_t n_blocks, uint32_t n_chunks, uint32_t slots, uint32_t whole_max_chunks,
+                                        uint32_t fill_pct) {
+    return ws_choose_slots(n_blocks, n_chunks, slots, whole_max_chunks, fill_pct);
+}
+
 int prism_cuda_upload_palettized_shard(prism_cuda_ctx *ctx, const char *name, const uint8_t *payload,
                                        size_t len, uint32_t dim_m, uint32_t dim_n, uint32_t bits,
                                        uint32_t row0, uint32_t rows, uint32_t col0, uint32_t cols,

@@ -467,13 +467,13 @@ bool ws_preferred(prism_cuda_ctx *ctx, const LutTensor &t, bool swiglu, uint32_t
 
 // Chooses the partition (see SkPart) for one activation vector of a batch: one CTA per SM.
 SkPart ws_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch, uint32_t fill_pct) {
-    uint32_t slots = (uint32_t)ctx->sm_count / (batch ? batch : 1);
     // Fewer blocks than CTAs, but at least fill_pct per 100, and rows short enough that a block is a few
     // microseconds of streaming: one whole block per CTA on n_blocks CTAs.  The idle SMs cost less than what
     // every CTA otherwise pays for covering parts of two blocks (a second table, partial sums, the arrival and
     // the fix-up at the end): measured down to 54 blocks per 100 SMs for one activation row (10240x8192 cut
     // in two: 11.2 -> 10.9 us; 2 x 3696 x 8192, 78 per 100: 13.6 -> 11.7 us).
-    if (ctx->ws_whole_blocks && n_blocks < slots && n_blocks * 100 >= slots * fill_pct && n_chunks <= (uint32_t)ctx->ws_whole_blocks) slots = n_blocks;
+    const uint32_t slots = ws_choose_slots(n_blocks, n_chunks, (uint32_t)ctx->sm_count / (batch ? batch : 1),
+                                           (uint32_t)ctx->ws_whole_blocks, fill_pct);
     return sk_choose_partition(n_blocks, n_chunks, slots, (uint32_t)ctx->sk_stream_chunks, (uint32_t)ctx->sk_min_chunks, 96);
 }
 

@@ -96,6 +96,17 @@ inline SkPart sk_choose_partition(uint32_t n_blocks, uint32_t n_chunks, uint32_t
     return p;
 }
 
+// How many CTAs the warp-specialised kernels use for n_blocks blocks of rows n_chunks long when `slots` CTAs can
+// be resident: all of them, or -- when the matrix has fewer blocks than that but at least fill_pct per 100, and
+// rows of at most whole_max_chunks chunks (0: never) -- one per block, so that every CTA gets one whole block
+// (sk_choose_partition then cuts nothing).  Pure host arithmetic.
+inline uint32_t ws_choose_slots(uint32_t n_blocks, uint32_t n_chunks, uint32_t slots, uint32_t whole_max_chunks, uint32_t fill_pct) {
+    if (slots == 0) slots = 1;
+    if (whole_max_chunks && n_blocks < slots && (uint64_t)n_blocks * 100 >= (uint64_t)slots * fill_pct && n_chunks <= whole_max_chunks)
+        return n_blocks;
+    return slots;
+}
+
 // gemv_ws.cu: the partition of the warp-specialised kernels (one CTA per SM)
 SkPart ws_partition(prism_cuda_ctx *ctx, uint32_t n_blocks, uint32_t n_chunks, uint32_t batch, uint32_t fill_pct);
 

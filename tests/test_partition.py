@@ -71,3 +71,23 @@ def test_bad_arguments_are_refused():
     assert L.prism_cuda_gemv_partition(4, 4, 148, 64, 8, None, None, 0) != 0
     small = (C.c_uint32 * 2)()
     assert L.prism_cuda_gemv_partition(128, 256, 148, 64, 8, C.byref(g), small, 2) != 0
+
+
+def test_whole_blocks_when_a_matrix_has_fewer_blocks_than_ctas():
+    """The warp-specialised GEMV uses one CTA per block -- and the partition then cuts no block -- when the
+    matrix has fewer blocks than CTA slots but enough of them, and rows that are not too long."""
+    L = _lib.load()
+    ctas = L.prism_cuda_gemv_partition_ctas
+    # 72B o and down projections on 148 SMs: 128 blocks
+    assert ctas(128, 256, 148, 1024, 50) == 128 and ctas(128, 924, 148, 1024, 50) == 128
+    # more blocks than slots, or rows too long, or switched off: every slot
+    assert ctas(160, 256, 148, 1024, 50) == 148
+    assert ctas(128, 2000, 148, 1024, 50) == 148
+    assert ctas(128, 256, 148, 0, 50) == 148
+    # the fill threshold: 116 blocks are 78 per 100 slots, 73 are 49
+    assert ctas(116, 256, 148, 1024, 50) == 116 and ctas(116, 256, 148, 1024, 85) == 148
+    assert ctas(73, 256, 148, 1024, 50) == 148 and ctas(74, 256, 148, 1024, 50) == 74
+    for n_blocks, n_chunks in ((128, 256), (128, 924), (116, 256), (80, 256)):
+        g = ctas(n_blocks, n_chunks, 148, 1024, 50)
+        b = partition(n_blocks, n_chunks, g)
+        assert len(b) == n_blocks + 1 and np.all(b % n_chunks == 0) and np.all(np.diff(b) == n_chunks)
